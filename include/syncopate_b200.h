@@ -1,0 +1,114 @@
+/*
+ * syncopate_b200 — C ABI of the B200 (sm_100a) backend for Syncopate's chunk-centric overlapped
+ * operators.  Plain C: pointers, sizes and PODs only; every function returns 0 on success or a
+ * negative SYN_ERR_* code (see syn_strerror).  No exception crosses this boundary.
+ *
+ * The library sits behind Syncopate's Python front end: plans are built and lowered on the host
+ * (build_*_plan -> CommGenerator.plan_signals / generate_code_for_plan ->
+ * lower_comm_plan_to_raw_schedules) and the per-rank wave offsets / shapes / signal indices / peer
+ * ranks produced by RawSchedule.gen_*_lists() (syncopate/interface/tile_schedule.py:90-145) are
+ * handed to the kernels below as HOST arrays; the library copies them into kernel parameters.
+ *
+ * Threading: a syn_ctx belongs to one host thread of one process (one process per GPU).
+ * Device pointers are CUDA device pointers of the current device unless stated otherwise.
+ * `stream` is a cudaStream_t passed as void* (NULL = legacy default stream).
+ */
+#ifndef SYNCOPATE_B200_H
+#define SYNCOPATE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SYN_MAX_WORLD 8
+#define SYN_MAX_WAVES 128
+#define SYN_MAX_COMM_OPS 64
+
+/* ------------------------------------------------------------------ error codes */
+#define SYN_OK 0
+#define SYN_ERR_INVALID (-1)       /* bad argument (NULL, negative size, unsupported block, ...) */
+#define SYN_ERR_SHAPE (-2)         /* schedule entry out of bounds or not a multiple of the block */
+#define SYN_ERR_CUDA (-3)          /* a CUDA runtime / driver call failed (syn_last_cuda_error) */
+#define SYN_ERR_TIMEOUT_FLAG (-4)  /* device: a signal flag never reached its value */
+#define SYN_ERR_TIMEOUT_MBAR (-5)  /* device: an intra-kernel pipeline wait ran out */
+#define SYN_ERR_TIMEOUT_COUNTER (-6)
+#define SYN_ERR_RENDEZVOUS (-7)    /* peers did not show up at the rendezvous in time */
+#define SYN_ERR_UNSUPPORTED (-8)
+#define SYN_ERR_TOO_LARGE (-9)     /* more waves / ops / bytes than the fixed limits above */
+
+const char* syn_strerror(int code);
+/* Text of the last CUDA error seen by this thread inside the library ("" if none). */
+const char* syn_last_cuda_error(void);
+/* Library version and the SM architecture it was compiled for (always "sm_100a"). */
+const char* syn_version(void);
+
+/* ------------------------------------------------------------------ schedules
+ * One lowered RawSchedule (syncopate/interface/tile_schedule.py:65-171), flattened wave-major.
+ * All arrays are HOST memory, int32, in ELEMENTS of the scheduled tensor (not tiles):
+ *   offsets[w*ndim + d], shapes[w*ndim + d]   gen_block_offset_lists / gen_block_shape_lists
+ *   signals[w]       flag index the wave waits on (consumer) or sets when complete (producer), -1 = none
+ *   target_ranks[w]  peer that owns / receives the wave's data, -1 or own rank = local (may be NULL)
+ *   dst_offsets[w*ndim + d]  offsets on the peer side (may be NULL = same as offsets)
+ * ndim = 2 for GEMM (M, N) and 4 for attention (Z, H, Q, KV).
+ */
+typedef struct syn_schedule {
+  int32_t num_waves;
+  int32_t ndim;
+  const int32_t* offsets;
+  const int32_t* shapes;
+  const int32_t* signals;
+  const int32_t* target_ranks;
+  const int32_t* dst_offsets;
+} syn_schedule;
+
+/* ------------------------------------------------------------------ GEMM
+ * C[M,N] = A[M,K] * B[N,K]^T, 16-bit inputs, fp32 accumulation in tensor memory, 16-bit output.
+ * Replaces the Triton persistent GEMM templates (syncopate/computation/gemm/template.py:21-159
+ * consumer, :224-351 producer; local_code.py:18-107 un-fused).  Tile order = waves in array order,
+ * grouped raster with GROUP_SIZE_M inside each wave (template.py:10-18, :103-136).
+ */
+#define SYN_DTYPE_F16 0
+#define SYN_DTYPE_BF16 1
+
+typedef struct syn_gemm_args {
+  const void* a; /* [M, K] row-major, leading dimension lda (elements) */
+  const void* b; /* [N, K] row-major (K-major weights), leading dimension ldb */
+  void* c;       /* [M, N] row-major, leading dimension ldc */
+  int32_t M, N, K;
+  int32_t lda, ldb, ldc;
+  int32_t dtype;        /* SYN_DTYPE_* */
+  int32_t block_m;      /* 128 (0 = default) */
+  int32_t block_n;      /* 64..256, multiple of 16 (0 = choose to minimise tail quantisation) */
+  int32_t block_k;      /* 64 (0 = default) */
+  int32_t group_size_m; /* grouped-raster height, 0 = 8 */
+  int32_t num_sms;      /* persistent grid size, 0 = all SMs of the device */
+  /* Signal flags (uint64 words, device memory).  A wave with signals[w] >= 0 starts only once
+   * signal_ptr[signals[w]] >= signal_value (consumer), or sets it to signal_value after its last
+   * tile is stored (producer; needs counter_ptr: uint32[num_waves], zero at the first call, kept
+   * by the library as a running count thereafter). */
+  const uint64_t* consumer_signal_ptr;
+  uint64_t* producer_signal_ptr;
+  uint32_t* producer_counter_ptr;
+  uint64_t signal_value;   /* value waited for / written; 0 = 1 */
+  uint64_t timeout_ns;     /* bound of every device-side wait; 0 = 2 s */
+  int32_t* status;         /* device int32[4] {code, wave, flag, block}; may be NULL */
+} syn_gemm_args;
+
+/* Un-fused / flag-gated persistent GEMM on one GPU.  `sched` may be NULL (one wave = whole C);
+ * `producer_sched` is the RawSchedule of C when the GEMM feeds communication (may be NULL).
+ * When both are given they must describe the same tile order (same shapes), as in the reference's
+ * dual-role kernels (syncopate/computation/transform/transformer.py:1086-1116). */
+int syn_gemm(const syn_gemm_args* args, const syn_schedule* sched, const syn_schedule* producer_sched,
+             void* stream);
+
+/* Smallest persistent-grid tail for an M x N output on `num_sms` SMs: returns the block_n the
+ * library would choose for block_n = 0. */
+int syn_gemm_pick_block_n(int M, int N, int num_sms);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SYNCOPATE_B200_H */

@@ -1,0 +1,165 @@
+"""ctypes binding of ``libsyncopate_b200.so`` (the C ABI declared in ``include/syncopate_b200.h``).
+
+The shared library is built in-tree by :mod:`syncopate_b200.build` (``nvcc`` for sm_100a).  There is
+no fallback of any kind: when the library is missing, :func:`lib` raises ``RuntimeError``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Optional, Sequence
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libsyncopate_b200.so")
+
+SYN_MAX_WORLD = 8
+SYN_DTYPE_F16 = 0
+SYN_DTYPE_BF16 = 1
+
+ERRORS = {
+    0: "SYN_OK",
+    -1: "SYN_ERR_INVALID",
+    -2: "SYN_ERR_SHAPE",
+    -3: "SYN_ERR_CUDA",
+    -4: "SYN_ERR_TIMEOUT_FLAG",
+    -5: "SYN_ERR_TIMEOUT_MBAR",
+    -6: "SYN_ERR_TIMEOUT_COUNTER",
+    -7: "SYN_ERR_RENDEZVOUS",
+    -8: "SYN_ERR_UNSUPPORTED",
+    -9: "SYN_ERR_TOO_LARGE",
+}
+
+
+class SynError(RuntimeError):
+    """A C-ABI call returned a negative code."""
+
+    def __init__(self, code: int, where: str, detail: str = ""):
+        self.code = code
+        name = ERRORS.get(code, str(code))
+        msg = f"{where}: {name}"
+        if detail:
+            msg += f" ({detail})"
+        super().__init__(msg)
+
+
+class Schedule(C.Structure):
+    """``syn_schedule``."""
+
+    _fields_ = [
+        ("num_waves", C.c_int32),
+        ("ndim", C.c_int32),
+        ("offsets", C.POINTER(C.c_int32)),
+        ("shapes", C.POINTER(C.c_int32)),
+        ("signals", C.POINTER(C.c_int32)),
+        ("target_ranks", C.POINTER(C.c_int32)),
+        ("dst_offsets", C.POINTER(C.c_int32)),
+    ]
+
+
+class GemmArgs(C.Structure):
+    """``syn_gemm_args``."""
+
+    _fields_ = [
+        ("a", C.c_void_p),
+        ("b", C.c_void_p),
+        ("c", C.c_void_p),
+        ("M", C.c_int32),
+        ("N", C.c_int32),
+        ("K", C.c_int32),
+        ("lda", C.c_int32),
+        ("ldb", C.c_int32),
+        ("ldc", C.c_int32),
+        ("dtype", C.c_int32),
+        ("block_m", C.c_int32),
+        ("block_n", C.c_int32),
+        ("block_k", C.c_int32),
+        ("group_size_m", C.c_int32),
+        ("num_sms", C.c_int32),
+        ("consumer_signal_ptr", C.c_void_p),
+        ("producer_signal_ptr", C.c_void_p),
+        ("producer_counter_ptr", C.c_void_p),
+        ("signal_value", C.c_uint64),
+        ("timeout_ns", C.c_uint64),
+        ("status", C.c_void_p),
+    ]
+
+
+_lib: Optional[C.CDLL] = None
+
+
+def lib() -> C.CDLL:
+    """Loads the shared library once; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m syncopate_b200.build` "
+                "(nvcc, sm_100a). There is no CPU or PyTorch fallback."
+            )
+        _lib = C.CDLL(LIB_PATH, mode=C.RTLD_GLOBAL)
+        _declare(_lib)
+    return _lib
+
+
+def _declare(l: C.CDLL) -> None:
+    l.syn_strerror.restype = C.c_char_p
+    l.syn_strerror.argtypes = [C.c_int]
+    l.syn_last_cuda_error.restype = C.c_char_p
+    l.syn_version.restype = C.c_char_p
+    l.syn_gemm.restype = C.c_int
+    l.syn_gemm.argtypes = [C.POINTER(GemmArgs), C.POINTER(Schedule), C.POINTER(Schedule), C.c_void_p]
+    l.syn_gemm_pick_block_n.restype = C.c_int
+    l.syn_gemm_pick_block_n.argtypes = [C.c_int, C.c_int, C.c_int]
+
+
+def check(code: int, where: str) -> None:
+    if code != 0:
+        detail = ""
+        if code == -3:
+            detail = lib().syn_last_cuda_error().decode()
+        raise SynError(code, where, detail)
+
+
+def int32_array(values: Optional[Sequence[int]]):
+    """Host int32 array (kept alive by the caller) or a NULL pointer."""
+    if values is None:
+        return None, C.POINTER(C.c_int32)()
+    flat = [int(v) for v in values]
+    arr = (C.c_int32 * max(len(flat), 1))(*flat)
+    return arr, C.cast(arr, C.POINTER(C.c_int32))
+
+
+def make_schedule(offsets, shapes, signals=None, target_ranks=None, dst_offsets=None, ndim: int = 2):
+    """Builds a ``syn_schedule`` from nested Python lists (the ``RawSchedule.gen_*`` outputs).
+
+    Returns ``(struct, keepalive)``; keep ``keepalive`` referenced until the call returns.
+    """
+
+    def flat(x):
+        if x is None:
+            return None
+        out = []
+        for row in x:
+            if isinstance(row, (list, tuple)):
+                out.extend(int(v) for v in row)
+            else:
+                out.append(int(row))
+        return out
+
+    offs, shp = flat(offsets), flat(shapes)
+    nw = len(shp) // ndim
+    keep = []
+    s = Schedule()
+    s.num_waves = nw
+    s.ndim = ndim
+    for name, vals in (
+        ("offsets", offs),
+        ("shapes", shp),
+        ("signals", flat(signals)),
+        ("target_ranks", flat(target_ranks)),
+        ("dst_offsets", flat(dst_offsets)),
+    ):
+        arr, ptr = int32_array(vals)
+        keep.append(arr)
+        setattr(s, name, ptr)
+    return s, keep

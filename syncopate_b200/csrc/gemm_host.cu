@@ -1,0 +1,240 @@
+// Host side of the GEMM entry points: argument checks, schedule -> kernel-parameter tables,
+// tensor maps, block-size choice, launch.
+#include "gemm_host.h"
+
+#include <algorithm>
+
+namespace syn {
+
+static inline int cdiv(int a, int b) { return (a + b - 1) / b; }
+
+static const int kBlockN[] = {256, 224, 192, 160, 128, 96, 64};
+
+static bool block_n_ok(const syn_schedule* s, int N, int bn) {
+  if (s == nullptr) return true;
+  for (int w = 0; w < s->num_waves; ++w) {
+    const int off = s->offsets[w * 2 + 1], len = s->shapes[w * 2 + 1];
+    if (off % bn != 0) return false;
+    if (len % bn != 0 && off + len != N) return false;
+  }
+  return true;
+}
+
+static long count_tiles(const syn_schedule* s, int M, int N, int bn) {
+  if (s == nullptr) return static_cast<long>(cdiv(M, GEMM_BM)) * cdiv(N, bn);
+  long t = 0;
+  for (int w = 0; w < s->num_waves; ++w)
+    t += static_cast<long>(cdiv(s->shapes[w * 2], GEMM_BM)) * cdiv(s->shapes[w * 2 + 1], bn);
+  return t;
+}
+
+int pick_block_n(const syn_schedule* s, int M, int N, int num_sms) {
+  int best = 0;
+  double best_cost = 0;
+  for (int bn : kBlockN) {
+    if (!block_n_ok(s, N, bn)) continue;
+    const long tiles = count_tiles(s, M, N, bn);
+    const long rounds = (tiles + num_sms - 1) / num_sms;
+    // time of a round grows with the tile width; narrow tiles re-read A more often and pay a
+    // larger fixed cost per tile, hence the small bias towards wide tiles
+    const double cost = static_cast<double>(rounds) * (bn + 16);
+    if (best == 0 || cost < best_cost - 1e-9) {
+      best = bn;
+      best_cost = cost;
+    }
+  }
+  return best;
+}
+
+int validate_schedule_2d(const syn_schedule* s, int M, int N, int bn) {
+  if (s == nullptr) return SYN_OK;
+  if (s->ndim != 2 || s->num_waves <= 0 || s->offsets == nullptr || s->shapes == nullptr) return SYN_ERR_INVALID;
+  if (s->num_waves > GEMM_MAX_WAVES) return SYN_ERR_TOO_LARGE;
+  for (int w = 0; w < s->num_waves; ++w) {
+    const int om = s->offsets[w * 2], on = s->offsets[w * 2 + 1];
+    const int sm = s->shapes[w * 2], sn = s->shapes[w * 2 + 1];
+    if (om < 0 || on < 0 || sm <= 0 || sn <= 0) return SYN_ERR_SHAPE;
+    if (om + sm > M || on + sn > N) return SYN_ERR_SHAPE;
+    if (om % GEMM_BM != 0 || on % bn != 0) return SYN_ERR_SHAPE;
+    if (sm % GEMM_BM != 0 && om + sm != M) return SYN_ERR_SHAPE;
+    if (sn % bn != 0 && on + sn != N) return SYN_ERR_SHAPE;
+  }
+  return SYN_OK;
+}
+
+int gemm_fill_common(GemmParams* p, const syn_gemm_args* a, const syn_schedule* sched, int bn) {
+  if (a == nullptr || a->a == nullptr || a->b == nullptr || a->c == nullptr) return SYN_ERR_INVALID;
+  if (a->M <= 0 || a->N <= 0 || a->K <= 0) return SYN_ERR_INVALID;
+  if (a->dtype != SYN_DTYPE_F16 && a->dtype != SYN_DTYPE_BF16) return SYN_ERR_UNSUPPORTED;
+  if (a->block_m != 0 && a->block_m != GEMM_BM) return SYN_ERR_UNSUPPORTED;
+  if (a->block_k != 0 && a->block_k != GEMM_BK) return SYN_ERR_UNSUPPORTED;
+  const int lda = a->lda ? a->lda : a->K, ldb = a->ldb ? a->ldb : a->K, ldc = a->ldc ? a->ldc : a->N;
+  if (lda < a->K || ldb < a->K || ldc < a->N) return SYN_ERR_INVALID;
+  // TMA wants 16-byte aligned bases and row pitches; the epilogue stores 16-byte vectors
+  if ((lda % 8) || (ldb % 8) || (ldc % 8) || (a->N % 8)) return SYN_ERR_INVALID;
+  if ((reinterpret_cast<uintptr_t>(a->a) & 15) || (reinterpret_cast<uintptr_t>(a->b) & 15) ||
+      (reinterpret_cast<uintptr_t>(a->c) & 15))
+    return SYN_ERR_INVALID;
+  int rc = validate_schedule_2d(sched, a->M, a->N, bn);
+  if (rc != SYN_OK) return rc;
+
+  memset(p, 0, sizeof(*p));
+  rc = encode_tmap_2d_sw128(&p->tmap_a, a->a, a->M, a->K, lda, GEMM_BM, GEMM_BK);
+  if (rc != SYN_OK) return rc;
+  rc = encode_tmap_2d_sw128(&p->tmap_b, a->b, a->N, a->K, ldb, bn, GEMM_BK);
+  if (rc != SYN_OK) return rc;
+  p->c = a->c;
+  p->ldc = ldc;
+  p->M = a->M;
+  p->N = a->N;
+  p->K = a->K;
+  p->k_blocks = cdiv(a->K, GEMM_BK);
+  p->dtype = a->dtype;
+  p->idesc = make_idesc_f16(GEMM_BM, bn, a->dtype == SYN_DTYPE_BF16 ? 1u : 0u, 0, 0);
+  p->group_m = a->group_size_m > 0 ? a->group_size_m : 8;
+  p->csig = a->consumer_signal_ptr;
+  p->counters = a->producer_counter_ptr;
+  p->signal_value = a->signal_value ? a->signal_value : 1;
+  p->timeout_ns = a->timeout_ns ? a->timeout_ns : 2000000000ull;
+  p->status = a->status;
+
+  int cum = 0;
+  if (sched == nullptr) {
+    GemmWave& w = p->waves[0];
+    w.tiles_m = static_cast<int16_t>(cdiv(a->M, GEMM_BM));
+    w.tiles_n = static_cast<int16_t>(cdiv(a->N, bn));
+    w.off_m = w.off_n = 0;
+    w.csig = -1;
+    w.route = -1;
+    cum = w.tiles_m * w.tiles_n;
+    w.cum = cum;
+    p->num_waves = 1;
+  } else {
+    for (int i = 0; i < sched->num_waves; ++i) {
+      GemmWave& w = p->waves[i];
+      const int tm = cdiv(sched->shapes[i * 2], GEMM_BM), tn = cdiv(sched->shapes[i * 2 + 1], bn);
+      if (tm > 32767 || tn > 32767) return SYN_ERR_TOO_LARGE;
+      w.tiles_m = static_cast<int16_t>(tm);
+      w.tiles_n = static_cast<int16_t>(tn);
+      w.off_m = static_cast<int16_t>(sched->offsets[i * 2] / GEMM_BM);
+      w.off_n = static_cast<int16_t>(sched->offsets[i * 2 + 1] / bn);
+      const int sig = sched->signals ? sched->signals[i] : -1;
+      if (sig > 32767) return SYN_ERR_TOO_LARGE;
+      w.csig = static_cast<int16_t>(a->consumer_signal_ptr != nullptr ? sig : -1);
+      w.route = -1;
+      cum += tm * tn;
+      w.cum = cum;
+    }
+    p->num_waves = sched->num_waves;
+  }
+  p->total_tiles = cum;
+  return SYN_OK;
+}
+
+template <int BN, bool FUSED>
+static int launch_bn(const GemmParams& p, int grid, cudaStream_t stream) {
+  using L = GemmSmem<BN>;
+  constexpr int kMaxSmem = 232448;
+  constexpr int kFixed = 1024 /*alignment slack*/ + (FUSED ? COMM_NBUF * COMM_PIECE : 0) + 256 /*barriers*/;
+  constexpr int kStagesRaw = (kMaxSmem - kFixed) / L::STAGE_BYTES;
+  constexpr int STAGES = kStagesRaw > 6 ? 6 : kStagesRaw;
+  static_assert(STAGES >= 3, "shared-memory ring too shallow");
+  constexpr int smem = STAGES * L::STAGE_BYTES + kFixed;
+  auto kern = gemm_kernel<BN, STAGES, FUSED>;
+  static bool configured = false;  // per instantiation; attribute is per device but all devices are B200s
+  static int configured_dev = -1;
+  int dev = 0;
+  SYN_CUDA_TRY(cudaGetDevice(&dev));
+  if (!configured || configured_dev != dev) {
+    SYN_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured = true;
+    configured_dev = dev;
+  }
+  kern<<<grid, GEMM_THREADS, smem, stream>>>(p);
+  SYN_CUDA_TRY(cudaGetLastError());
+  return SYN_OK;
+}
+
+int gemm_launch(const GemmParams& p, int bn, bool fused, int grid, cudaStream_t stream) {
+#define SYN_BN_CASE(BN_)                                                     \
+  case BN_:                                                                  \
+    return fused ? launch_bn<BN_, true>(p, grid, stream) : launch_bn<BN_, false>(p, grid, stream);
+  switch (bn) {
+    SYN_BN_CASE(256)
+    SYN_BN_CASE(224)
+    SYN_BN_CASE(192)
+    SYN_BN_CASE(160)
+    SYN_BN_CASE(128)
+    SYN_BN_CASE(96)
+    SYN_BN_CASE(64)
+    default:
+      return SYN_ERR_UNSUPPORTED;
+  }
+#undef SYN_BN_CASE
+}
+
+int gemm_resolve_grid_and_bn(const syn_gemm_args* a, const syn_schedule* sched, int* grid, int* bn) {
+  int sms = 0;
+  int rc = device_sm_count(&sms);
+  if (rc != SYN_OK) return rc;
+  int g = a->num_sms > 0 ? std::min(a->num_sms, sms) : sms;
+  int b = a->block_n;
+  if (b == 0) b = pick_block_n(sched, a->M, a->N, g);
+  if (b == 0) return SYN_ERR_SHAPE;
+  *grid = g;
+  *bn = b;
+  return SYN_OK;
+}
+
+}  // namespace syn
+
+extern "C" {
+
+int syn_gemm_pick_block_n(int M, int N, int num_sms) {
+  if (M <= 0 || N <= 0 || num_sms <= 0) return SYN_ERR_INVALID;
+  return syn::pick_block_n(nullptr, M, N, num_sms);
+}
+
+int syn_gemm(const syn_gemm_args* args, const syn_schedule* sched, const syn_schedule* producer_sched,
+             void* stream) {
+  using namespace syn;
+  if (args == nullptr) return SYN_ERR_INVALID;
+  int grid = 0, bn = 0;
+  int rc = gemm_resolve_grid_and_bn(args, sched ? sched : producer_sched, &grid, &bn);
+  if (rc != SYN_OK) return rc;
+  const syn_schedule* order = sched ? sched : producer_sched;
+  GemmParams p;
+  rc = gemm_fill_common(&p, args, order, bn);
+  if (rc != SYN_OK) return rc;
+  bool fused = false;
+  if (producer_sched != nullptr && args->producer_signal_ptr != nullptr) {
+    if (args->producer_counter_ptr == nullptr) return SYN_ERR_INVALID;
+    if (sched != nullptr) {
+      // dual role: both schedules must walk the same tiles in the same order
+      if (sched->num_waves != producer_sched->num_waves) return SYN_ERR_SHAPE;
+      for (int i = 0; i < sched->num_waves * 2; ++i)
+        if (sched->offsets[i] != producer_sched->offsets[i] || sched->shapes[i] != producer_sched->shapes[i])
+          return SYN_ERR_SHAPE;
+    }
+    rc = validate_schedule_2d(producer_sched, args->M, args->N, bn);
+    if (rc != SYN_OK) return rc;
+    for (int i = 0; i < producer_sched->num_waves; ++i) {
+      const int sig = producer_sched->signals ? producer_sched->signals[i] : -1;
+      if (sig < 0) continue;
+      GemmRoute& r = p.routes[i];
+      r.base = static_cast<char*>(args->c) +
+               static_cast<size_t>(producer_sched->offsets[i * 2]) * p.ldc * 2;
+      r.ld = p.ldc;
+      r.flag = args->producer_signal_ptr + sig;
+      r.gate = nullptr;
+      r.reduce = 0;
+      p.waves[i].route = static_cast<int16_t>(i);
+      fused = true;
+    }
+  }
+  grid = std::min(grid, p.total_tiles);
+  if (grid <= 0) return SYN_ERR_INVALID;
+  return gemm_launch(p, bn, fused, grid, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,447 @@
+// Persistent, warp-specialised bf16/fp16 GEMM for sm_100a: TMA-fed shared-memory ring,
+// tcgen05.mma with fp32 accumulators double-buffered in tensor memory, wave-ordered tile
+// scheduler with signal flags, optional in-kernel communication:
+//   * comm warp: every CTA copies its share of each scheduled chunk between peer-mapped
+//     buffers with bulk async copies and publishes a per-chunk flag (all-gather + GEMM),
+//   * routed epilogue: a wave's tiles are stored to a peer's staging slab and the peer's flag
+//     is raised after the wave's last tile; the wave that owns the local slab adds the staged
+//     partial sums in fp32 before storing (GEMM + reduce-scatter).
+//
+// Behaviour follows Syncopate's Triton templates: consumer wait per wave
+// (syncopate/computation/gemm/template.py:90-128), producer counter + notify (:343-348),
+// grouped raster inside a wave (:10-18, :130-136).
+#pragma once
+#include "ptx.cuh"
+
+namespace syn {
+
+constexpr int GEMM_BM = 128;
+constexpr int GEMM_BK = 64;          // 64 x 16-bit = one 128-byte swizzle row
+constexpr int GEMM_UMMA_K = 16;
+constexpr int GEMM_MAX_WAVES = 64;
+constexpr int GEMM_MAX_COMM_OPS = 64;
+constexpr int GEMM_THREADS = 256;    // warp0 TMA, warp1 MMA, warp2 TMEM alloc, warp3 comm, warps4-7 epilogue
+constexpr int COMM_PIECE = 8192;     // bytes per bulk copy of the comm warp
+constexpr int COMM_NBUF = 4;
+
+struct GemmWave {
+  int16_t tiles_m, tiles_n;  // tile grid of the wave
+  int16_t off_m, off_n;      // first tile of the wave (tile units)
+  int16_t csig;              // consumer flag index, -1 = none
+  int16_t route;             // index into GemmParams::routes, -1 = plain local store
+  int32_t cum;               // tiles in waves [0, w]
+};
+
+// Where the tiles of a wave go, and what to raise when the wave is complete.
+struct GemmRoute {
+  void* base;             // address of element (row off_m*BM, col 0) of the wave in the destination
+  uint64_t* flag;         // raised to `signal_value` after the last tile (local or peer memory); may be null
+  const uint64_t* gate;   // flag that must be >= gate_value before the first store of the wave; may be null
+  uint64_t gate_value;
+  int32_t ld;             // destination leading dimension (elements)
+  int32_t reduce;         // 1 = add the staged partial sums (reduce-scatter owner wave)
+};
+
+// One 2-D strided copy between mapped buffers, executed cooperatively by all comm warps.
+struct CommOp {
+  const char* src;
+  char* dst;
+  uint64_t src_pitch, dst_pitch;
+  uint32_t rows, row_bytes;
+  const uint64_t* wait_flag;  // local flag that must be >= signal_value before the copy; may be null
+  uint64_t* set_flag;         // raised after every CTA's share has landed; may be null
+};
+
+struct GemmParams {
+  CUtensorMap tmap_a;
+  CUtensorMap tmap_b;
+  void* c;
+  int32_t ldc;
+  int32_t M, N, K;
+  int32_t k_blocks;
+  int32_t dtype;          // 0 fp16, 1 bf16
+  uint32_t idesc;
+  int32_t group_m;
+  int32_t total_tiles;
+  int32_t num_waves;
+  int32_t num_comm_ops;
+  int32_t num_red;        // staged partial slabs to add in `reduce` routes
+  int32_t red_ld;
+  const uint64_t* csig;   // consumer flags
+  uint32_t* counters;     // [num_waves] producer counters then [num_comm_ops] comm counters, self-resetting
+  uint64_t signal_value;
+  uint64_t timeout_ns;
+  int32_t* status;
+  const void* red_src[7];       // staged slabs (address of the slab's row 0)
+  const uint64_t* red_flag[7];  // flag guarding each slab
+  GemmWave waves[GEMM_MAX_WAVES];
+  GemmRoute routes[GEMM_MAX_WAVES];
+  CommOp comm[GEMM_MAX_COMM_OPS];
+};
+
+struct TileCursor {
+  int wave = 0;
+  int past = 0;
+  // Maps a global tile id (monotone per CTA) to its wave and tile coordinates.
+  __device__ __forceinline__ bool seek(const GemmParams& p, int tile, int& m_blk, int& n_blk) {
+    bool moved = false;
+    while (tile >= p.waves[wave].cum) {
+      past = p.waves[wave].cum;
+      ++wave;
+      moved = true;
+    }
+    const int local = tile - past;
+    const int tm = p.waves[wave].tiles_m, tn = p.waves[wave].tiles_n;
+    const int in_group = p.group_m * tn;
+    const int group_id = local / in_group;
+    const int first_m = group_id * p.group_m;
+    const int gsz = min(tm - first_m, p.group_m);
+    const int r = local - group_id * in_group;
+    m_blk = first_m + (r % gsz) + p.waves[wave].off_m;
+    n_blk = (r / gsz) + p.waves[wave].off_n;
+    return moved;
+  }
+};
+
+template <int BN>
+struct GemmSmem {
+  static constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;
+  static constexpr int B_BYTES = BN * GEMM_BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+};
+
+__device__ __forceinline__ uint32_t pack2(float lo, float hi, int dtype) {
+  if (dtype == 1) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  } else {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+}
+__device__ __forceinline__ float2 unpack2(uint32_t u, int dtype) {
+  if (dtype == 1) {
+    return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u));
+  } else {
+    return __half22float2(*reinterpret_cast<__half2*>(&u));
+  }
+}
+
+// The comm warp of each CTA: walks the op list in order; for each op copies pieces
+// blockIdx.x, blockIdx.x + gridDim.x, ... through a small shared-memory ring.
+__device__ __forceinline__ void comm_warp_run(const CommOp* ops, int num_ops, uint32_t* counters,
+                                              uint64_t signal_value, char* ring, uint64_t* bars,
+                                              volatile int* abort_word, uint64_t timeout_ns, int lane) {
+  uint32_t issued = 0;    // loads issued so far, over all ops (ring slot = n % NBUF, parity = (n / NBUF) & 1)
+  uint32_t consumed = 0;  // stores issued so far, over all ops (same order as the loads)
+  for (int o = 0; o < num_ops; ++o) {
+    const CommOp& op = ops[o];
+    if (lane == 0) {
+      if (op.wait_flag != nullptr) flag_wait_ge(op.wait_flag, signal_value, abort_word, timeout_ns);
+      const uint32_t ppr = (op.row_bytes + COMM_PIECE - 1) / COMM_PIECE;
+      const uint32_t total = op.rows * ppr;
+      constexpr uint32_t LOOKAHEAD = COMM_NBUF - 2;
+      uint32_t next_load = blockIdx.x;  // piece index of the next load to issue
+      uint32_t cur = blockIdx.x;        // piece index of the next store to issue
+      auto issue_load = [&](uint32_t piece) {
+        const uint32_t row = piece / ppr, col = (piece - row * ppr) * COMM_PIECE;
+        const uint32_t bytes = min(static_cast<uint32_t>(COMM_PIECE), op.row_bytes - col);
+        const uint32_t slot = issued % COMM_NBUF;
+        mbar_expect_tx(&bars[slot], bytes);
+        bulk_g2s(ring + slot * COMM_PIECE, op.src + row * op.src_pitch + col, bytes, &bars[slot]);
+        ++issued;
+      };
+      while (issued - consumed < LOOKAHEAD && next_load < total) {
+        issue_load(next_load);
+        next_load += gridDim.x;
+      }
+      while (cur < total) {
+        if (next_load < total) {
+          // the slot about to be refilled was last read by a store at least two groups back
+          bulk_wait_read<1>();
+          issue_load(next_load);
+          next_load += gridDim.x;
+        }
+        const uint32_t slot = consumed % COMM_NBUF;
+        mbar_wait(&bars[slot], (consumed / COMM_NBUF) & 1u, abort_word, timeout_ns);
+        const uint32_t row = cur / ppr, col = (cur - row * ppr) * COMM_PIECE;
+        const uint32_t bytes = min(static_cast<uint32_t>(COMM_PIECE), op.row_bytes - col);
+        bulk_s2g(op.dst + row * op.dst_pitch + col, ring + slot * COMM_PIECE, bytes);
+        bulk_commit();
+        ++consumed;
+        cur += gridDim.x;
+      }
+      bulk_wait<0>();
+      fence_proxy_async();
+      if (op.set_flag != nullptr) {
+        __threadfence_system();
+        const uint32_t old = atomicAdd(&counters[o], 1u);
+        if (old == gridDim.x - 1) {
+          counters[o] = 0;
+          __threadfence_system();
+          st_release_sys_u64(op.set_flag, signal_value);
+        }
+      }
+    }
+  }
+}
+
+template <int BN, int STAGES, bool FUSED>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_kernel(const __grid_constant__ GemmParams p) {
+  using L = GemmSmem<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * L::A_BYTES;
+  uint8_t* ring = smem + STAGES * L::STAGE_BYTES;  // FUSED only
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ring + (FUSED ? COMM_NBUF * COMM_PIECE : 0));
+  uint64_t* full_bar = bars;
+  uint64_t* empty_bar = bars + STAGES;
+  uint64_t* tfull_bar = bars + 2 * STAGES;
+  uint64_t* tempty_bar = bars + 2 * STAGES + 2;
+  uint64_t* comm_bar = bars + 2 * STAGES + 4;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4 + COMM_NBUF);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  int* abort_info = const_cast<int*>(abort_word) + 1;  // {wave, flag}
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  constexpr uint32_t TMEM_COLS = (2 * BN <= 256) ? 256 : 512;
+  constexpr int ACC_STRIDE = TMEM_COLS / 2;  // column offset of the second accumulator
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull_bar[i], 1);
+      mbar_init(&tempty_bar[i], 4);
+    }
+    for (int i = 0; i < COMM_NBUF; ++i) mbar_init(&comm_bar[i], 1);
+    *abort_word = 0;
+    abort_info[0] = -1;
+    abort_info[1] = -1;
+    fence_mbar_init();
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_holder, TMEM_COLS);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    prefetch_tmap(&p.tmap_a);
+    prefetch_tmap(&p.tmap_b);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      TileCursor cur;
+      int stage = 0;
+      uint32_t phase = 0;
+      bool first = true;
+      for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
+        int m_blk, n_blk;
+        const bool moved = cur.seek(p, tile, m_blk, n_blk);
+        if (moved || first) {
+          const int sig = p.waves[cur.wave].csig;
+          if (sig >= 0 && p.csig != nullptr) {
+            if (!flag_wait_ge(p.csig + sig, p.signal_value, abort_word, p.timeout_ns)) {
+              if (abort_info[0] < 0) {
+                abort_info[0] = cur.wave;
+                abort_info[1] = sig;
+              }
+            }
+            fence_proxy_async();  // order the flag read before async-proxy (TMA) reads of the chunk
+          }
+          first = false;
+        }
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          mbar_wait(&empty_bar[stage], phase ^ 1u, abort_word, p.timeout_ns);
+          mbar_expect_tx(&full_bar[stage], L::STAGE_BYTES);
+          tma_load_2d(sA + stage * L::A_BYTES, &p.tmap_a, &full_bar[stage], kb * GEMM_BK, m_blk * GEMM_BM);
+          tma_load_2d(sB + stage * L::B_BYTES, &p.tmap_b, &full_bar[stage], kb * GEMM_BK, n_blk * BN);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
+        mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, abort_word, p.timeout_ns);
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * ACC_STRIDE);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          mbar_wait(&full_bar[stage], phase, abort_word, p.timeout_ns);
+          tc_fence_after();
+          const uint64_t a_desc = make_smem_desc_sw128(smem_u32(sA + stage * L::A_BYTES), 16, 1024);
+          const uint64_t b_desc = make_smem_desc_sw128(smem_u32(sB + stage * L::B_BYTES), 16, 1024);
+#pragma unroll
+          for (int k = 0; k < GEMM_BK / GEMM_UMMA_K; ++k) {
+            // advancing 16 elements along K inside the 128-byte swizzle row = +32 bytes = +2 (16-byte units)
+            umma_f16_ss(d_tmem, a_desc + static_cast<uint64_t>(2 * k), b_desc + static_cast<uint64_t>(2 * k),
+                        p.idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty_bar[stage]);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        umma_commit(&tfull_bar[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else if (warp == 3) {
+    // ------------------------------------------------------------ comm warp
+    if constexpr (FUSED) {
+      comm_warp_run(p.comm, p.num_comm_ops, p.counters + p.num_waves, p.signal_value,
+                    reinterpret_cast<char*>(ring), comm_bar, abort_word, p.timeout_ns, lane);
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------ epilogue (TMEM -> registers -> global)
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    TileCursor cur;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool first = true;
+    bool red_ready = false;
+    for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
+      int m_blk, n_blk;
+      const bool moved = cur.seek(p, tile, m_blk, n_blk);
+      const GemmWave& wv = p.waves[cur.wave];
+      // destination of this tile
+      char* out_base = reinterpret_cast<char*>(p.c);
+      int out_ld = p.ldc;
+      int out_row = m_blk * GEMM_BM + q * 32 + lane;  // row inside the destination
+      const int grow = out_row;                       // global row of C
+      bool reduce = false;
+      if constexpr (FUSED) {
+        if (wv.route >= 0) {
+          const GemmRoute& rt = p.routes[wv.route];
+          out_base = reinterpret_cast<char*>(rt.base);
+          out_ld = rt.ld;
+          out_row -= wv.off_m * GEMM_BM;
+          reduce = rt.reduce != 0;
+          if ((moved || first) && rt.gate != nullptr) {
+            if (lane == 0) flag_wait_ge(rt.gate, rt.gate_value, abort_word, p.timeout_ns);
+            __syncwarp();
+          }
+          if (reduce && !red_ready) {
+            if (lane < p.num_red) {
+              if (!flag_wait_ge(p.red_flag[lane], p.signal_value, abort_word, p.timeout_ns)) {
+                abort_info[0] = cur.wave;
+                abort_info[1] = -2 - lane;
+              }
+            }
+            __syncwarp();
+            red_ready = true;
+          }
+        }
+      }
+      first = false;
+      mbar_wait(&tfull_bar[acc], acc_phase, abort_word, p.timeout_ns);
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * ACC_STRIDE);
+      const int col0 = n_blk * BN;
+      const bool row_ok = grow < p.M;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c * 32, r);
+        tmem_ld_wait();
+        const int col = col0 + c * 32;
+        if constexpr (FUSED) {
+          if (reduce && row_ok) {
+            // add the partial sums staged by the peers (16-bit on the wire, fp32 here)
+            for (int s = 0; s < p.num_red; ++s) {
+              const uint4* src = reinterpret_cast<const uint4*>(
+                  reinterpret_cast<const char*>(p.red_src[s]) +
+                  (static_cast<size_t>(out_row) * p.red_ld + col) * 2);
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                if (col + v * 8 < p.N) {
+                  const uint4 u = __ldcg(src + v);
+                  const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    const float2 f = unpack2(w4[j], p.dtype);
+                    r[v * 8 + 2 * j] = __float_as_uint(__uint_as_float(r[v * 8 + 2 * j]) + f.x);
+                    r[v * 8 + 2 * j + 1] = __float_as_uint(__uint_as_float(r[v * 8 + 2 * j + 1]) + f.y);
+                  }
+                }
+              }
+            }
+          }
+        }
+        if (row_ok) {
+          uint4* dst = reinterpret_cast<uint4*>(out_base + (static_cast<size_t>(out_row) * out_ld + col) * 2);
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            if (col + v * 8 < p.N) {
+              uint4 u;
+              u.x = pack2(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]), p.dtype);
+              u.y = pack2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]), p.dtype);
+              u.z = pack2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]), p.dtype);
+              u.w = pack2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]), p.dtype);
+              dst[v] = u;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+
+      if constexpr (FUSED) {
+        // wave completion: count stored tiles; the last one raises the wave's flag
+        if (wv.route >= 0 && p.routes[wv.route].flag != nullptr) {
+          __threadfence_system();
+          asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
+          if (warp == 4 && lane == 0) {
+            const uint32_t tiles_w = static_cast<uint32_t>(wv.tiles_m) * static_cast<uint32_t>(wv.tiles_n);
+            __threadfence_system();
+            const uint32_t old = atomicAdd(&p.counters[cur.wave], 1u);
+            if (old == tiles_w - 1) {
+              p.counters[cur.wave] = 0;
+              __threadfence_system();
+              st_release_sys_u64(p.routes[wv.route].flag, p.signal_value);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && *abort_word != 0 && p.status != nullptr) {
+    if (atomicCAS(p.status, 0, *abort_word) == 0) {
+      p.status[1] = abort_info[0];
+      p.status[2] = abort_info[1];
+      p.status[3] = static_cast<int>(blockIdx.x);
+    }
+  }
+}
+
+}  // namespace syn

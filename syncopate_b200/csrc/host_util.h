@@ -1,0 +1,37 @@
+// Host-side helpers shared by the C-ABI translation units: error plumbing, driver entry points
+// (resolved at run time so that the library links without libcuda), tensor-map encoding.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "../../include/syncopate_b200.h"
+
+namespace syn {
+
+void set_cuda_error(const char* what, const char* detail);
+int device_sm_count(int* out);
+
+#define SYN_CUDA_TRY(expr)                                  \
+  do {                                                      \
+    cudaError_t _e = (expr);                                \
+    if (_e != cudaSuccess) {                                \
+      ::syn::set_cuda_error(#expr, cudaGetErrorString(_e)); \
+      return SYN_ERR_CUDA;                                  \
+    }                                                       \
+  } while (0)
+
+// 2-D row-major 16-bit tensor [rows, cols] with leading dimension ld (elements); box = [box_rows, 64]
+// elements with the 128-byte swizzle the UMMA shared-memory descriptors expect.
+int encode_tmap_2d_sw128(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                         uint32_t box_rows, uint32_t box_cols);
+// 3-D variant: [d2, rows, cols] with strides (stride2, ld, 1) in elements.
+int encode_tmap_3d_sw128(CUtensorMap* out, const void* base, uint64_t d2, uint64_t rows, uint64_t cols,
+                         uint64_t stride2, uint64_t ld, uint32_t box_rows, uint32_t box_cols);
+
+// Maps a device status code (ptx.cuh) to the negative C-ABI code.
+int status_to_err(int dev_code);
+
+}  // namespace syn
