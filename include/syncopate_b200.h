@@ -24,7 +24,7 @@ extern "C" {
 #endif
 
 #define SYN_MAX_WORLD 8
-#define SYN_MAX_WAVES 128
+#define SYN_MAX_WAVES 64
 #define SYN_MAX_COMM_OPS 64
 
 /* ------------------------------------------------------------------ error codes */
@@ -107,6 +107,85 @@ int syn_gemm(const syn_gemm_args* args, const syn_schedule* sched, const syn_sch
 /* Smallest persistent-grid tail for an M x N output on `num_sms` SMs: returns the block_n the
  * library would choose for block_n = 0. */
 int syn_gemm_pick_block_n(int M, int N, int num_sms);
+
+/* ------------------------------------------------------------------ symmetric memory
+ * Replaces the NVSHMEM symmetric heap of the reference's CommContext
+ * (syncopate/communication/comm_runtime/communication_context.py:31-76: nvshmem_create_tensors
+ * returns the peer-mapped views of every rank's buffer).  One process per GPU; every rank calls
+ * the same sequence of syn_symm_alloc with the same sizes.  Buffers are cudaMalloc'ed, exported
+ * with CUDA IPC and opened by every peer, so that kernels address a peer's copy through plain
+ * pointers over NVLink.  Handles are exchanged through small files in `rendezvous_dir` (a
+ * directory all ranks of the box can reach, e.g. under /dev/shm or /tmp).
+ */
+typedef struct syn_ctx syn_ctx;
+
+/* View of one symmetric buffer from this rank: ptrs[r] addresses rank r's copy (ptrs[rank] is
+ * local).  Tests on one GPU may fill it by hand with local pointers to emulate several ranks. */
+typedef struct syn_symm {
+  int32_t world;
+  int32_t rank;
+  void* ptrs[SYN_MAX_WORLD];
+} syn_symm;
+
+int syn_ctx_create(int rank, int world, int device, const char* rendezvous_dir, syn_ctx** out);
+/* Unmaps peers, frees local buffers, removes this rank's rendezvous files.  Never blocks on peers. */
+int syn_ctx_destroy(syn_ctx* ctx);
+/* Collective: allocates `bytes` (zero-filled) on every rank and fills `out` with all ranks' pointers.
+ * Waits at most `timeout_s` seconds for the peers (0 = 120 s) and returns SYN_ERR_RENDEZVOUS after. */
+int syn_symm_alloc(syn_ctx* ctx, size_t bytes, int timeout_s, syn_symm* out);
+int syn_symm_free(syn_ctx* ctx, void* local_ptr);
+/* Device-side barrier over all ranks on `stream` (replaces nvshmem_barrier_all_on_stream, e.g.
+ * tests/test_ag_gemm_gen.py:53): a one-block kernel raises this rank's slot on every peer and waits,
+ * bounded by timeout_ns (0 = 2 s), for all slots.  Errors surface through syn_ctx_status. */
+int syn_barrier(syn_ctx* ctx, void* stream, uint64_t timeout_ns);
+/* Device int32[4] status block of the context {code, wave, flag, block}; kernels given it record
+ * the first timed-out wait there.  syn_ctx_status synchronises `stream`, reads and clears it and
+ * returns 0 or the SYN_ERR_TIMEOUT_* code; out4 (host, may be NULL) receives the four words. */
+int32_t* syn_ctx_status_ptr(syn_ctx* ctx);
+int syn_ctx_status(syn_ctx* ctx, void* stream, int32_t* out4);
+
+/* ------------------------------------------------------------------ fused operators
+ * The flag value of one fused call is `gemm.signal_value` (an epoch that the caller increases by
+ * one per call; flags are never reset, waits are `>=`).  `counters` is device uint32
+ * [SYN_MAX_WAVES + SYN_MAX_COMM_OPS], zero before the first call and left zero by every call.
+ */
+
+/* All-gather + GEMM (replaces kernel_gemm_consumer + the copy-engine / SM-copy program,
+ * syncopate/computation/gemm/template.py:21-159, tests/test_ag_gemm_gen.py:44-77, and the direct
+ * remote read of template_ag.py:43-187).  gemm.a is this rank's copy of the gathered buffer
+ * [M, K] with its own shard in place; `a_sched` is the RawSchedule of that buffer (ndim 2, blocks
+ * [rows, K]).  For every wave whose target rank is another rank, the comm warps of all CTAs pull
+ * the block from its owner's copy (a.ptrs[owner], owner = row offset / rows per rank) into
+ * gemm.a and raise recv_flags[signals[w]]; GEMM tiles of the wave's rows (all N columns) start
+ * once that flag is up.  recv_flags = gemm.consumer_signal_ptr (local). */
+typedef struct syn_ag_gemm_args {
+  syn_gemm_args gemm;
+  syn_symm a;
+  uint32_t* counters;
+} syn_ag_gemm_args;
+int syn_ag_gemm(const syn_ag_gemm_args* args, const syn_schedule* a_sched, void* stream);
+
+/* GEMM + reduce-scatter (replaces kernel_gemm_producer + ring_reduce_tma and the direct remote
+ * reduce, syncopate/computation/gemm/template.py:224-351, tests/test_gemm_rs.py:22-72,
+ * template_rs.py:37-209).  The partial product C = A * B^T [M, N] is never stored whole: the tiles
+ * of wave w (rows of `src_sched`, the RawSchedule of the partial-C buffer) go, as 16-bit values,
+ * straight from the epilogue into the target rank's staging slab stage.ptrs[target] +
+ * ((epoch & 1) * world + rank) * slab, and once the wave's last tile has landed
+ * recv_flags.ptrs[target][remote_signals[w]] is raised.  The wave whose target is this rank (last
+ * in the plan) waits for the flags listed in `dst_sched` (RawSchedule of the receive buffer:
+ * target = sending rank, signal = local flag), adds the staged partial sums to its own
+ * accumulators in fp32 and writes `out` [M / world, N].  gemm.c is unused and may be NULL. */
+typedef struct syn_gemm_rs_args {
+  syn_gemm_args gemm;
+  syn_symm stage;               /* 16-bit [2, world, M / world, N] on every rank */
+  syn_symm recv_flags;          /* uint64 flags on every rank */
+  const int32_t* remote_signals; /* host int32[num_waves of src_sched], -1 = none */
+  void* out;                    /* [M / world, N] */
+  int32_t ldo;                  /* 0 = N */
+  uint32_t* counters;
+} syn_gemm_rs_args;
+int syn_gemm_rs(const syn_gemm_rs_args* args, const syn_schedule* src_sched, const syn_schedule* dst_sched,
+                void* stream);
 
 #ifdef __cplusplus
 }

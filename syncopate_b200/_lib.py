@@ -84,6 +84,41 @@ class GemmArgs(C.Structure):
     ]
 
 
+class Symm(C.Structure):
+    """``syn_symm``: all ranks' pointers of one symmetric buffer."""
+
+    _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("ptrs", C.c_void_p * SYN_MAX_WORLD)]
+
+    @classmethod
+    def of(cls, rank: int, ptrs: Sequence[int]) -> "Symm":
+        s = cls()
+        s.world = len(ptrs)
+        s.rank = rank
+        for i, p in enumerate(ptrs):
+            s.ptrs[i] = p
+        return s
+
+
+class AgGemmArgs(C.Structure):
+    """``syn_ag_gemm_args``."""
+
+    _fields_ = [("gemm", GemmArgs), ("a", Symm), ("counters", C.c_void_p)]
+
+
+class GemmRsArgs(C.Structure):
+    """``syn_gemm_rs_args``."""
+
+    _fields_ = [
+        ("gemm", GemmArgs),
+        ("stage", Symm),
+        ("recv_flags", Symm),
+        ("remote_signals", C.POINTER(C.c_int32)),
+        ("out", C.c_void_p),
+        ("ldo", C.c_int32),
+        ("counters", C.c_void_p),
+    ]
+
+
 _lib: Optional[C.CDLL] = None
 
 
@@ -110,6 +145,24 @@ def _declare(l: C.CDLL) -> None:
     l.syn_gemm.argtypes = [C.POINTER(GemmArgs), C.POINTER(Schedule), C.POINTER(Schedule), C.c_void_p]
     l.syn_gemm_pick_block_n.restype = C.c_int
     l.syn_gemm_pick_block_n.argtypes = [C.c_int, C.c_int, C.c_int]
+    l.syn_ctx_create.restype = C.c_int
+    l.syn_ctx_create.argtypes = [C.c_int, C.c_int, C.c_int, C.c_char_p, C.POINTER(C.c_void_p)]
+    l.syn_ctx_destroy.restype = C.c_int
+    l.syn_ctx_destroy.argtypes = [C.c_void_p]
+    l.syn_symm_alloc.restype = C.c_int
+    l.syn_symm_alloc.argtypes = [C.c_void_p, C.c_size_t, C.c_int, C.POINTER(Symm)]
+    l.syn_symm_free.restype = C.c_int
+    l.syn_symm_free.argtypes = [C.c_void_p, C.c_void_p]
+    l.syn_barrier.restype = C.c_int
+    l.syn_barrier.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64]
+    l.syn_ctx_status_ptr.restype = C.c_void_p
+    l.syn_ctx_status_ptr.argtypes = [C.c_void_p]
+    l.syn_ctx_status.restype = C.c_int
+    l.syn_ctx_status.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]
+    l.syn_ag_gemm.restype = C.c_int
+    l.syn_ag_gemm.argtypes = [C.POINTER(AgGemmArgs), C.POINTER(Schedule), C.c_void_p]
+    l.syn_gemm_rs.restype = C.c_int
+    l.syn_gemm_rs.argtypes = [C.POINTER(GemmRsArgs), C.POINTER(Schedule), C.POINTER(Schedule), C.c_void_p]
 
 
 def check(code: int, where: str) -> None:

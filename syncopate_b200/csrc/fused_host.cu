@@ -1,0 +1,190 @@
+// Host side of the fused operators: turns lowered schedules plus symmetric-buffer tables into the
+// comm-op list and the routed-epilogue table of the persistent GEMM kernel.
+#include <algorithm>
+#include <vector>
+
+#include "gemm_host.h"
+
+namespace syn {
+
+static int check_symm(const syn_symm& s) {
+  if (s.world <= 0 || s.world > SYN_MAX_WORLD || s.rank < 0 || s.rank >= s.world) return SYN_ERR_INVALID;
+  for (int r = 0; r < s.world; ++r)
+    if (s.ptrs[r] == nullptr) return SYN_ERR_INVALID;
+  return SYN_OK;
+}
+
+}  // namespace syn
+
+extern "C" {
+
+int syn_ag_gemm(const syn_ag_gemm_args* args, const syn_schedule* a_sched, void* stream) {
+  using namespace syn;
+  if (args == nullptr || a_sched == nullptr) return SYN_ERR_INVALID;
+  const syn_gemm_args& g = args->gemm;
+  int rc = check_symm(args->a);
+  if (rc != SYN_OK) return rc;
+  if (a_sched->ndim != 2 || a_sched->num_waves <= 0 || a_sched->num_waves > GEMM_MAX_WAVES) return SYN_ERR_INVALID;
+  if (a_sched->offsets == nullptr || a_sched->shapes == nullptr) return SYN_ERR_INVALID;
+  if (args->a.ptrs[args->a.rank] != g.a) return SYN_ERR_INVALID;  // gemm.a must be the local copy
+  const int world = args->a.world, rank = args->a.rank;
+  const int lda = g.lda ? g.lda : g.K;
+  if (g.M % world != 0) return SYN_ERR_SHAPE;
+  const int rows_per_rank = g.M / world;
+
+  // GEMM waves over C: the rows of each A block, all N columns
+  const int nw = a_sched->num_waves;
+  std::vector<int32_t> c_off(nw * 2), c_shape(nw * 2);
+  for (int w = 0; w < nw; ++w) {
+    const int r0 = a_sched->offsets[w * 2], k0 = a_sched->offsets[w * 2 + 1];
+    const int rows = a_sched->shapes[w * 2], cols = a_sched->shapes[w * 2 + 1];
+    if (r0 < 0 || rows <= 0 || r0 + rows > g.M || k0 < 0 || cols <= 0 || k0 + cols > g.K) return SYN_ERR_SHAPE;
+    c_off[w * 2] = r0;
+    c_off[w * 2 + 1] = 0;
+    c_shape[w * 2] = rows;
+    c_shape[w * 2 + 1] = g.N;
+  }
+  syn_schedule c_sched = *a_sched;
+  c_sched.offsets = c_off.data();
+  c_sched.shapes = c_shape.data();
+
+  int grid = 0, bn = 0;
+  rc = gemm_resolve_grid_and_bn(&g, &c_sched, &grid, &bn);
+  if (rc != SYN_OK) return rc;
+  GemmParams p;
+  rc = gemm_fill_common(&p, &g, &c_sched, bn);
+  if (rc != SYN_OK) return rc;
+
+  // comm ops: one pull per remote block, in wave order
+  int n_ops = 0;
+  bool any_signal = false;
+  for (int w = 0; w < nw; ++w) {
+    const int sig = a_sched->signals ? a_sched->signals[w] : -1;
+    const int tgt = a_sched->target_ranks ? a_sched->target_ranks[w] : -1;
+    if (sig >= 0) any_signal = true;
+    if (sig < 0 || tgt < 0 || tgt == rank) continue;  // resident block
+    if (g.consumer_signal_ptr == nullptr || args->counters == nullptr) return SYN_ERR_INVALID;
+    if (n_ops >= GEMM_MAX_COMM_OPS) return SYN_ERR_TOO_LARGE;
+    const int r0 = a_sched->offsets[w * 2], k0 = a_sched->offsets[w * 2 + 1];
+    const int rows = a_sched->shapes[w * 2], cols = a_sched->shapes[w * 2 + 1];
+    // the block's owner holds it at the same place of its own copy of the gathered buffer; on an
+    // all-to-all fabric a ring plan's block is fetched from its owner too, in the plan's order
+    const int owner = r0 / rows_per_rank;
+    if (owner < 0 || owner >= world || (r0 + rows - 1) / rows_per_rank != owner) return SYN_ERR_SHAPE;
+    if (owner == rank) continue;
+    const int pr0 = a_sched->dst_offsets ? a_sched->dst_offsets[w * 2] : r0;
+    const int pk0 = a_sched->dst_offsets ? a_sched->dst_offsets[w * 2 + 1] : k0;
+    const int src_r0 = (tgt == owner) ? pr0 : r0;
+    const int src_k0 = (tgt == owner) ? pk0 : k0;
+    CommOp& op = p.comm[n_ops++];
+    op.src = static_cast<const char*>(args->a.ptrs[owner]) + (static_cast<size_t>(src_r0) * lda + src_k0) * 2;
+    op.dst = static_cast<char*>(const_cast<void*>(g.a)) + (static_cast<size_t>(r0) * lda + k0) * 2;
+    if ((reinterpret_cast<uintptr_t>(op.src) & 15) || (reinterpret_cast<uintptr_t>(op.dst) & 15) || (cols % 8))
+      return SYN_ERR_INVALID;
+    if (cols == lda) {  // contiguous block: one long row
+      op.rows = 1;
+      op.row_bytes = static_cast<uint32_t>(static_cast<size_t>(rows) * cols * 2);
+      if (static_cast<size_t>(rows) * cols * 2 > 0xFFFFFFFFull) return SYN_ERR_TOO_LARGE;
+      op.src_pitch = op.dst_pitch = 0;
+    } else {
+      op.rows = static_cast<uint32_t>(rows);
+      op.row_bytes = static_cast<uint32_t>(cols * 2);
+      op.src_pitch = op.dst_pitch = static_cast<uint64_t>(lda) * 2;
+    }
+    op.wait_flag = nullptr;
+    op.set_flag = const_cast<uint64_t*>(g.consumer_signal_ptr) + sig;
+  }
+  p.num_comm_ops = n_ops;
+  p.counters = args->counters;
+  (void)any_signal;
+  grid = std::min(grid, p.total_tiles);
+  if (grid <= 0) return SYN_ERR_INVALID;
+  return gemm_launch(p, bn, /*fused=*/n_ops > 0, grid, static_cast<cudaStream_t>(stream));
+}
+
+int syn_gemm_rs(const syn_gemm_rs_args* args, const syn_schedule* src_sched, const syn_schedule* dst_sched,
+                void* stream) {
+  using namespace syn;
+  if (args == nullptr || src_sched == nullptr || dst_sched == nullptr) return SYN_ERR_INVALID;
+  syn_gemm_args g = args->gemm;
+  int rc = check_symm(args->stage);
+  if (rc != SYN_OK) return rc;
+  rc = check_symm(args->recv_flags);
+  if (rc != SYN_OK) return rc;
+  const int world = args->stage.world, rank = args->stage.rank;
+  if (args->recv_flags.world != world || args->recv_flags.rank != rank) return SYN_ERR_INVALID;
+  if (args->out == nullptr || args->counters == nullptr) return SYN_ERR_INVALID;
+  if (src_sched->ndim != 2 || src_sched->target_ranks == nullptr) return SYN_ERR_INVALID;
+  if (g.M % world != 0) return SYN_ERR_SHAPE;
+  const int slab_rows = g.M / world;
+  const int ldo = args->ldo ? args->ldo : g.N;
+  if (ldo < g.N || (ldo % 8) || (reinterpret_cast<uintptr_t>(args->out) & 15)) return SYN_ERR_INVALID;
+  // the whole partial product is never stored; give the argument check a non-null placeholder
+  if (g.c == nullptr) g.c = args->out;
+  g.consumer_signal_ptr = nullptr;
+
+  int grid = 0, bn = 0;
+  rc = gemm_resolve_grid_and_bn(&g, src_sched, &grid, &bn);
+  if (rc != SYN_OK) return rc;
+  GemmParams p;
+  rc = gemm_fill_common(&p, &g, src_sched, bn);
+  if (rc != SYN_OK) return rc;
+  const uint64_t epoch = p.signal_value;
+  const size_t slab_elems = static_cast<size_t>(slab_rows) * g.N;
+  const size_t half = static_cast<size_t>(epoch & 1) * world;
+
+  for (int w = 0; w < src_sched->num_waves; ++w) {
+    const int r0 = src_sched->offsets[w * 2], rows = src_sched->shapes[w * 2];
+    if (src_sched->offsets[w * 2 + 1] != 0 || src_sched->shapes[w * 2 + 1] != g.N) return SYN_ERR_SHAPE;
+    const int owner = r0 / slab_rows;  // rank whose output the rows belong to
+    if ((r0 + rows - 1) / slab_rows != owner) return SYN_ERR_SHAPE;
+    int tgt = src_sched->target_ranks[w];
+    if (tgt < 0) tgt = rank;
+    if (tgt != owner) return SYN_ERR_SHAPE;
+    GemmRoute& rt = p.routes[w];
+    p.waves[w].route = static_cast<int16_t>(w);
+    rt.gate = nullptr;
+    rt.gate_value = 0;
+    const int row_in_slab = r0 - owner * slab_rows;
+    if (tgt == rank) {
+      rt.base = static_cast<char*>(args->out) + static_cast<size_t>(row_in_slab) * ldo * 2;
+      rt.ld = ldo;
+      rt.flag = nullptr;
+      rt.reduce = 1;
+    } else {
+      char* slab = static_cast<char*>(args->stage.ptrs[tgt]) + (half + rank) * slab_elems * 2;
+      rt.base = slab + static_cast<size_t>(row_in_slab) * g.N * 2;
+      rt.ld = g.N;
+      const int rsig = args->remote_signals ? args->remote_signals[w] : -1;
+      rt.flag = rsig >= 0 ? static_cast<uint64_t*>(args->recv_flags.ptrs[tgt]) + rsig : nullptr;
+      rt.reduce = 0;
+    }
+  }
+  // staged partial sums to add in the owner wave, with the local flags that publish them
+  int n_red = 0;
+  for (int w = 0; w < dst_sched->num_waves; ++w) {
+    const int src_rank = dst_sched->target_ranks ? dst_sched->target_ranks[w] : -1;
+    const int sig = dst_sched->signals ? dst_sched->signals[w] : -1;
+    if (src_rank < 0 || src_rank == rank) continue;
+    if (src_rank >= world || sig < 0 || n_red >= 7) return SYN_ERR_SHAPE;
+    bool seen = false;
+    for (int i = 0; i < n_red; ++i)
+      if (p.red_flag[i] == static_cast<const uint64_t*>(args->recv_flags.ptrs[rank]) + sig) seen = true;
+    if (seen) continue;
+    p.red_src[n_red] = static_cast<const char*>(args->stage.ptrs[rank]) + (half + src_rank) * slab_elems * 2;
+    p.red_flag[n_red] = static_cast<const uint64_t*>(args->recv_flags.ptrs[rank]) + sig;
+    ++n_red;
+  }
+  if (n_red != world - 1) return SYN_ERR_SHAPE;
+  p.num_red = n_red;
+  p.red_ld = g.N;
+  p.red_row0 = rank * slab_rows;
+  p.counters = args->counters;
+  p.c = args->out;
+  p.ldc = ldo;
+  grid = std::min(grid, p.total_tiles);
+  if (grid <= 0) return SYN_ERR_INVALID;
+  return gemm_launch(p, bn, /*fused=*/true, grid, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

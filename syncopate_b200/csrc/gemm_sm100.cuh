@@ -67,6 +67,7 @@ struct GemmParams {
   int32_t num_comm_ops;
   int32_t num_red;        // staged partial slabs to add in `reduce` routes
   int32_t red_ld;
+  int32_t red_row0;       // global C row of the staged slabs' row 0
   const uint64_t* csig;   // consumer flags
   uint32_t* counters;     // [num_waves] producer counters then [num_comm_ops] comm counters, self-resetting
   uint64_t signal_value;
@@ -371,7 +372,7 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
             for (int s = 0; s < p.num_red; ++s) {
               const uint4* src = reinterpret_cast<const uint4*>(
                   reinterpret_cast<const char*>(p.red_src[s]) +
-                  (static_cast<size_t>(out_row) * p.red_ld + col) * 2);
+                  (static_cast<size_t>(grow - p.red_row0) * p.red_ld + col) * 2);
 #pragma unroll
               for (int v = 0; v < 4; ++v) {
                 if (col + v * 8 < p.N) {

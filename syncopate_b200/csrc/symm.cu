@@ -1,0 +1,241 @@
+// Symmetric memory over CUDA IPC, flag barrier and status block: the replacement of the NVSHMEM
+// runtime used by the reference's CommContext
+// (syncopate/communication/comm_runtime/communication_context.py:31-106).
+#include <errno.h>
+#include <fcntl.h>
+#include <sys/stat.h>
+#include <time.h>
+#include <unistd.h>
+
+#include <string>
+#include <vector>
+
+#include "host_util.h"
+#include "ptx.cuh"
+
+struct syn_symm_record {
+  void* local;
+  void* peers[SYN_MAX_WORLD];
+  size_t bytes;
+};
+
+struct syn_ctx {
+  int rank, world, device;
+  std::string dir;
+  uint64_t seq;        // number of symmetric allocations so far (same on every rank)
+  uint64_t barrier_epoch;
+  std::vector<syn_symm_record> bufs;
+  std::vector<std::string> my_files;
+  int32_t* status;      // device int32[4]
+  syn_symm barrier_flags;  // uint64[world] on every rank
+};
+
+namespace syn {
+
+static void sleep_ms(int ms) {
+  struct timespec ts = {ms / 1000, (ms % 1000) * 1000000L};
+  nanosleep(&ts, nullptr);
+}
+
+static bool write_file_atomic(const std::string& path, const void* data, size_t n) {
+  const std::string tmp = path + ".tmp";
+  int fd = open(tmp.c_str(), O_CREAT | O_TRUNC | O_WRONLY, 0600);
+  if (fd < 0) return false;
+  const ssize_t w = write(fd, data, n);
+  close(fd);
+  if (w != static_cast<ssize_t>(n)) return false;
+  return rename(tmp.c_str(), path.c_str()) == 0;
+}
+
+static bool read_file(const std::string& path, void* data, size_t n) {
+  int fd = open(path.c_str(), O_RDONLY);
+  if (fd < 0) return false;
+  const ssize_t r = read(fd, data, n);
+  close(fd);
+  return r == static_cast<ssize_t>(n);
+}
+
+struct HandleRecord {
+  cudaIpcMemHandle_t handle;
+  uint64_t bytes;
+};
+
+__global__ void barrier_kernel(syn_symm flags, uint64_t epoch, uint64_t timeout_ns, int32_t* status) {
+  __shared__ int abort_word;
+  if (threadIdx.x == 0) abort_word = 0;
+  __syncthreads();
+  const int peer = threadIdx.x;
+  if (peer < flags.world) {
+    // everything this rank wrote before the barrier must be visible to a peer that sees the slot
+    __threadfence_system();
+    st_release_sys_u64(reinterpret_cast<uint64_t*>(flags.ptrs[peer]) + flags.rank, epoch);
+    const uint64_t* mine = reinterpret_cast<const uint64_t*>(flags.ptrs[flags.rank]) + peer;
+    if (!flag_wait_ge(mine, epoch, &abort_word, timeout_ns)) {
+      if (status != nullptr && atomicCAS(status, 0, SYN_DEV_TIMEOUT_FLAG) == 0) {
+        status[1] = -1;
+        status[2] = peer;
+        status[3] = -1;
+      }
+    }
+  }
+}
+
+}  // namespace syn
+
+extern "C" {
+
+int syn_ctx_create(int rank, int world, int device, const char* rendezvous_dir, syn_ctx** out) {
+  using namespace syn;
+  if (out == nullptr || world <= 0 || world > SYN_MAX_WORLD || rank < 0 || rank >= world) return SYN_ERR_INVALID;
+  if (world > 1 && (rendezvous_dir == nullptr || rendezvous_dir[0] == 0)) return SYN_ERR_INVALID;
+  SYN_CUDA_TRY(cudaSetDevice(device));
+  syn_ctx* c = new syn_ctx();
+  c->rank = rank;
+  c->world = world;
+  c->device = device;
+  c->dir = rendezvous_dir ? rendezvous_dir : "";
+  c->seq = 0;
+  c->barrier_epoch = 0;
+  c->status = nullptr;
+  if (world > 1) mkdir(c->dir.c_str(), 0700);  // may exist already
+  cudaError_t e = cudaMalloc(&c->status, 4 * sizeof(int32_t));
+  if (e == cudaSuccess) e = cudaMemset(c->status, 0, 4 * sizeof(int32_t));
+  if (e != cudaSuccess) {
+    set_cuda_error("cudaMalloc(status)", cudaGetErrorString(e));
+    delete c;
+    return SYN_ERR_CUDA;
+  }
+  int rc = syn_symm_alloc(c, sizeof(uint64_t) * SYN_MAX_WORLD, 0, &c->barrier_flags);
+  if (rc != SYN_OK) {
+    syn_ctx_destroy(c);
+    return rc;
+  }
+  *out = c;
+  return SYN_OK;
+}
+
+int syn_ctx_destroy(syn_ctx* c) {
+  if (c == nullptr) return SYN_ERR_INVALID;
+  cudaSetDevice(c->device);
+  cudaDeviceSynchronize();
+  for (auto& b : c->bufs) {
+    for (int r = 0; r < c->world; ++r)
+      if (r != c->rank && b.peers[r] != nullptr) cudaIpcCloseMemHandle(b.peers[r]);
+    if (b.local != nullptr) cudaFree(b.local);
+  }
+  if (c->status != nullptr) cudaFree(c->status);
+  for (auto& f : c->my_files) unlink(f.c_str());
+  delete c;
+  return SYN_OK;
+}
+
+int syn_symm_alloc(syn_ctx* c, size_t bytes, int timeout_s, syn_symm* out) {
+  using namespace syn;
+  if (c == nullptr || out == nullptr || bytes == 0) return SYN_ERR_INVALID;
+  SYN_CUDA_TRY(cudaSetDevice(c->device));
+  syn_symm_record rec;
+  memset(&rec, 0, sizeof(rec));
+  rec.bytes = bytes;
+  SYN_CUDA_TRY(cudaMalloc(&rec.local, bytes));
+  cudaError_t e = cudaMemset(rec.local, 0, bytes);
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) {
+    set_cuda_error("cudaMemset(symmetric buffer)", cudaGetErrorString(e));
+    cudaFree(rec.local);
+    return SYN_ERR_CUDA;
+  }
+  rec.peers[c->rank] = rec.local;
+  const uint64_t seq = c->seq++;
+  if (c->world > 1) {
+    HandleRecord mine;
+    memset(&mine, 0, sizeof(mine));
+    e = cudaIpcGetMemHandle(&mine.handle, rec.local);
+    if (e != cudaSuccess) {
+      set_cuda_error("cudaIpcGetMemHandle", cudaGetErrorString(e));
+      cudaFree(rec.local);
+      return SYN_ERR_CUDA;
+    }
+    mine.bytes = bytes;
+    char name[128];
+    snprintf(name, sizeof(name), "/syn_%llu_%d.ipc", static_cast<unsigned long long>(seq), c->rank);
+    const std::string my_path = c->dir + name;
+    if (!write_file_atomic(my_path, &mine, sizeof(mine))) {
+      cudaFree(rec.local);
+      return SYN_ERR_RENDEZVOUS;
+    }
+    c->my_files.push_back(my_path);
+    const int limit_ms = (timeout_s > 0 ? timeout_s : 120) * 1000;
+    for (int r = 0; r < c->world; ++r) {
+      if (r == c->rank) continue;
+      snprintf(name, sizeof(name), "/syn_%llu_%d.ipc", static_cast<unsigned long long>(seq), r);
+      const std::string path = c->dir + name;
+      HandleRecord theirs;
+      int waited = 0;
+      while (!read_file(path, &theirs, sizeof(theirs))) {
+        if (waited >= limit_ms) {
+          c->bufs.push_back(rec);  // freed by syn_ctx_destroy
+          return SYN_ERR_RENDEZVOUS;
+        }
+        sleep_ms(5);
+        waited += 5;
+      }
+      if (theirs.bytes != bytes) {
+        c->bufs.push_back(rec);
+        return SYN_ERR_INVALID;  // ranks disagree on the allocation sequence
+      }
+      e = cudaIpcOpenMemHandle(&rec.peers[r], theirs.handle, cudaIpcMemLazyEnablePeerAccess);
+      if (e != cudaSuccess) {
+        set_cuda_error("cudaIpcOpenMemHandle", cudaGetErrorString(e));
+        rec.peers[r] = nullptr;
+        c->bufs.push_back(rec);
+        return SYN_ERR_CUDA;
+      }
+    }
+  }
+  c->bufs.push_back(rec);
+  out->world = c->world;
+  out->rank = c->rank;
+  for (int r = 0; r < SYN_MAX_WORLD; ++r) out->ptrs[r] = r < c->world ? rec.peers[r] : nullptr;
+  return SYN_OK;
+}
+
+int syn_symm_free(syn_ctx* c, void* local_ptr) {
+  if (c == nullptr || local_ptr == nullptr) return SYN_ERR_INVALID;
+  for (size_t i = 0; i < c->bufs.size(); ++i) {
+    if (c->bufs[i].local != local_ptr) continue;
+    cudaSetDevice(c->device);
+    cudaDeviceSynchronize();
+    for (int r = 0; r < c->world; ++r)
+      if (r != c->rank && c->bufs[i].peers[r] != nullptr) cudaIpcCloseMemHandle(c->bufs[i].peers[r]);
+    cudaFree(c->bufs[i].local);
+    c->bufs.erase(c->bufs.begin() + i);
+    return SYN_OK;
+  }
+  return SYN_ERR_INVALID;
+}
+
+int syn_barrier(syn_ctx* c, void* stream, uint64_t timeout_ns) {
+  using namespace syn;
+  if (c == nullptr) return SYN_ERR_INVALID;
+  if (c->world == 1) return SYN_OK;
+  const uint64_t epoch = ++c->barrier_epoch;
+  barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      c->barrier_flags, epoch, timeout_ns ? timeout_ns : 2000000000ull, c->status);
+  SYN_CUDA_TRY(cudaGetLastError());
+  return SYN_OK;
+}
+
+int32_t* syn_ctx_status_ptr(syn_ctx* c) { return c ? c->status : nullptr; }
+
+int syn_ctx_status(syn_ctx* c, void* stream, int32_t* out4) {
+  using namespace syn;
+  if (c == nullptr) return SYN_ERR_INVALID;
+  SYN_CUDA_TRY(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  int32_t host[4] = {0, 0, 0, 0};
+  SYN_CUDA_TRY(cudaMemcpy(host, c->status, sizeof(host), cudaMemcpyDeviceToHost));
+  if (out4 != nullptr) memcpy(out4, host, sizeof(host));
+  if (host[0] != 0) SYN_CUDA_TRY(cudaMemset(c->status, 0, sizeof(host)));
+  return status_to_err(host[0]);
+}
+
+}  // extern "C"
