@@ -87,8 +87,8 @@ typedef struct syn_gemm_args {
   int32_t num_sms;      /* persistent grid size, 0 = all SMs of the device */
   /* Signal flags (uint64 words, device memory).  A wave with signals[w] >= 0 starts only once
    * signal_ptr[signals[w]] >= signal_value (consumer), or sets it to signal_value after its last
-   * tile is stored (producer; needs counter_ptr: uint32[num_waves], zero at the first call, kept
-   * by the library as a running count thereafter). */
+   * tile is stored (producer; needs counter_ptr: uint32[num_waves], zero before the first call;
+   * every call leaves it zero again). */
   const uint64_t* consumer_signal_ptr;
   uint64_t* producer_signal_ptr;
   uint32_t* producer_counter_ptr;
@@ -143,6 +143,14 @@ int syn_barrier(syn_ctx* ctx, void* stream, uint64_t timeout_ns);
  * returns 0 or the SYN_ERR_TIMEOUT_* code; out4 (host, may be NULL) receives the four words. */
 int32_t* syn_ctx_status_ptr(syn_ctx* ctx);
 int syn_ctx_status(syn_ctx* ctx, void* stream, int32_t* out4);
+
+/* Stream-ordered flag operations (replace _set_signal_cuda / _wait_eq_cuda of the reference's
+ * op interpreter, communication_context.py:145-160): one-thread kernels that store `value` with
+ * system-scope release, or wait (bounded) until *flag >= value; a wait that runs out records
+ * {SYN_DEV_TIMEOUT_FLAG, -1, tag, -1} in `status` (device int32[4], may be NULL). */
+int syn_flag_set(uint64_t* flag, uint64_t value, void* stream);
+int syn_flag_wait(const uint64_t* flag, uint64_t value, uint64_t timeout_ns, int32_t* status, int tag,
+                  void* stream);
 
 /* ------------------------------------------------------------------ fused operators
  * The flag value of one fused call is `gemm.signal_value` (an epoch that the caller increases by

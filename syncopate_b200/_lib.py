@@ -159,6 +159,10 @@ def _declare(l: C.CDLL) -> None:
     l.syn_ctx_status_ptr.argtypes = [C.c_void_p]
     l.syn_ctx_status.restype = C.c_int
     l.syn_ctx_status.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]
+    l.syn_flag_set.restype = C.c_int
+    l.syn_flag_set.argtypes = [C.c_void_p, C.c_uint64, C.c_void_p]
+    l.syn_flag_wait.restype = C.c_int
+    l.syn_flag_wait.argtypes = [C.c_void_p, C.c_uint64, C.c_uint64, C.c_void_p, C.c_int, C.c_void_p]
     l.syn_ag_gemm.restype = C.c_int
     l.syn_ag_gemm.argtypes = [C.POINTER(AgGemmArgs), C.POINTER(Schedule), C.c_void_p]
     l.syn_gemm_rs.restype = C.c_int

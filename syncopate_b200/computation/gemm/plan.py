@@ -45,3 +45,23 @@ def rs_remote_signals(comm_info, rank: int, src_schedule) -> List[int]:
 
 
 __all__ = ["push_completion_signals", "rs_remote_signals"]
+
+
+def tile_order(wave_offsets, wave_sizes, block_m: int = 128, block_n: int = 256, group_size_m: int = 8):
+    """Host model of the kernel's tile scheduler: the ``(pid_m, pid_n)`` sequence for global tile
+    ids 0, 1, 2, ...  Waves are walked in array order; inside a wave the grouped raster of
+    syncopate/computation/gemm/template.py:10-18 applies to the wave's own tile grid, then the
+    wave's offset is added (:130-136).  Offsets and sizes are in elements."""
+    order = []
+    for (off_m, off_n), (size_m, size_n) in zip(wave_offsets, wave_sizes):
+        tm, tn = -(-size_m // block_m), -(-size_n // block_n)
+        for local in range(tm * tn):
+            in_group = group_size_m * tn
+            group_id, r = divmod(local, in_group)
+            first_m = group_id * group_size_m
+            gsz = min(tm - first_m, group_size_m)
+            order.append((first_m + r % gsz + off_m // block_m, r // gsz + off_n // block_n))
+    return order
+
+
+__all__ += ["tile_order"]

@@ -80,9 +80,45 @@ __global__ void barrier_kernel(syn_symm flags, uint64_t epoch, uint64_t timeout_
   }
 }
 
+__global__ void flag_set_kernel(uint64_t* flag, uint64_t value) {
+  __threadfence_system();
+  st_release_sys_u64(flag, value);
+}
+
+__global__ void flag_wait_kernel(const uint64_t* flag, uint64_t value, uint64_t timeout_ns, int32_t* status,
+                                 int tag) {
+  __shared__ int abort_word;
+  abort_word = 0;
+  if (!flag_wait_ge(flag, value, &abort_word, timeout_ns)) {
+    if (status != nullptr && atomicCAS(status, 0, SYN_DEV_TIMEOUT_FLAG) == 0) {
+      status[1] = -1;
+      status[2] = tag;
+      status[3] = -1;
+    }
+  }
+}
+
 }  // namespace syn
 
 extern "C" {
+
+int syn_flag_set(uint64_t* flag, uint64_t value, void* stream) {
+  using namespace syn;
+  if (flag == nullptr) return SYN_ERR_INVALID;
+  flag_set_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(flag, value);
+  SYN_CUDA_TRY(cudaGetLastError());
+  return SYN_OK;
+}
+
+int syn_flag_wait(const uint64_t* flag, uint64_t value, uint64_t timeout_ns, int32_t* status, int tag,
+                  void* stream) {
+  using namespace syn;
+  if (flag == nullptr) return SYN_ERR_INVALID;
+  flag_wait_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(
+      flag, value, timeout_ns ? timeout_ns : 2000000000ull, status, tag);
+  SYN_CUDA_TRY(cudaGetLastError());
+  return SYN_OK;
+}
 
 int syn_ctx_create(int rank, int world, int device, const char* rendezvous_dir, syn_ctx** out) {
   using namespace syn;

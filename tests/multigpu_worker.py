@@ -1,0 +1,83 @@
+"""Multi-process worker for the multi-GPU tests: run under torchrun with one rank per GPU.
+Checks the fused operators over real peer-mapped memory against a gather-then-operate reference
+computed with torch.distributed (test plumbing only)."""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+
+from syncopate_b200.operators import AllGatherGemm, GemmReduceScatter  # noqa: E402
+from syncopate_b200.runtime import init_from_env  # noqa: E402
+
+TOL = 1e-2
+
+
+def seeded(seed, shape, scale, dtype, device):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g, dtype=torch.float32) * scale).to(dtype).to(device)
+
+
+def rel(x, ref):
+    return ((x.float() - ref.float()).norm() / ref.float().norm()).item()
+
+
+def main():
+    rank, world, ctx = init_from_env()
+    dev = ctx.device
+    dt = torch.bfloat16
+    failures = []
+
+    for kind, rows, K, N in (("swizzle", 256, 512, 512), ("ring", 128, 256, 512), ("swizzle", 1024, 8192, 28672 // world)):
+        op = AllGatherGemm(ctx, rows, K, N, dt, plan=kind, timeout_ns=2_000_000_000)
+        shards = [seeded(1000 + r, (rows, K), 1.0, dt, dev) for r in range(world)]
+        b = seeded(5000 + rank, (N, K), 0.02, dt, dev)
+        full = torch.cat(shards, 0)
+        ref = full.float() @ b.float().t()
+        for it in range(3):
+            op.a.local.fill_(float("nan"))
+            op.shard.copy_(shards[rank])
+            torch.cuda.synchronize()
+            ctx.barrier()
+            c = op(b)
+            ctx.check()
+            e = rel(c, ref)
+            same = torch.equal(op.a.local, full)
+            if not (e < TOL and same):
+                failures.append(f"ag_gemm {kind} rows={rows} it={it} rank={rank}: relerr={e:.3e} gathered_ok={same}")
+            ctx.barrier()  # nobody may overwrite its shard while a peer still pulls it
+            torch.cuda.synchronize()
+
+    for kind, M, N, Kl in (("direct", 1024, 512, 256), ("a2a", 512, 1024, 512), ("direct", 8192, 8192, 28672 // world)):
+        op = GemmReduceScatter(ctx, M, N, dt, plan=kind, timeout_ns=2_000_000_000)
+        a = seeded(2000 + rank, (M, Kl), 1.0, dt, dev)
+        b = seeded(3000 + rank, (N, Kl), 0.02, dt, dev)
+        part = a.float() @ b.float().t()
+        dist.all_reduce(part)
+        ref = part[rank * op.slab : (rank + 1) * op.slab]
+        for it in range(3):
+            out = op(a, b)
+            ctx.check()
+            e = rel(out, ref)
+            if not e < TOL:
+                failures.append(f"gemm_rs {kind} M={M} it={it} rank={rank}: relerr={e:.3e}")
+
+    torch.cuda.synchronize()
+    flag = torch.tensor([len(failures)], device=dev)
+    dist.all_reduce(flag)
+    for f in failures:
+        print("FAIL", f, flush=True)
+    if rank == 0:
+        print("MULTIGPU_OK" if flag.item() == 0 else f"MULTIGPU_FAILED {flag.item()}", flush=True)
+    ctx.close()
+    dist.barrier()
+    dist.destroy_process_group()
+    sys.exit(0 if flag.item() == 0 else 1)
+
+
+if __name__ == "__main__":
+    main()
