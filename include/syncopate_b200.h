@@ -104,6 +104,19 @@ typedef struct syn_gemm_args {
 int syn_gemm(const syn_gemm_args* args, const syn_schedule* sched, const syn_schedule* producer_sched,
              void* stream);
 
+/* Same operation as syn_gemm in its producer role, for callers that cannot allocate device memory
+ * (a process whose GPU memory is wholly owned by its own pool, a latency-critical step that must
+ * not hit cudaMalloc's device-wide synchronisation, a plugin in a host that forbids allocation
+ * after start-up).  It has no counterpart in the reference.  args->producer_counter_ptr is
+ * ignored: the per-wave tile counters live in a 256-byte device array inside the library (every
+ * GPU that loads the library holds one until exit), so at most SYN_MAX_WAVES (64) waves are
+ * accepted (SYN_ERR_TOO_LARGE beyond).  No cudaMalloc / cudaFree / allocating routine is called.
+ * The first call on each device looks up the array's device address; make that first call outside
+ * any stream capture.  Each call zeroes the array on `stream` before launching.  All calls on a
+ * device share the array: two calls that may overlap on the GPU (different streams) race. */
+int syn_gemm_noalloc(const syn_gemm_args* args, const syn_schedule* sched, const syn_schedule* producer_sched,
+                     void* stream);
+
 /* Smallest persistent-grid tail for an M x N output on `num_sms` SMs: returns the block_n the
  * library would choose for block_n = 0. */
 int syn_gemm_pick_block_n(int M, int N, int num_sms);
