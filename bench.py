@@ -218,7 +218,7 @@ def run_own_arm(args):
     b = seeded(5000 + rank, (n_local, K_DIM), 0.02, dt).to(dev)
     c = torch.empty(M, n_local, dtype=dt, device=dev)
     if world > 1:
-        op = AllGatherGemm(ctx, ROWS, K_DIM, n_local, dt, plan="swizzle")
+        op = AllGatherGemm(ctx, ROWS, K_DIM, n_local, dt, plan="swizzle", comm=args.comm)
         op.shard.copy_(seeded(1000 + rank, (ROWS, K_DIM), 1.0, dt).to(dev))
         step = lambda: op(b, c)
         a_host_shape = (ROWS, K_DIM)
@@ -362,6 +362,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--comm", default="sm", choices=["sm", "ce"],
+                    help="who moves the all-gather chunks: the kernel's comm warps (sm) or copy engines (ce)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

@@ -162,6 +162,9 @@ int syn_ctx_status(syn_ctx* ctx, void* stream, int32_t* out4);
  * system-scope release, or wait (bounded) until *flag >= value; a wait that runs out records
  * {SYN_DEV_TIMEOUT_FLAG, -1, tag, -1} in `status` (device int32[4], may be NULL). */
 int syn_flag_set(uint64_t* flag, uint64_t value, void* stream);
+/* Copy-engine transfer between (peer-mapped) device pointers, the CopyEngineOp of the reference's
+ * interpreter (communication_context.py:129-143). */
+int syn_memcpy_async(void* dst, const void* src, size_t bytes, void* stream);
 int syn_flag_wait(const uint64_t* flag, uint64_t value, uint64_t timeout_ns, int32_t* status, int tag,
                   void* stream);
 

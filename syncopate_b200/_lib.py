@@ -10,7 +10,8 @@ import os
 from typing import Optional, Sequence
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libsyncopate_b200.so")
+# SYNCOPATE_B200_LIB points at another build of the same library (tuning experiments).
+LIB_PATH = os.environ.get("SYNCOPATE_B200_LIB") or os.path.join(_HERE, "libsyncopate_b200.so")
 
 SYN_MAX_WORLD = 8
 SYN_DTYPE_F16 = 0
@@ -161,6 +162,8 @@ def _declare(l: C.CDLL) -> None:
     l.syn_ctx_status_ptr.argtypes = [C.c_void_p]
     l.syn_ctx_status.restype = C.c_int
     l.syn_ctx_status.argtypes = [C.c_void_p, C.c_void_p, C.POINTER(C.c_int32)]
+    l.syn_memcpy_async.restype = C.c_int
+    l.syn_memcpy_async.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]
     l.syn_flag_set.restype = C.c_int
     l.syn_flag_set.argtypes = [C.c_void_p, C.c_uint64, C.c_void_p]
     l.syn_flag_wait.restype = C.c_int

@@ -57,11 +57,9 @@ int syn_ag_gemm(const syn_ag_gemm_args* args, const syn_schedule* a_sched, void*
 
   // comm ops: one pull per remote block, in wave order
   int n_ops = 0;
-  bool any_signal = false;
   for (int w = 0; w < nw; ++w) {
     const int sig = a_sched->signals ? a_sched->signals[w] : -1;
     const int tgt = a_sched->target_ranks ? a_sched->target_ranks[w] : -1;
-    if (sig >= 0) any_signal = true;
     if (sig < 0 || tgt < 0 || tgt == rank) continue;  // resident block
     if (g.consumer_signal_ptr == nullptr || args->counters == nullptr) return SYN_ERR_INVALID;
     if (n_ops >= GEMM_MAX_COMM_OPS) return SYN_ERR_TOO_LARGE;
@@ -96,7 +94,6 @@ int syn_ag_gemm(const syn_ag_gemm_args* args, const syn_schedule* a_sched, void*
   }
   p.num_comm_ops = n_ops;
   p.counters = args->counters;
-  (void)any_signal;
   grid = std::min(grid, p.total_tiles);
   if (grid <= 0) return SYN_ERR_INVALID;
   return gemm_launch(p, bn, /*fused=*/n_ops > 0, grid, static_cast<cudaStream_t>(stream));
@@ -124,12 +121,15 @@ int syn_gemm_rs(const syn_gemm_rs_args* args, const syn_schedule* src_sched, con
   g.consumer_signal_ptr = nullptr;
 
   int grid = 0, bn = 0;
-  rc = gemm_resolve_grid_and_bn(&g, src_sched, &grid, &bn);
+  rc = gemm_resolve_grid_and_bn(&g, src_sched, &grid, &bn, /*multiple=*/64);
   if (rc != SYN_OK) return rc;
   GemmParams p;
   rc = gemm_fill_common(&p, &g, src_sched, bn);
   if (rc != SYN_OK) return rc;
   const uint64_t epoch = p.signal_value;
+  int tmap_of_rank[SYN_MAX_WORLD];
+  for (int r = 0; r < SYN_MAX_WORLD; ++r) tmap_of_rank[r] = -1;
+  int n_maps = 0;
   const size_t slab_elems = static_cast<size_t>(slab_rows) * g.N;
   const size_t half = static_cast<size_t>(epoch & 1) * world;
 
@@ -146,19 +146,30 @@ int syn_gemm_rs(const syn_gemm_rs_args* args, const syn_schedule* src_sched, con
     rt.gate = nullptr;
     rt.gate_value = 0;
     const int row_in_slab = r0 - owner * slab_rows;
+    char* slab0;  // row 0 of the destination slab
+    int slab_ld;
     if (tgt == rank) {
-      rt.base = static_cast<char*>(args->out) + static_cast<size_t>(row_in_slab) * ldo * 2;
-      rt.ld = ldo;
+      slab0 = static_cast<char*>(args->out);
+      slab_ld = ldo;
       rt.flag = nullptr;
       rt.reduce = 1;
     } else {
-      char* slab = static_cast<char*>(args->stage.ptrs[tgt]) + (half + rank) * slab_elems * 2;
-      rt.base = slab + static_cast<size_t>(row_in_slab) * g.N * 2;
-      rt.ld = g.N;
+      slab0 = static_cast<char*>(args->stage.ptrs[tgt]) + (half + rank) * slab_elems * 2;
+      slab_ld = g.N;
       const int rsig = args->remote_signals ? args->remote_signals[w] : -1;
       rt.flag = rsig >= 0 ? static_cast<uint64_t*>(args->recv_flags.ptrs[tgt]) + rsig : nullptr;
       rt.reduce = 0;
     }
+    rt.base = slab0 + static_cast<size_t>(row_in_slab) * slab_ld * 2;
+    rt.ld = slab_ld;
+    // tiles leave through shared memory and TMA stores: one output map per destination slab
+    if (tmap_of_rank[tgt] < 0) {
+      rc = encode_tmap_2d_sw128(&p.tmap_out[n_maps], slab0, slab_rows, g.N, slab_ld, GEMM_BM, 64);
+      if (rc != SYN_OK) return rc;
+      tmap_of_rank[tgt] = n_maps++;
+    }
+    rt.tmap = static_cast<int16_t>(tmap_of_rank[tgt]);
+    rt.tmap_row0 = row_in_slab;
   }
   // staged partial sums to add in the owner wave, with the local flags that publish them
   int n_red = 0;

@@ -28,10 +28,11 @@ static long count_tiles(const syn_schedule* s, int M, int N, int bn) {
   return t;
 }
 
-int pick_block_n(const syn_schedule* s, int M, int N, int num_sms) {
+int pick_block_n(const syn_schedule* s, int M, int N, int num_sms, int multiple) {
   int best = 0;
   double best_cost = 0;
   for (int bn : kBlockN) {
+    if (bn % multiple != 0) continue;
     if (!block_n_ok(s, N, bn)) continue;
     const long tiles = count_tiles(s, M, N, bn);
     const long rounds = (tiles + num_sms - 1) / num_sms;
@@ -79,6 +80,7 @@ int gemm_fill_common(GemmParams* p, const syn_gemm_args* a, const syn_schedule* 
   if (rc != SYN_OK) return rc;
 
   memset(p, 0, sizeof(*p));
+  for (int i = 0; i < GEMM_MAX_WAVES; ++i) p->routes[i].tmap = -1;  // direct stores unless a caller says otherwise
   rc = encode_tmap_2d_sw128(&p->tmap_a, a->a, a->M, a->K, lda, GEMM_BM, GEMM_BK);
   if (rc != SYN_OK) return rc;
   rc = encode_tmap_2d_sw128(&p->tmap_b, a->b, a->N, a->K, ldb, bn, GEMM_BK);
@@ -173,14 +175,14 @@ int gemm_launch(const GemmParams& p, int bn, bool fused, int grid, cudaStream_t 
 #undef SYN_BN_CASE
 }
 
-int gemm_resolve_grid_and_bn(const syn_gemm_args* a, const syn_schedule* sched, int* grid, int* bn) {
+int gemm_resolve_grid_and_bn(const syn_gemm_args* a, const syn_schedule* sched, int* grid, int* bn, int multiple) {
   int sms = 0;
   int rc = device_sm_count(&sms);
   if (rc != SYN_OK) return rc;
   int g = a->num_sms > 0 ? std::min(a->num_sms, sms) : sms;
   int b = a->block_n;
-  if (b == 0) b = pick_block_n(sched, a->M, a->N, g);
-  if (b == 0) return SYN_ERR_SHAPE;
+  if (b == 0) b = pick_block_n(sched, a->M, a->N, g, multiple);
+  if (b == 0 || b % multiple != 0) return SYN_ERR_SHAPE;
   *grid = g;
   *bn = b;
   return SYN_OK;
@@ -192,7 +194,7 @@ extern "C" {
 
 int syn_gemm_pick_block_n(int M, int N, int num_sms) {
   if (M <= 0 || N <= 0 || num_sms <= 0) return SYN_ERR_INVALID;
-  return syn::pick_block_n(nullptr, M, N, num_sms);
+  return syn::pick_block_n(nullptr, M, N, num_sms, 32);
 }
 
 int syn_gemm(const syn_gemm_args* args, const syn_schedule* sched, const syn_schedule* producer_sched,

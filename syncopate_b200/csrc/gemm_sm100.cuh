@@ -21,8 +21,15 @@ constexpr int GEMM_UMMA_K = 16;
 constexpr int GEMM_MAX_WAVES = 64;
 constexpr int GEMM_MAX_COMM_OPS = 64;
 constexpr int GEMM_THREADS = 256;    // warp0 TMA, warp1 MMA, warp2 TMEM alloc, warp3 comm, warps4-7 epilogue
-constexpr int COMM_PIECE = 8192;     // bytes per bulk copy of the comm warp
-constexpr int COMM_NBUF = 4;
+#ifndef SYN_COMM_PIECE
+#define SYN_COMM_PIECE 8192
+#endif
+#ifndef SYN_COMM_NBUF
+#define SYN_COMM_NBUF 4
+#endif
+constexpr int COMM_PIECE = SYN_COMM_PIECE;  // bytes per bulk copy of the comm warp
+constexpr int COMM_NBUF = SYN_COMM_NBUF;    // ring slots (NBUF - 1 loads in flight at most)
+static_assert(COMM_PIECE * COMM_NBUF >= 2 * 128 * 128, "the routed epilogue stages two 128 x 64 16-bit half tiles there");
 
 struct GemmWave {
   int16_t tiles_m, tiles_n;  // tile grid of the wave
@@ -39,7 +46,10 @@ struct GemmRoute {
   const uint64_t* gate;   // flag that must be >= gate_value before the first store of the wave; may be null
   uint64_t gate_value;
   int32_t ld;             // destination leading dimension (elements)
-  int32_t reduce;         // 1 = add the staged partial sums (reduce-scatter owner wave)
+  int16_t reduce;         // 1 = add the staged partial sums (reduce-scatter owner wave)
+  int16_t tmap;           // index into GemmParams::tmap_out: tiles leave through shared memory and TMA
+                          // stores (full 128-byte lines, the form NVLink carries well); -1 = direct stores
+  int32_t tmap_row0;      // row of the wave's first tile row in that map's coordinates
 };
 
 // One 2-D strided copy between mapped buffers, executed cooperatively by all comm warps.
@@ -55,6 +65,7 @@ struct CommOp {
 struct GemmParams {
   CUtensorMap tmap_a;
   CUtensorMap tmap_b;
+  CUtensorMap tmap_out[8];  // destinations of TMA-store routes (one per target rank)
   void* c;
   int32_t ldc;
   int32_t M, N, K;
@@ -360,6 +371,15 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * ACC_STRIDE);
       const int col0 = n_blk * BN;
       const bool row_ok = grow < p.M;
+      int tmap_idx = -1, tmap_y = 0;
+      if constexpr (FUSED) {
+        if (wv.route >= 0 && p.routes[wv.route].tmap >= 0) {
+          tmap_idx = p.routes[wv.route].tmap;
+          tmap_y = p.routes[wv.route].tmap_row0 + (m_blk - wv.off_m) * GEMM_BM;
+        }
+      }
+      const bool leader = (warp == 4 && lane == 0);
+      const int srow = q * 32 + lane;  // row of this thread inside the 128-row staging tile
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -389,18 +409,46 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
             }
           }
         }
-        if (row_ok) {
+        uint4 packed[4];
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          packed[v].x = pack2(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]), p.dtype);
+          packed[v].y = pack2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]), p.dtype);
+          packed[v].z = pack2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]), p.dtype);
+          packed[v].w = pack2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]), p.dtype);
+        }
+        bool staged = false;
+        if constexpr (FUSED) {
+          if (tmap_idx >= 0) {
+            staged = true;
+            // 64-column halves of the tile go through two 16 KB staging buffers (the comm ring's
+            // space, which a routed epilogue does not otherwise use), laid out with the 128-byte
+            // swizzle of the output tensor map
+            uint8_t* sbuf = ring + ((c >> 1) & 1) * (GEMM_BM * 128);
+            if ((c & 1) == 0) {
+              if (leader) bulk_wait_read<1>();  // the store that last read this buffer is done with it
+              asm volatile("bar.sync 1, 128;" ::: "memory");
+            }
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const int chunk16 = (c & 1) * 4 + v;
+              *reinterpret_cast<uint4*>(sbuf + srow * 128 + ((chunk16 ^ (srow & 7)) << 4)) = packed[v];
+            }
+            if ((c & 1) == 1) {
+              fence_proxy_async_smem();
+              asm volatile("bar.sync 1, 128;" ::: "memory");
+              if (leader) {
+                tma_store_2d(&p.tmap_out[tmap_idx], sbuf, col0 + (c >> 1) * 64, tmap_y);
+                bulk_commit();
+              }
+            }
+          }
+        }
+        if (!staged && row_ok) {
           uint4* dst = reinterpret_cast<uint4*>(out_base + (static_cast<size_t>(out_row) * out_ld + col) * 2);
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
-            if (col + v * 8 < p.N) {
-              uint4 u;
-              u.x = pack2(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]), p.dtype);
-              u.y = pack2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]), p.dtype);
-              u.z = pack2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]), p.dtype);
-              u.w = pack2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]), p.dtype);
-              dst[v] = u;
-            }
+            if (col + v * 8 < p.N) dst[v] = packed[v];
           }
         }
       }
@@ -413,6 +461,12 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
       if constexpr (FUSED) {
         // wave completion: count stored tiles; the last one raises the wave's flag
         if (wv.route >= 0 && p.routes[wv.route].flag != nullptr) {
+          if (tmap_idx >= 0) {
+            if (leader) {
+              bulk_wait<0>();  // this tile's TMA stores have been performed
+              fence_proxy_async();
+            }
+          }
           __threadfence_system();
           asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
           if (warp == 4 && lane == 0) {
@@ -430,6 +484,9 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
     }
   }
 
+  if constexpr (FUSED) {
+    if (warp == 4 && lane == 0) bulk_wait<0>();  // staged tiles still being read by TMA stores
+  }
   tc_fence_before();
   __syncthreads();
   if (warp == 2) {

@@ -102,9 +102,34 @@ __global__ void flag_wait_kernel(const uint64_t* flag, uint64_t value, uint64_t 
 
 extern "C" {
 
+int syn_memcpy_async(void* dst, const void* src, size_t bytes, void* stream) {
+  using namespace syn;
+  if (dst == nullptr || src == nullptr) return SYN_ERR_INVALID;
+  if (bytes == 0) return SYN_OK;
+  SYN_CUDA_TRY(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, static_cast<cudaStream_t>(stream)));
+  return SYN_OK;
+}
+
 int syn_flag_set(uint64_t* flag, uint64_t value, void* stream) {
   using namespace syn;
   if (flag == nullptr) return SYN_ERR_INVALID;
+  // A stream memory operation needs no SM, so it cannot be starved by a persistent kernel that
+  // fills the GPU while waiting for this very flag; the one-thread kernel is the fallback.
+  typedef CUresult (*write_value_fn)(CUstream, CUdeviceptr, cuuint64_t, unsigned int);
+  static write_value_fn write_value = nullptr;
+  static bool looked_up = false;
+  if (!looked_up) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuStreamWriteValue64", &fn, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      write_value = reinterpret_cast<write_value_fn>(fn);
+    looked_up = true;
+  }
+  if (write_value != nullptr) {
+    CUresult r = write_value(static_cast<CUstream>(stream), reinterpret_cast<CUdeviceptr>(flag), value, 0);
+    if (r == CUDA_SUCCESS) return SYN_OK;
+  }
   flag_set_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(flag, value);
   SYN_CUDA_TRY(cudaGetLastError());
   return SYN_OK;

@@ -28,7 +28,8 @@ from .runtime import SymmetricContext
 NUM_COUNTERS = 128  # SYN_MAX_WAVES + SYN_MAX_COMM_OPS
 
 
-def plan_all_gather(world: int, rows_per_rank: int, K: int, dtype: torch.dtype, kind: str = "swizzle"):
+def plan_all_gather(world: int, rows_per_rank: int, K: int, dtype: torch.dtype, kind: str = "swizzle",
+                    copy_engine: bool = False):
     """(generator, comm_info, lowered) for gathering ``[rows_per_rank, K]`` shards along dim 0."""
     shape = (rows_per_rank * world, K)
     if kind == "swizzle":
@@ -39,7 +40,7 @@ def plan_all_gather(world: int, rows_per_rank: int, K: int, dtype: torch.dtype, 
         raise ValueError("kind must be 'swizzle' or 'ring'")
     gen = CommGenerator(plans)
     gen.plan_signals(plan_compute_signals=True)
-    info = gen.generate_code_for_plan(CodeGenOptions(copy_engine=False))
+    info = gen.generate_code_for_plan(CodeGenOptions(copy_engine=copy_engine))
     return gen, info, lower_comm_plan_to_raw_schedules(gen)
 
 
@@ -69,21 +70,39 @@ def plan_reduce_scatter(world: int, M: int, N: int, dtype: torch.dtype, kind: st
 
 
 class AllGatherGemm:
-    """``C[rows * world, N] = all_gather(A_shard)[rows * world, K] @ B[N, K]^T`` per rank."""
+    """``C[rows * world, N] = all_gather(A_shard)[rows * world, K] @ B[N, K]^T`` per rank.
+
+    ``comm="sm"``: the kernel's comm warps pull the chunks (``CodeGenOptions(copy_engine=False)``
+    program); ``comm="ce"``: the rank's copy-engine program (``copy_engine=True``) runs on a side
+    stream through ``CommContext.execute`` while the flag-gated GEMM runs on the caller's stream,
+    as in the reference's tests/test_ag_gemm_gen.py:44-77."""
 
     def __init__(self, ctx: SymmetricContext, rows_per_rank: int, K: int, N: int, dtype=torch.bfloat16,
-                 plan: str = "swizzle", num_sms: int = 0, block_n: int = 0, timeout_ns: int = 0):
+                 plan: str = "swizzle", num_sms: int = 0, block_n: int = 0, timeout_ns: int = 0, comm: str = "sm"):
         self.ctx = ctx
         self.world, self.rank = ctx.world, ctx.rank
         self.rows, self.K, self.N, self.dtype = rows_per_rank, K, N, dtype
         self.M = rows_per_rank * self.world
         self.num_sms, self.block_n, self.timeout_ns = num_sms, block_n, timeout_ns
-        self.generator, self.info, lowered = plan_all_gather(self.world, rows_per_rank, K, dtype, plan)
+        self.comm = comm
+        self.generator, self.info, lowered = plan_all_gather(self.world, rows_per_rank, K, dtype, plan,
+                                                             copy_engine=(comm == "ce"))
         self.schedule = lowered[self.rank]["a"]
+        self.epoch = 0
+        if comm == "ce":
+            from .communication.comm_runtime.communication_context import CommContext
+
+            self.info.local_world_size = self.world
+            self.comm_ctx = CommContext(self.rank, self.info, symmetric=ctx, timeout_ns=timeout_ns)
+            self.a = self.comm_ctx._buffers["a"]
+            self.flags = self.comm_ctx._recv
+            self._wave_offsets = [[o[0], 0] for o in self.schedule.gen_block_offset_lists()]
+            self._wave_sizes = [[s[0], N] for s in self.schedule.gen_block_shape_lists()]
+            self._signals = self.schedule.gen_signal_lists()
+            return
         self.a = ctx.alloc((self.M, K), dtype)
         self.flags = ctx.alloc((max(self.info.recv_signal_num, 1),), torch.int64)
         self.counters = torch.zeros(NUM_COUNTERS, dtype=torch.int32, device=ctx.device)
-        self.epoch = 0
 
     @property
     def shard(self) -> torch.Tensor:
@@ -97,6 +116,17 @@ class AllGatherGemm:
         if self.world == 1:
             return gemm(self.a.local, b, c, 1, self.num_sms, BLOCK_SIZE_N=self.block_n, status=self.ctx.status,
                         timeout_ns=self.timeout_ns, stream=stream)
+        if self.comm == "ce":
+            cur = stream or torch.cuda.current_stream()
+            self.comm_ctx.signal_value = self.epoch
+            self.comm_ctx.start_after(cur)
+            self.comm_ctx.execute(neglect_local=True)
+            gemm(self.a.local, b, c, self.world, self.num_sms, BLOCK_SIZE_N=self.block_n,
+                 cur_wave_sizes=self._wave_sizes, wave_offsets=self._wave_offsets, signal_ptr=self.flags.local,
+                 signal_offsets=self._signals, signal_value=self.epoch, status=self.ctx.status,
+                 timeout_ns=self.timeout_ns, stream=cur)
+            self.comm_ctx.end_before(cur)
+            return c
         return ag_gemm(self.a.symm, self.a.local, b, c, self.schedule, self.flags.local, self.counters,
                        epoch=self.epoch, num_sms=self.num_sms, block_n=self.block_n, timeout_ns=self.timeout_ns,
                        status=self.ctx.status, stream=stream)

@@ -32,8 +32,11 @@ def main():
     dt = torch.bfloat16
     failures = []
 
-    for kind, rows, K, N in (("swizzle", 256, 512, 512), ("ring", 128, 256, 512), ("swizzle", 1024, 8192, 28672 // world)):
-        op = AllGatherGemm(ctx, rows, K, N, dt, plan=kind, timeout_ns=2_000_000_000)
+    for kind, comm, rows, K, N in (("swizzle", "sm", 256, 512, 512), ("ring", "sm", 128, 256, 512),
+                                   ("swizzle", "ce", 256, 512, 512),
+                                   ("swizzle", "sm", 1024, 8192, 28672 // world),
+                                   ("swizzle", "ce", 1024, 8192, 28672 // world)):
+        op = AllGatherGemm(ctx, rows, K, N, dt, plan=kind, comm=comm, timeout_ns=2_000_000_000)
         shards = [seeded(1000 + r, (rows, K), 1.0, dt, dev) for r in range(world)]
         b = seeded(5000 + rank, (N, K), 0.02, dt, dev)
         full = torch.cat(shards, 0)
@@ -48,11 +51,11 @@ def main():
             e = rel(c, ref)
             same = torch.equal(op.a.local, full)
             if not (e < TOL and same):
-                failures.append(f"ag_gemm {kind} rows={rows} it={it} rank={rank}: relerr={e:.3e} gathered_ok={same}")
+                failures.append(f"ag_gemm {kind}/{comm} rows={rows} it={it} rank={rank}: relerr={e:.3e} gathered_ok={same}")
             ctx.barrier()  # nobody may overwrite its shard while a peer still pulls it
             torch.cuda.synchronize()
 
-    for kind, M, N, Kl in (("direct", 1024, 512, 256), ("a2a", 512, 1024, 512), ("direct", 8192, 8192, 28672 // world)):
+    for kind, M, N, Kl in (("direct", 256 * world, 512, 256), ("a2a", 128 * world, 1024, 512), ("direct", 8192, 8192, 28672 // world)):
         op = GemmReduceScatter(ctx, M, N, dt, plan=kind, timeout_ns=2_000_000_000)
         a = seeded(2000 + rank, (M, Kl), 1.0, dt, dev)
         b = seeded(3000 + rank, (N, Kl), 0.02, dt, dev)
