@@ -180,6 +180,7 @@ def workload_config(n_gpus: int):
         "tp": tp, "flop_per_rank": 2.0 * ROWS * tp * K_DIM * (N_TOTAL // tp),
         "l2": "inputs+outputs 250 MB per step exceed the 126 MB L2; no explicit flush",
         "plan": "build_all_gather_plan_1d_swizzle pull",
+        "comm": "copy-engine program on a side stream + flag-gated tcgen05 GEMM (--comm ce) or in-kernel comm warps (--comm sm)",
     }
 
 
@@ -362,7 +363,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--comm", default="sm", choices=["sm", "ce"],
+    ap.add_argument("--comm", default="ce", choices=["sm", "ce"],
                     help="who moves the all-gather chunks: the kernel's comm warps (sm) or copy engines (ce)")
     args = ap.parse_args()
     if args.impl == "reference":
