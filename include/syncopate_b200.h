@@ -211,6 +211,78 @@ typedef struct syn_gemm_rs_args {
 int syn_gemm_rs(const syn_gemm_rs_args* args, const syn_schedule* src_sched, const syn_schedule* dst_sched,
                 void* stream);
 
+/* ------------------------------------------------------------------ attention
+ * Flash-attention forward over a wave schedule (replaces the TLX kernel
+ * _attn_fwd_ws_pipelined_pingpong and its host wrapper, syncopate/computation/attn/template.py:47-436,
+ * and the un-fused local_code.py).  q [Z, Hq, Sq, D], k / v [Z, Hkv, Skv, D], o [Z, Hq, Sq, D] with
+ * arbitrary element strides for (z, h, s) and D = 128 contiguous (so BHSD and BSHD layouts and
+ * slices of a stacked [3, ...] buffer all work); 16-bit inputs, fp32 softmax, 16-bit output.
+ * Hq must be a multiple of Hkv (grouped-query heads share a KV head).
+ *
+ * `sched` has ndim = 4 with axes (Z, H, Q, KV) in tokens, as the reference's wave metadata
+ * (tests/test_all2all_attn_transform.py:58-117, tests/test_double_ring_ag_attn.py:60-81): a wave
+ * covers the (z, h, q) box and attends to keys [kv_off, kv_off + kv_len); Q and KV offsets and
+ * lengths must be multiples of 128.  A wave with signals[w] >= 0 starts only once
+ * signal_ptr[signals[w]] >= signal_value.  A query row visited by several waves ends with the
+ * log-sum-exp merge of its partial results; `lse` [Z, Hq, Sq] receives log2-domain LSE values.
+ * `causal`: key j is visible to query i iff kv_pos(j) <= q_pos(i), positions being
+ * q_pos[tile] + row and kv_pos[block] + col (device int32 arrays per 128 rows / keys; NULL =
+ * the index itself).  Key blocks with no visible key are skipped.
+ * `visit` is device int32 [Z, Hq, Sq] scratch, zero before the first call; `epoch` must be positive
+ * and increase from call to call (rows not visited by a call keep their old contents).
+ */
+typedef struct syn_attn_args {
+  const void* q;
+  const void* k;
+  const void* v;
+  void* o;
+  float* lse;
+  int32_t* visit;
+  int32_t Z, Hq, Hkv, Sq, Skv, D;
+  int64_t q_strides[3]; /* elements: z, h, s */
+  int64_t k_strides[3];
+  int64_t v_strides[3];
+  int64_t o_strides[3];
+  float sm_scale;
+  int32_t causal;
+  const int32_t* q_pos;
+  const int32_t* kv_pos;
+  int32_t dtype;
+  int32_t num_sms;
+  int32_t epoch;
+  const uint64_t* signal_ptr;
+  uint64_t signal_value; /* 0 = 1 */
+  uint64_t timeout_ns;   /* 0 = 2 s */
+  int32_t* status;
+} syn_attn_args;
+
+/* One 2-D strided copy for the kernel's comm warps: `rows` rows of `row_bytes` bytes from
+ * bufs[src_buf].ptrs[src_rank] + src_offset (pitch src_pitch) to bufs[dst_buf].ptrs[dst_rank] +
+ * dst_offset (pitch dst_pitch); one end must be this rank.  When it has landed,
+ * flags.ptrs[flag_rank][flag] is raised to signal_value (flag < 0: nothing).  Addresses, pitches
+ * and row_bytes must be multiples of 16.  This is the N-D box form of the reference's SMCopyOp
+ * (syncopate/communication/comm_runtime/operations.py:20-33) cut into 2-D pieces. */
+typedef struct syn_copy_op {
+  int32_t src_rank, dst_rank;
+  int32_t src_buf, dst_buf;
+  uint64_t src_offset, dst_offset;
+  uint64_t src_pitch, dst_pitch;
+  uint32_t rows, row_bytes;
+  int32_t flag_rank, flag;
+} syn_copy_op;
+
+typedef struct syn_attn_comm {
+  int32_t num_ops;
+  const syn_copy_op* ops;  /* host array, executed in order, each op spread over all CTAs */
+  int32_t num_bufs;
+  syn_symm bufs[4];
+  syn_symm flags;          /* uint64 flag arrays */
+  uint32_t* counters;      /* device uint32[SYN_MAX_COMM_OPS], zero before the first call */
+} syn_attn_comm;
+
+/* `comm` may be NULL (data already in place; flags, if any, raised by somebody else). */
+int syn_attention(const syn_attn_args* args, const syn_schedule* sched, const syn_attn_comm* comm, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -120,6 +120,72 @@ class GemmRsArgs(C.Structure):
     ]
 
 
+class AttnArgs(C.Structure):
+    """``syn_attn_args``."""
+
+    _fields_ = [
+        ("q", C.c_void_p),
+        ("k", C.c_void_p),
+        ("v", C.c_void_p),
+        ("o", C.c_void_p),
+        ("lse", C.c_void_p),
+        ("visit", C.c_void_p),
+        ("Z", C.c_int32),
+        ("Hq", C.c_int32),
+        ("Hkv", C.c_int32),
+        ("Sq", C.c_int32),
+        ("Skv", C.c_int32),
+        ("D", C.c_int32),
+        ("q_strides", C.c_int64 * 3),
+        ("k_strides", C.c_int64 * 3),
+        ("v_strides", C.c_int64 * 3),
+        ("o_strides", C.c_int64 * 3),
+        ("sm_scale", C.c_float),
+        ("causal", C.c_int32),
+        ("q_pos", C.c_void_p),
+        ("kv_pos", C.c_void_p),
+        ("dtype", C.c_int32),
+        ("num_sms", C.c_int32),
+        ("epoch", C.c_int32),
+        ("signal_ptr", C.c_void_p),
+        ("signal_value", C.c_uint64),
+        ("timeout_ns", C.c_uint64),
+        ("status", C.c_void_p),
+    ]
+
+
+class CopyOp(C.Structure):
+    """``syn_copy_op``."""
+
+    _fields_ = [
+        ("src_rank", C.c_int32),
+        ("dst_rank", C.c_int32),
+        ("src_buf", C.c_int32),
+        ("dst_buf", C.c_int32),
+        ("src_offset", C.c_uint64),
+        ("dst_offset", C.c_uint64),
+        ("src_pitch", C.c_uint64),
+        ("dst_pitch", C.c_uint64),
+        ("rows", C.c_uint32),
+        ("row_bytes", C.c_uint32),
+        ("flag_rank", C.c_int32),
+        ("flag", C.c_int32),
+    ]
+
+
+class AttnComm(C.Structure):
+    """``syn_attn_comm``."""
+
+    _fields_ = [
+        ("num_ops", C.c_int32),
+        ("ops", C.POINTER(CopyOp)),
+        ("num_bufs", C.c_int32),
+        ("bufs", Symm * 4),
+        ("flags", Symm),
+        ("counters", C.c_void_p),
+    ]
+
+
 _lib: Optional[C.CDLL] = None
 
 
@@ -170,6 +236,8 @@ def _declare(l: C.CDLL) -> None:
     l.syn_flag_wait.argtypes = [C.c_void_p, C.c_uint64, C.c_uint64, C.c_void_p, C.c_int, C.c_void_p]
     l.syn_ag_gemm.restype = C.c_int
     l.syn_ag_gemm.argtypes = [C.POINTER(AgGemmArgs), C.POINTER(Schedule), C.c_void_p]
+    l.syn_attention.restype = C.c_int
+    l.syn_attention.argtypes = [C.POINTER(AttnArgs), C.POINTER(Schedule), C.POINTER(AttnComm), C.c_void_p]
     l.syn_gemm_rs.restype = C.c_int
     l.syn_gemm_rs.argtypes = [C.POINTER(GemmRsArgs), C.POINTER(Schedule), C.POINTER(Schedule), C.c_void_p]
 

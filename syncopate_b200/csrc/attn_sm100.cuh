@@ -1,0 +1,457 @@
+// Flash-attention forward for sm_100a over a wave schedule: tcgen05.mma for S = Q K^T and O += P V,
+// S / P / partial O in tensor memory, online softmax in the exp2 domain, causal masking by true
+// token positions, grouped-query heads, and log-sum-exp merging of the partial results of a query
+// tile that several waves visit.
+//
+// Follows the behaviour of Syncopate's wave-dispatched FA kernel
+// (syncopate/computation/attn/template.py:47-361): a work unit is (z, h, 128-row Q tile) of a wave
+// and runs over the wave's KV range (:80-121); a wave with a signal index waits for its flag first
+// (:90-97); a Q tile visited again merges (O, log2-LSE) with what is stored (:339-349).  Instead of
+// the reference's global spin lock, every Q tile is owned by one CTA for the whole launch (tile
+// id modulo grid size), which visits it wave after wave, so merges need no lock.
+//
+// Roles per CTA (256 threads): warp 0 TMA producer, warp 1 MMA issuer, warp 2 TMEM allocator,
+// warp 3 comm warp (copies scheduled chunks between peer-mapped buffers, optional), warps 4-7
+// softmax / accumulate / merge / store (thread t owns query row t of the tile).
+#pragma once
+#include "gemm_sm100.cuh"  // CommOp, comm_warp_run, pack helpers
+
+namespace syn {
+
+constexpr int ATTN_BM = 128;   // query rows per tile
+constexpr int ATTN_BN = 128;   // keys per block
+constexpr int ATTN_D = 128;    // head dimension
+constexpr int ATTN_MAX_WAVES = 96;
+constexpr int ATTN_MAX_COMM_OPS = 48;
+constexpr int ATTN_KV_STAGES = 2;
+constexpr int ATTN_TILE_BYTES = ATTN_BM * ATTN_D * 2;  // 32 KB: two 128 x 64 swizzled boxes
+
+struct AttnWave {
+  int16_t z0, nz, h0, nh;  // batch / head box of the wave
+  int32_t q0t, nqt;        // first query tile and number of query tiles (units of 128 rows)
+  int32_t kb0, kb1;        // key-block range [kb0, kb1) (units of 128 keys)
+  int32_t sig;             // flag index to wait for, -1 = none
+};
+
+struct AttnParams {
+  CUtensorMap tmap_q, tmap_k, tmap_v;  // 4-D (d, s, h, z), box 64 x 128
+  void* o;
+  float* lse;              // [Z, Hq, Sq] log2 domain
+  int32_t* visit;          // [Z, Hq, Sq]: epoch of the last launch that wrote the row
+  int64_t o_sz, o_sh, o_ss;  // output strides in elements (z, h, s)
+  int32_t Z, Hq, Hkv, Sq, Skv;
+  int32_t q_tiles;         // ceil(Sq / 128)
+  int32_t causal;
+  int32_t dtype;
+  int32_t epoch;
+  int32_t num_waves;
+  int32_t num_comm_ops;
+  float scale_log2;        // sm_scale * log2(e)
+  const int32_t* q_pos;    // true position of the first row of each query tile, null = tile * 128
+  const int32_t* kv_pos;   // true position of the first key of each key block, null = block * 128
+  const uint64_t* flags;
+  uint32_t* counters;      // comm counters [num_comm_ops]
+  uint64_t signal_value;
+  uint64_t timeout_ns;
+  int32_t* status;
+  uint32_t idesc_qk, idesc_pv;
+  AttnWave waves[ATTN_MAX_WAVES];
+  CommOp comm[ATTN_MAX_COMM_OPS];
+};
+
+// Enumerates, in wave order, the units this CTA owns.  All roles run the same enumeration.
+struct UnitCursor {
+  int wave = 0, zi = 0, hi = 0, qt = -1;
+  bool wave_started = false;
+  bool new_wave = false;  // set when the returned unit is the CTA's first of its wave
+  __device__ __forceinline__ bool next(const AttnParams& p, int& z, int& h, int& qtile) {
+    const int G = gridDim.x, c = blockIdx.x;
+    while (wave < p.num_waves) {
+      const AttnWave& w = p.waves[wave];
+      while (zi < w.nz) {
+        while (hi < w.nh) {
+          const int zz = w.z0 + zi, hh = w.h0 + hi;
+          if (qt < 0) {
+            const long base = (static_cast<long>(zz) * p.Hq + hh) * p.q_tiles;
+            const int r = static_cast<int>(((c - base) % G + G) % G);  // residue the tile index must have
+            qt = w.q0t + ((r - w.q0t) % G + G) % G;
+          } else {
+            qt += G;
+          }
+          if (qt < w.q0t + w.nqt) {
+            z = zz;
+            h = hh;
+            qtile = qt;
+            new_wave = !wave_started;
+            wave_started = true;
+            return true;
+          }
+          qt = -1;
+          ++hi;
+        }
+        hi = 0;
+        ++zi;
+      }
+      zi = 0;
+      ++wave;
+      wave_started = false;
+    }
+    return false;
+  }
+};
+
+// 0 = skip the block (no key visible to any row), 1 = no mask needed, 2 = mask by position.
+__device__ __forceinline__ int block_mode(const AttnParams& p, int qpos0, int kb) {
+  if (!p.causal) return 1;
+  const int kpos0 = p.kv_pos ? __ldg(p.kv_pos + kb) : kb * ATTN_BN;
+  if (kpos0 > qpos0 + ATTN_BM - 1) return 0;
+  if (kpos0 + ATTN_BN - 1 <= qpos0) return 1;
+  return 2;
+}
+
+template <bool FUSED>
+__global__ void __launch_bounds__(256, 1) attn_kernel(const __grid_constant__ AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;                                        // 2 tiles
+  uint8_t* sK = sQ + 2 * ATTN_TILE_BYTES;                    // ATTN_KV_STAGES tiles
+  uint8_t* sV = sK + ATTN_KV_STAGES * ATTN_TILE_BYTES;       // ATTN_KV_STAGES tiles
+  uint8_t* ring = sV + ATTN_KV_STAGES * ATTN_TILE_BYTES;     // FUSED only
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ring + (FUSED ? COMM_NBUF * COMM_PIECE : 0));
+  uint64_t* q_full = bars;            // [2]
+  uint64_t* q_empty = bars + 2;       // [2]
+  uint64_t* k_full = bars + 4;        // [KV_STAGES]
+  uint64_t* k_empty = bars + 6;
+  uint64_t* v_full = bars + 8;
+  uint64_t* v_empty = bars + 10;
+  uint64_t* s_full = bars + 12;       // [2] MMA -> softmax
+  uint64_t* p_full = bars + 14;       // [2] softmax -> MMA
+  uint64_t* o_full = bars + 16;       // [2] MMA -> softmax
+  uint64_t* o_empty = bars + 18;      // [2] softmax -> MMA
+  uint64_t* comm_bar = bars + 20;     // [COMM_NBUF]
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 20 + COMM_NBUF);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  int* abort_info = const_cast<int*>(abort_word) + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&q_full[i], 1);
+      mbar_init(&q_empty[i], 1);
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_full[i], 128);
+      mbar_init(&o_full[i], 1);
+      mbar_init(&o_empty[i], 128);
+    }
+    for (int i = 0; i < COMM_NBUF; ++i) mbar_init(&comm_bar[i], 1);
+    *abort_word = 0;
+    abort_info[0] = -1;
+    abort_info[1] = -1;
+    fence_mbar_init();
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_holder, 512);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    prefetch_tmap(&p.tmap_q);
+    prefetch_tmap(&p.tmap_k);
+    prefetch_tmap(&p.tmap_v);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  const int group = p.Hq / p.Hkv;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      UnitCursor cur;
+      int z, h, qt;
+      uint32_t u = 0, g = 0;  // running unit / key-block counters (ring positions)
+      int flag_wave = -1;     // last wave whose flag this CTA has waited for
+      while (cur.next(p, z, h, qt)) {
+        const AttnWave& w = p.waves[cur.wave];
+        const int qpos0 = p.q_pos ? __ldg(p.q_pos + qt) : qt * ATTN_BM;
+        int active = 0;
+        for (int kb = w.kb0; kb < w.kb1; ++kb) active += block_mode(p, qpos0, kb) != 0;
+        if (active == 0) continue;
+        if (cur.wave != flag_wave && w.sig >= 0 && p.flags != nullptr) {
+          flag_wave = cur.wave;
+          if (!flag_wait_ge(p.flags + w.sig, p.signal_value, abort_word, p.timeout_ns)) {
+            if (abort_info[0] < 0) {
+              abort_info[0] = cur.wave;
+              abort_info[1] = w.sig;
+            }
+          }
+          fence_proxy_async();
+        }
+        const int qb = u & 1;
+        mbar_wait(&q_empty[qb], ((u >> 1) & 1u) ^ 1u, abort_word, p.timeout_ns);
+        mbar_expect_tx(&q_full[qb], ATTN_TILE_BYTES);
+        tma_load_4d(sQ + qb * ATTN_TILE_BYTES, &p.tmap_q, &q_full[qb], 0, qt * ATTN_BM, h, z);
+        tma_load_4d(sQ + qb * ATTN_TILE_BYTES + ATTN_TILE_BYTES / 2, &p.tmap_q, &q_full[qb], 64, qt * ATTN_BM, h, z);
+        ++u;
+        const int hk = h / group;
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
+          if (block_mode(p, qpos0, kb) == 0) continue;
+          const int st = g % ATTN_KV_STAGES;
+          const uint32_t par = ((g / ATTN_KV_STAGES) & 1u) ^ 1u;
+          mbar_wait(&k_empty[st], par, abort_word, p.timeout_ns);
+          mbar_expect_tx(&k_full[st], ATTN_TILE_BYTES);
+          tma_load_4d(sK + st * ATTN_TILE_BYTES, &p.tmap_k, &k_full[st], 0, kb * ATTN_BN, hk, z);
+          tma_load_4d(sK + st * ATTN_TILE_BYTES + ATTN_TILE_BYTES / 2, &p.tmap_k, &k_full[st], 64, kb * ATTN_BN, hk, z);
+          mbar_wait(&v_empty[st], par, abort_word, p.timeout_ns);
+          mbar_expect_tx(&v_full[st], ATTN_TILE_BYTES);
+          tma_load_4d(sV + st * ATTN_TILE_BYTES, &p.tmap_v, &v_full[st], 0, kb * ATTN_BN, hk, z);
+          tma_load_4d(sV + st * ATTN_TILE_BYTES + ATTN_TILE_BYTES / 2, &p.tmap_v, &v_full[st], 64, kb * ATTN_BN, hk, z);
+          ++g;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      UnitCursor cur;
+      int z, h, qt;
+      uint32_t u = 0, g = 0;
+      auto issue_qk = [&](uint32_t gi, int qb) {
+        const int st = gi % ATTN_KV_STAGES;
+        mbar_wait(&k_full[st], (gi / ATTN_KV_STAGES) & 1u, abort_word, p.timeout_ns);
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (gi & 1u) * 128u;
+#pragma unroll
+        for (int kk = 0; kk < ATTN_D / 16; ++kk) {
+          const uint32_t half = (kk >> 2) * (ATTN_TILE_BYTES / 2);
+          const uint64_t a = make_smem_desc_sw128(smem_u32(sQ + qb * ATTN_TILE_BYTES + half), 16, 1024) + 2 * (kk & 3);
+          const uint64_t b = make_smem_desc_sw128(smem_u32(sK + st * ATTN_TILE_BYTES + half), 16, 1024) + 2 * (kk & 3);
+          umma_f16_ss(d_tmem, a, b, p.idesc_qk, kk != 0 ? 1u : 0u);
+        }
+        umma_commit(&k_empty[st]);
+        umma_commit(&s_full[gi & 1u]);
+      };
+      while (cur.next(p, z, h, qt)) {
+        const AttnWave& w = p.waves[cur.wave];
+        const int qpos0 = p.q_pos ? __ldg(p.q_pos + qt) : qt * ATTN_BM;
+        int active = 0;
+        for (int kb = w.kb0; kb < w.kb1; ++kb) active += block_mode(p, qpos0, kb) != 0;
+        if (active == 0) continue;
+        const int qb = u & 1;
+        mbar_wait(&q_full[qb], (u >> 1) & 1u, abort_word, p.timeout_ns);
+        issue_qk(g, qb);
+        for (int j = 0; j < active; ++j) {
+          const uint32_t gi = g + j;
+          if (j + 1 < active) issue_qk(gi + 1, qb);
+          // P_j is in tensor memory and the partial-O buffer is free again
+          mbar_wait(&p_full[gi & 1u], (gi >> 1) & 1u, abort_word, p.timeout_ns);
+          mbar_wait(&o_empty[gi & 1u], ((gi >> 1) & 1u) ^ 1u, abort_word, p.timeout_ns);
+          const int st = gi % ATTN_KV_STAGES;
+          mbar_wait(&v_full[st], (gi / ATTN_KV_STAGES) & 1u, abort_word, p.timeout_ns);
+          tc_fence_after();
+          const uint32_t p_tmem = tmem_base + (gi & 1u) * 128u;         // bf16 pairs over the first 64 columns of S
+          const uint32_t o_tmem = tmem_base + 256u + (gi & 1u) * 128u;
+#pragma unroll
+          for (int kk = 0; kk < ATTN_BN / 16; ++kk) {
+            // V block in shared memory: [128 keys][64 d] per box, keys are the K axis (128 B apart),
+            // d is the contiguous (MN) axis; the second box (d 64..127) lies 16 KB further
+            const uint64_t b = make_smem_desc_sw128(smem_u32(sV + st * ATTN_TILE_BYTES + kk * 16 * 128),
+                                                    ATTN_TILE_BYTES / 2, 1024);
+            umma_f16_ts(o_tmem, p_tmem + kk * 8, b, p.idesc_pv, kk != 0 ? 1u : 0u);
+          }
+          umma_commit(&v_empty[st]);
+          umma_commit(&o_full[gi & 1u]);
+        }
+        umma_commit(&q_empty[qb]);
+        g += active;
+        ++u;
+      }
+    }
+  } else if (warp == 3) {
+    if constexpr (FUSED) {
+      comm_warp_run(p.comm, p.num_comm_ops, p.counters, p.signal_value, reinterpret_cast<char*>(ring), comm_bar,
+                    abort_word, p.timeout_ns, lane);
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------ softmax / accumulate / merge / store
+    const int q = warp & 3;
+    const int row = q * 32 + lane;  // query row inside the tile, also the TMEM lane
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    UnitCursor cur;
+    int z, h, qt;
+    uint32_t g = 0;
+    float o_acc[ATTN_D];
+    while (cur.next(p, z, h, qt)) {
+      const AttnWave& w = p.waves[cur.wave];
+      const int qpos0 = p.q_pos ? __ldg(p.q_pos + qt) : qt * ATTN_BM;
+      int active = 0;
+      for (int kb = w.kb0; kb < w.kb1; ++kb) active += block_mode(p, qpos0, kb) != 0;
+      if (active == 0) continue;
+      float m = -INFINITY, l = 0.f;
+#pragma unroll
+      for (int i = 0; i < ATTN_D; ++i) o_acc[i] = 0.f;
+      int j = 0;
+      for (int kb = w.kb0; kb < w.kb1; ++kb) {
+        const int mode = block_mode(p, qpos0, kb);
+        if (mode == 0) continue;
+        const uint32_t gi = g + j;
+        const uint32_t s_tmem = lane_base + (gi & 1u) * 128u;
+        // keys 0..lim of the block are visible to this row
+        int lim = ATTN_BN - 1;
+        if (mode == 2) {
+          const int kpos0 = p.kv_pos ? __ldg(p.kv_pos + kb) : kb * ATTN_BN;
+          lim = min(ATTN_BN - 1, qpos0 + row - kpos0);
+        }
+        mbar_wait(&s_full[gi & 1u], (gi >> 1) & 1u, abort_word, p.timeout_ns);
+        tc_fence_after();
+        // pass 1: row maximum
+        float mx = -INFINITY;
+#pragma unroll 1
+        for (int c = 0; c < ATTN_BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(s_tmem + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float s = __uint_as_float(r[i]);
+            if (c * 32 + i <= lim) mx = fmaxf(mx, s);
+          }
+        }
+        const float m_new = fmaxf(m, mx * p.scale_log2);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        const float alpha = exp2f(m - m_use);  // 0 when nothing was accumulated yet
+        // pass 2: probabilities, written over S as 16-bit pairs
+        float l_part = 0.f;
+#pragma unroll 1
+        for (int c = 0; c < ATTN_BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(s_tmem + c * 32, r);
+          tmem_ld_wait();
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            float p0 = exp2f(__uint_as_float(r[2 * i]) * p.scale_log2 - m_use);
+            float p1 = exp2f(__uint_as_float(r[2 * i + 1]) * p.scale_log2 - m_use);
+            if (c * 32 + 2 * i > lim) p0 = 0.f;
+            if (c * 32 + 2 * i + 1 > lim) p1 = 0.f;
+            l_part += p0 + p1;
+            pk[i] = pack2(p0, p1, p.dtype);
+          }
+          tmem_st_32x16(s_tmem + c * 16, pk);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(&p_full[gi & 1u]);
+        // fold in the partial O of the previous block (computed relative to the old maximum)
+        if (j > 0) {
+          const uint32_t gp = gi - 1;
+          mbar_wait(&o_full[gp & 1u], (gp >> 1) & 1u, abort_word, p.timeout_ns);
+          tc_fence_after();
+          const uint32_t o_tmem = lane_base + 256u + (gp & 1u) * 128u;
+#pragma unroll
+          for (int c = 0; c < ATTN_D / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld_32x32(o_tmem + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] += __uint_as_float(r[i]);
+          }
+          tc_fence_before();
+          mbar_arrive(&o_empty[gp & 1u]);
+        }
+#pragma unroll
+        for (int i = 0; i < ATTN_D; ++i) o_acc[i] *= alpha;
+        l = l * alpha + l_part;
+        m = m_new;
+        ++j;
+      }
+      {
+        const uint32_t gp = g + active - 1;
+        mbar_wait(&o_full[gp & 1u], (gp >> 1) & 1u, abort_word, p.timeout_ns);
+        tc_fence_after();
+        const uint32_t o_tmem = lane_base + 256u + (gp & 1u) * 128u;
+#pragma unroll
+        for (int c = 0; c < ATTN_D / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(o_tmem + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] += __uint_as_float(r[i]);
+        }
+        tc_fence_before();
+        mbar_arrive(&o_empty[gp & 1u]);
+      }
+      g += active;
+
+      // ---- finalise this visit and merge with what earlier waves left for the row
+      const int srow = qt * ATTN_BM + row;
+      if (srow < p.Sq) {
+        const size_t stat_idx = (static_cast<size_t>(z) * p.Hq + h) * p.Sq + srow;
+        uint4* o_ptr = reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.o) +
+                                                (z * p.o_sz + h * p.o_sh + static_cast<int64_t>(srow) * p.o_ss) * 2);
+        const bool seen = p.visit[stat_idx] == p.epoch;
+        float lse_new = (l > 0.f) ? m + log2f(l) : -INFINITY;
+        const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
+        float w_new = inv_l, w_old = 0.f;
+        if (seen) {
+          const float lse_old = p.lse[stat_idx];
+          const float mm = fmaxf(lse_old, lse_new);
+          if (mm == -INFINITY) {
+            w_new = 0.f;
+            w_old = 1.f;
+          } else {
+            const float e_old = exp2f(lse_old - mm), e_new = exp2f(lse_new - mm);
+            const float tot = e_old + e_new;
+            w_old = e_old / tot;
+            w_new = e_new / tot * inv_l;
+            lse_new = mm + log2f(tot);
+          }
+        }
+#pragma unroll
+        for (int v = 0; v < ATTN_D / 8; ++v) {
+          float f[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) f[i] = o_acc[v * 8 + i] * w_new;
+          if (seen) {
+            const uint4 old = o_ptr[v];
+            const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float2 t = unpack2(ow[i], p.dtype);
+              f[2 * i] += t.x * w_old;
+              f[2 * i + 1] += t.y * w_old;
+            }
+          }
+          uint4 out;
+          out.x = pack2(f[0], f[1], p.dtype);
+          out.y = pack2(f[2], f[3], p.dtype);
+          out.z = pack2(f[4], f[5], p.dtype);
+          out.w = pack2(f[6], f[7], p.dtype);
+          o_ptr[v] = out;
+        }
+        p.lse[stat_idx] = lse_new;
+        p.visit[stat_idx] = p.epoch;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+  if (threadIdx.x == 0 && *abort_word != 0 && p.status != nullptr) {
+    if (atomicCAS(p.status, 0, *abort_word) == 0) {
+      p.status[1] = abort_info[0];
+      p.status[2] = abort_info[1];
+      p.status[3] = static_cast<int>(blockIdx.x);
+    }
+  }
+}
+
+}  // namespace syn

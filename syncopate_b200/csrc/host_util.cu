@@ -90,6 +90,29 @@ int encode_tmap_3d_sw128(CUtensorMap* out, const void* base, uint64_t d2, uint64
   return SYN_OK;
 }
 
+int encode_tmap_4d_sw128(CUtensorMap* out, const void* base, uint64_t d3, uint64_t d2, uint64_t rows, uint64_t cols,
+                         uint64_t s3, uint64_t s2, uint64_t ld, uint32_t box_rows, uint32_t box_cols) {
+  encode_tiled_fn fn = get_encode_tiled();
+  if (fn == nullptr) {
+    set_cuda_error("cudaGetDriverEntryPoint(cuTensorMapEncodeTiled)", "not available");
+    return SYN_ERR_CUDA;
+  }
+  cuuint64_t gdim[4] = {cols, rows, d2, d3};
+  cuuint64_t gstride[3] = {ld * 2, s2 * 2, s3 * 2};
+  cuuint32_t box[4] = {box_cols, box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), gdim, gstride, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char buf[64];
+    snprintf(buf, sizeof(buf), "CUresult %d", static_cast<int>(r));
+    set_cuda_error("cuTensorMapEncodeTiled(4d)", buf);
+    return SYN_ERR_CUDA;
+  }
+  return SYN_OK;
+}
+
 int status_to_err(int dev_code) {
   switch (dev_code) {
     case 0: return SYN_OK;

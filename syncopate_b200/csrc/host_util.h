@@ -31,6 +31,10 @@ int encode_tmap_2d_sw128(CUtensorMap* out, const void* base, uint64_t rows, uint
 int encode_tmap_3d_sw128(CUtensorMap* out, const void* base, uint64_t d2, uint64_t rows, uint64_t cols,
                          uint64_t stride2, uint64_t ld, uint32_t box_rows, uint32_t box_cols);
 
+// 4-D 16-bit tensor [d3, d2, rows, cols] with element strides (s3, s2, ld, 1); box = [1, 1, box_rows, box_cols].
+int encode_tmap_4d_sw128(CUtensorMap* out, const void* base, uint64_t d3, uint64_t d2, uint64_t rows, uint64_t cols,
+                         uint64_t s3, uint64_t s2, uint64_t ld, uint32_t box_rows, uint32_t box_cols);
+
 // Maps a device status code (ptx.cuh) to the negative C-ABI code.
 int status_to_err(int dev_code);
 
