@@ -280,6 +280,12 @@ typedef struct syn_attn_comm {
   uint32_t* counters;      /* device uint32[SYN_MAX_COMM_OPS], zero before the first call */
 } syn_attn_comm;
 
+/* Stand-alone SM copy: executes `comm->ops` in order on `num_sms` CTAs (0 = all) and raises each
+ * op's flag when it has landed; pushes (dst on a peer) and pulls alike.  Replaces the reference's
+ * persistent copy kernels for SMCopyOp records (comm_runtime/tma_persistent_copy.py:114-171). */
+int syn_copy(const syn_attn_comm* comm, int num_sms, uint64_t signal_value, uint64_t timeout_ns, int32_t* status,
+             void* stream);
+
 /* `comm` may be NULL (data already in place; flags, if any, raised by somebody else). */
 int syn_attention(const syn_attn_args* args, const syn_schedule* sched, const syn_attn_comm* comm, void* stream);
 

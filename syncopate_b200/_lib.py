@@ -236,6 +236,8 @@ def _declare(l: C.CDLL) -> None:
     l.syn_flag_wait.argtypes = [C.c_void_p, C.c_uint64, C.c_uint64, C.c_void_p, C.c_int, C.c_void_p]
     l.syn_ag_gemm.restype = C.c_int
     l.syn_ag_gemm.argtypes = [C.POINTER(AgGemmArgs), C.POINTER(Schedule), C.c_void_p]
+    l.syn_copy.restype = C.c_int
+    l.syn_copy.argtypes = [C.POINTER(AttnComm), C.c_int, C.c_uint64, C.c_uint64, C.c_void_p, C.c_void_p]
     l.syn_attention.restype = C.c_int
     l.syn_attention.argtypes = [C.POINTER(AttnArgs), C.POINTER(Schedule), C.POINTER(AttnComm), C.c_void_p]
     l.syn_gemm_rs.restype = C.c_int
@@ -293,3 +295,18 @@ def make_schedule(offsets, shapes, signals=None, target_ranks=None, dst_offsets=
         keep.append(arr)
         setattr(s, name, ptr)
     return s, keep
+
+
+def make_attn_comm(ops, bufs, flags, counters_ptr):
+    """``syn_attn_comm`` from a list of CopyOp, a list of Symm buffer tables, the flag table and the
+    device pointer of the counters.  Returns ``(struct, keepalive)``."""
+    arr = (CopyOp * max(len(ops), 1))(*ops)
+    c = AttnComm()
+    c.num_ops = len(ops)
+    c.ops = C.cast(arr, C.POINTER(CopyOp))
+    c.num_bufs = len(bufs)
+    for i, b in enumerate(bufs):
+        c.bufs[i] = b
+    c.flags = flags
+    c.counters = counters_ptr
+    return c, arr

@@ -163,3 +163,190 @@ class GemmReduceScatter:
         return gemm_rs(a, b, out, self.src_schedule, self.dst_schedule, self.remote_signals, self.stage.symm,
                        self.flags.symm, self.counters, epoch=self.epoch, num_sms=self.num_sms,
                        block_n=self.block_n, timeout_ns=self.timeout_ns, status=self.ctx.status, stream=stream)
+
+
+# ----------------------------------------------------------------------------------------------
+# attention operators
+# ----------------------------------------------------------------------------------------------
+import ctypes as _C
+
+from . import _lib as _L
+from .communication.common_descriptors import (
+    build_all_to_all_plan_dim,
+    build_double_ring_all_gather_plan,
+)
+from .computation.attn import AttentionState, attention_forward
+from .computation.attn.plan import (
+    all_gather_wave_metadata,
+    all_to_all_wave_metadata,
+    completion_signals,
+    pull_ops_from_schedule,
+    push_ops_from_schedule,
+    zigzag_tables,
+)
+
+
+def _plan(plans):
+    gen = CommGenerator(plans)
+    gen.plan_signals(plan_compute_signals=True)
+    info = gen.generate_code_for_plan(CodeGenOptions(copy_engine=False))
+    return gen, info, lower_comm_plan_to_raw_schedules(gen)
+
+
+def _local_table(ctx, t: torch.Tensor) -> "_L.Symm":
+    """Buffer table for a buffer only this rank touches (every slot holds the local address)."""
+    return _L.Symm.of(ctx.rank, [t.data_ptr()] * ctx.world)
+
+
+class UlyssesAttention:
+    """Sequence-parallel attention, Ulysses style: all-to-all (sequence-sharded -> head-sharded),
+    causal flash attention over the full sequence for this rank's heads, all-to-all back.
+
+    Per rank: ``qkv`` ``[3, B, H, S / world, D]`` in, ``[B, S / world, H, D]`` out.  The inbound
+    all-to-all runs inside the attention kernel (comm warps pull the slabs in the plan's order, the
+    tiles follow the triangular (Q slab, KV slab) order of the reference driver,
+    tests/test_all2all_attn_transform.py:58-117); the outbound one is an SM copy kernel launched
+    behind it (tests/test_attn_all2all_transform.py is the reference's overlapped form)."""
+
+    def __init__(self, ctx, B: int, H: int, S_local: int, D: int = 128, dtype=torch.bfloat16, causal: bool = True,
+                 sm_scale: Optional[float] = None, timeout_ns: int = 0):
+        self.ctx, self.world, self.rank = ctx, ctx.world, ctx.rank
+        W = self.world
+        self.B, self.H, self.S_local, self.D, self.dtype, self.causal = B, H, S_local, D, dtype, causal
+        self.sm_scale = sm_scale if sm_scale is not None else D ** -0.5
+        self.timeout_ns = timeout_ns
+        self.S, self.Hl = S_local * W, H // W
+        es = dtype.itemsize
+        # ---- inbound plan: [3, B, H, S/W, D] -> [3, B, H/W, S, D]
+        self.in_src_shape = (3, B, H, S_local, D)
+        self.in_dst_shape = (3, B, self.Hl, self.S, D)
+        _g, self.in_info, low = _plan({
+            r: build_all_to_all_plan_dim(self.in_src_shape, dtype=dtype, mesh_size=W, rank=r, src_buffer="src",
+                                         dst_buffer="dst", src_split_axis=3, dst_split_axis=2, transfer_kind="pull")
+            for r in range(W)})
+        self.in_schedule = low[self.rank]["dst"]
+        self.qkv_src = ctx.alloc(self.in_src_shape, dtype)       # peers read it
+        self.in_flags = ctx.alloc((max(self.in_info.recv_signal_num, 1),), torch.int64)
+        self.qkv_dst = torch.zeros(self.in_dst_shape, dtype=dtype, device=ctx.device)
+        self.waves = all_to_all_wave_metadata(self.in_schedule, {"batch": 1, "head": 2, "seq": 3})
+        self.in_ops = pull_ops_from_schedule(self.in_schedule, self.rank, W, self.in_src_shape, self.in_dst_shape, es,
+                                             src_buf=0, dst_buf=1)
+        self.counters = torch.zeros(NUM_COUNTERS, dtype=torch.int32, device=ctx.device)
+        self.in_comm, self._keep_in = _L.make_attn_comm(
+            self.in_ops, [self.qkv_src.symm, _local_table(ctx, self.qkv_dst)], self.in_flags.symm,
+            self.counters.data_ptr())
+        # ---- attention output in [B, S, H/W, D], read by the kernel as [B, H/W, S, D]
+        self.attn_out = torch.zeros(B, self.S, self.Hl, D, dtype=dtype, device=ctx.device)
+        self.state = AttentionState(B, self.Hl, self.S, ctx.device)
+        # ---- outbound plan: [B, S, H/W, D] -> [B, S/W, H, D]
+        self.out_src_shape = (B, self.S, self.Hl, D)
+        self.out_dst_shape = (B, S_local, H, D)
+        _g2, self.out_info, low2 = _plan({
+            r: build_all_to_all_plan_dim(self.out_src_shape, dtype=dtype, mesh_size=W, rank=r, src_buffer="src",
+                                         dst_buffer="dst", src_split_axis=2, dst_split_axis=1, transfer_kind="push",
+                                         compute_producer=True)
+            for r in range(W)})
+        self.out_schedule = low2[self.rank]["src"]
+        self.out = ctx.alloc(self.out_dst_shape, dtype)           # peers write it
+        self.out_flags = ctx.alloc((max(self.out_info.recv_signal_num, 1),), torch.int64)
+        self.out_counters = torch.zeros(NUM_COUNTERS, dtype=torch.int32, device=ctx.device)
+        sig = completion_signals(self.out_info, self.rank, self.out_schedule)
+        self.out_ops = push_ops_from_schedule(self.out_schedule, self.rank, self.out_src_shape, self.out_dst_shape, es,
+                                              src_buf=0, dst_buf=1, remote_signals=sig)
+        self.out_comm, self._keep_out = _L.make_attn_comm(
+            self.out_ops, [_local_table(ctx, self.attn_out), self.out.symm], self.out_flags.symm,
+            self.out_counters.data_ptr())
+        self.epoch = 0
+
+    def launch_attention(self, stream=None):
+        """Inbound all-to-all fused with attention; fills ``attn_out``."""
+        self.epoch += 1
+        offs, sizes, sigs, _cum = self.waves
+        q, k, v = self.qkv_dst[0], self.qkv_dst[1], self.qkv_dst[2]
+        attention_forward(q, k, v, self.sm_scale, self.attn_out.permute(0, 2, 1, 3), wave_offsets=offs,
+                          wave_sizes=sizes, signal_ptr=self.in_flags.local, signal_offsets=sigs, causal=self.causal,
+                          state=self.state, signal_value=self.epoch, comm=self.in_comm, timeout_ns=self.timeout_ns,
+                          status=self.ctx.status, stream=stream)
+
+    def launch_scatter(self, stream=None):
+        """Outbound all-to-all: pushes ``attn_out`` slabs to their ranks and raises their flags."""
+        s = (stream or torch.cuda.current_stream()).cuda_stream or None
+        _L.check(_L.lib().syn_copy(_C.byref(self.out_comm), 0, self.epoch, self.timeout_ns,
+                                   self.ctx.status.data_ptr(), s), "syn_copy")
+
+    def wait_output(self, stream=None):
+        """Stream-ordered wait until every rank's slab has landed in ``out``."""
+        s = (stream or torch.cuda.current_stream()).cuda_stream or None
+        for i in range(self.out_info.recv_signal_num):
+            _L.check(_L.lib().syn_flag_wait(self.out_flags.local.data_ptr() + 8 * i, self.epoch, self.timeout_ns,
+                                            self.ctx.status.data_ptr(), i, s), "syn_flag_wait")
+
+    def __call__(self, stream=None) -> torch.Tensor:
+        self.launch_attention(stream)
+        self.launch_scatter(stream)
+        self.wait_output(stream)
+        return self.out.local
+
+
+class ContextParallelAttention:
+    """Context-parallel attention: queries stay local, K/V chunks are all-gathered by the kernel's
+    comm warps in the order of the plan (swizzled direct, ring or double ring; on an all-to-all
+    fabric every chunk is fetched from its owner), and the flash-attention tiles consume chunk
+    after chunk (tests/test_allgather_attn_transform.py, test_ring_allgather_attn_transform.py,
+    test_double_ring_ag_attn.py in the reference).  Causal masking uses true token positions, so the
+    zigzag placement (rank r holds chunks r and 2 * world - 1 - r) balances the work."""
+
+    def __init__(self, ctx, B: int, Hq: int, Hkv: int, S_local: int, D: int = 128, dtype=torch.bfloat16,
+                 causal: bool = True, zigzag: bool = True, plan: str = "swizzle", inner_mesh_size: int = 2,
+                 sm_scale: Optional[float] = None, timeout_ns: int = 0):
+        self.ctx, self.world, self.rank = ctx, ctx.world, ctx.rank
+        W = self.world
+        self.B, self.Hq, self.Hkv, self.S_local, self.D = B, Hq, Hkv, S_local, D
+        self.dtype, self.causal, self.timeout_ns = dtype, causal, timeout_ns
+        self.sm_scale = sm_scale if sm_scale is not None else D ** -0.5
+        self.S = S_local * W
+        self.kv_shape = (2, B, Hkv, self.S, D)
+        if plan == "swizzle":
+            plans = {r: build_all_gather_plan_1d_swizzle(self.kv_shape, dtype, 3, W, r, "kv", "pull") for r in range(W)}
+        elif plan == "ring":
+            plans = {r: build_ring_all_gather_plan(self.kv_shape, dtype, 3, W, r, "kv") for r in range(W)}
+        elif plan == "double_ring":
+            plans = {r: build_double_ring_all_gather_plan(self.kv_shape, dtype, 3, W, inner_mesh_size, r, "kv")
+                     for r in range(W)}
+        else:
+            raise ValueError("plan must be 'swizzle', 'ring' or 'double_ring'")
+        _g, self.info, low = _plan(plans)
+        self.schedule = low[self.rank]["kv"]
+        self.kv = ctx.alloc(self.kv_shape, dtype)
+        self.flags = ctx.alloc((max(self.info.recv_signal_num, 1),), torch.int64)
+        self.counters = torch.zeros(NUM_COUNTERS, dtype=torch.int32, device=ctx.device)
+        self.waves = all_gather_wave_metadata(self.schedule, S_local, {"batch": 1, "head": 2, "seq": 3}, q_heads=Hq)
+        self.ops = pull_ops_from_schedule(self.schedule, self.rank, W, self.kv_shape, self.kv_shape, dtype.itemsize,
+                                          src_buf=0, dst_buf=0, gather_axis=3)
+        self.comm, self._keep = _L.make_attn_comm(self.ops, [self.kv.symm], self.flags.symm, self.counters.data_ptr())
+        self.q_pos = self.kv_pos = None
+        if causal and zigzag:
+            qp, kp = zigzag_tables(W, self.rank, self.S)
+            self.q_pos = torch.tensor(qp, dtype=torch.int32, device=ctx.device)
+            self.kv_pos = torch.tensor(kp, dtype=torch.int32, device=ctx.device)
+        elif causal:
+            self.q_pos = torch.arange(self.rank * S_local, (self.rank + 1) * S_local, 128, dtype=torch.int32,
+                                      device=ctx.device)
+        self.state = AttentionState(B, Hq, S_local, ctx.device)
+        self.epoch = 0
+
+    @property
+    def kv_shard(self) -> torch.Tensor:
+        """This rank's slab ``[2, B, Hkv, S / world, D]`` of the gathered K/V buffer."""
+        return self.kv.local[:, :, :, self.rank * self.S_local : (self.rank + 1) * self.S_local]
+
+    def __call__(self, q: torch.Tensor, out: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+        if out is None:
+            out = torch.empty_like(q)
+        self.epoch += 1
+        offs, sizes, sigs, _cum = self.waves
+        comm = self.comm if self.ops else None
+        return attention_forward(q, self.kv.local[0], self.kv.local[1], self.sm_scale, out, wave_offsets=offs,
+                                 wave_sizes=sizes, signal_ptr=self.flags.local, signal_offsets=sigs, causal=self.causal,
+                                 q_pos=self.q_pos, kv_pos=self.kv_pos, state=self.state, signal_value=self.epoch,
+                                 comm=comm, timeout_ns=self.timeout_ns, status=self.ctx.status, stream=stream)

@@ -110,6 +110,58 @@ class SymmetricContext:
             pass
 
 
+class EmulatedWorld:
+    """All ranks of a plan inside one process on one GPU: every "symmetric" allocation is a set of
+    ``world`` ordinary device tensors and each rank's table holds their addresses.  For one-GPU
+    tests of the fused kernels (a rank's launch may only depend on data and flags that earlier
+    launches left behind, never on a kernel that has not run yet)."""
+
+    def __init__(self, world: int, device: Optional[int] = None):
+        self.world = world
+        self.device_index = torch.cuda.current_device() if device is None else device
+        self.device = torch.device("cuda", self.device_index)
+        self._allocs: List[List[torch.Tensor]] = []
+        self.contexts = [EmulatedContext(self, r) for r in range(world)]
+
+    def _get(self, index: int, shape, dtype) -> List[torch.Tensor]:
+        if index == len(self._allocs):
+            self._allocs.append([torch.zeros(*shape, dtype=dtype, device=self.device) for _ in range(self.world)])
+        group = self._allocs[index]
+        if tuple(group[0].shape) != tuple(shape) or group[0].dtype != dtype:
+            raise RuntimeError("ranks of an emulated world must allocate the same sequence of buffers")
+        return group
+
+
+class EmulatedContext:
+    """One rank of an :class:`EmulatedWorld`; same surface as :class:`SymmetricContext`."""
+
+    def __init__(self, world: EmulatedWorld, rank: int):
+        self._world = world
+        self.rank, self.world = rank, world.world
+        self.device_index, self.device = world.device_index, world.device
+        self._next = 0
+        self.status = torch.zeros(4, dtype=torch.int32, device=self.device)
+
+    def alloc(self, shape, dtype: torch.dtype, timeout_s: int = 0) -> SymmetricTensor:
+        group = self._world._get(self._next, tuple(int(s) for s in shape), dtype)
+        self._next += 1
+        return SymmetricTensor(L.Symm.of(self.rank, [t.data_ptr() for t in group]), shape, dtype, self.device)
+
+    def barrier(self, stream=None, timeout_ns: int = 0) -> None:
+        torch.cuda.synchronize()
+
+    def check(self, stream=None) -> None:
+        torch.cuda.synchronize()
+        words = self.status.tolist()
+        if words[0] != 0:
+            self.status.zero_()
+            code = {1: -4, 2: -5, 3: -6}.get(words[0], -1)
+            raise L.SynError(code, "device status", f"wave={words[1]} flag={words[2]} block={words[3]}")
+
+    def close(self) -> None:
+        pass
+
+
 def init_from_env(backend: Optional[str] = None) -> Tuple[int, int, SymmetricContext]:
     """Launcher glue for ``torchrun`` (replaces utils/launch.sh + ``initialize_distributed``): reads
     RANK / LOCAL_RANK / WORLD_SIZE, binds the GPU, initialises ``torch.distributed`` when more than
