@@ -11,7 +11,12 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
 
-from syncopate_b200.operators import AllGatherGemm, GemmReduceScatter  # noqa: E402
+from syncopate_b200.operators import (  # noqa: E402
+    AllGatherGemm,
+    ContextParallelAttention,
+    GemmReduceScatter,
+    UlyssesAttention,
+)
 from syncopate_b200.runtime import init_from_env  # noqa: E402
 
 TOL = 1e-2
@@ -68,6 +73,65 @@ def main():
             e = rel(out, ref)
             if not e < TOL:
                 failures.append(f"gemm_rs {kind} M={M} it={it} rank={rank}: relerr={e:.3e}")
+
+    # ---- attention operators (reference: gather with torch.distributed, dense fp32 attention per head)
+    def dense(q, k, v, causal, q_pos=None, k_pos=None):
+        Hq, Hkv = q.shape[0], k.shape[0]
+        out = torch.empty(q.shape, dtype=torch.float32, device=q.device)
+        for h in range(Hq):
+            s = (q[h].float() @ k[h // (Hq // Hkv)].float().t()) * (q.shape[-1] ** -0.5)
+            if causal:
+                qp = torch.arange(q.shape[1], device=q.device) if q_pos is None else q_pos
+                kp = torch.arange(k.shape[1], device=q.device) if k_pos is None else k_pos
+                s = s.masked_fill(kp[None, :] > qp[:, None], float("-inf"))
+            out[h] = torch.nan_to_num(torch.softmax(s, -1)) @ v[h // (Hq // Hkv)].float()
+        return out
+
+    B, H, Sl = 1, 2 * world, 256
+    op = UlyssesAttention(ctx, B, H, Sl, 128, dt, causal=True, timeout_ns=2_000_000_000)
+    qkv = seeded(7000 + rank, (3, B, H, Sl, 128), 1.0, dt, dev)
+    gathered = [torch.empty_like(qkv) for _ in range(world)]
+    dist.all_gather(gathered, qkv)
+    full = torch.cat(gathered, dim=3)  # [3, B, H, S, D]
+    for it in range(2):
+        op.qkv_src.local.copy_(qkv)
+        torch.cuda.synchronize()
+        ctx.barrier()
+        out = op()
+        ctx.check()
+        ref = dense(full[0, 0], full[1, 0], full[2, 0], True)[:, rank * Sl : (rank + 1) * Sl].permute(1, 0, 2)
+        e = (out[0].float() - ref).abs().max().item()
+        if not e < 2e-2:
+            failures.append(f"ulysses it={it} rank={rank}: maxabs={e:.3e}")
+        ctx.barrier()
+        torch.cuda.synchronize()
+
+    for plan in ("swizzle", "ring", "double_ring"):
+        Hq, Hkv = 8, 2
+        op = ContextParallelAttention(ctx, 1, Hq, Hkv, Sl, 128, dt, causal=True, zigzag=True, plan=plan,
+                                      timeout_ns=2_000_000_000)
+        kv = seeded(8000 + rank, (2, 1, Hkv, Sl, 128), 1.0, dt, dev)
+        q = seeded(9000 + rank, (1, Hq, Sl, 128), 1.0, dt, dev)
+        gathered = [torch.empty_like(kv) for _ in range(world)]
+        dist.all_gather(gathered, kv)
+        full = torch.cat(gathered, dim=3)
+        steps = torch.arange(128, device=dev)
+        q_pos = (op.q_pos[:, None] + steps[None, :]).reshape(-1)
+        k_pos = (op.kv_pos[:, None] + steps[None, :]).reshape(-1)
+        ref = dense(q[0], full[0, 0], full[1, 0], True, q_pos, k_pos)
+        for it in range(2):
+            op.kv.local.fill_(float("nan"))
+            op.kv_shard.copy_(kv)
+            torch.cuda.synchronize()
+            ctx.barrier()
+            out = op(q)
+            ctx.check()
+            e = (out[0].float() - ref).abs().max().item()
+            same = torch.equal(op.kv.local, full)
+            if not (e < 2e-2 and same):
+                failures.append(f"cp {plan} it={it} rank={rank}: maxabs={e:.3e} gathered_ok={same}")
+            ctx.barrier()
+            torch.cuda.synchronize()
 
     torch.cuda.synchronize()
     flag = torch.tensor([len(failures)], device=dev)

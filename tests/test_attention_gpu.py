@@ -1,0 +1,172 @@
+"""GPU parity of the attention kernel and of the two attention operators against the CPU oracle
+(fp32 dense attention of the same seeded inputs).  Tolerance: max-abs error <= 2e-2 on bf16
+outputs of O(1) magnitude (the bound the operators are specified to); ~8e-3 is what 16-bit P and
+output rounding give."""
+import os
+import sys
+
+import pytest
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from oracle import emulate as E  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-2
+DT = torch.bfloat16
+
+
+def _seeded(seed, shape):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(*shape, generator=g, dtype=torch.float32).to(DT)
+
+
+def _dense(q, k, v, causal, q_pos=None, k_pos=None):
+    """Oracle for [Z, H, S, D] tensors."""
+    return torch.stack([E.attention_dense(q[z], k[z], v[z], q.shape[-1] ** -0.5, q_pos, k_pos, causal)[0]
+                        for z in range(q.shape[0])])
+
+
+@pytest.mark.parametrize(
+    "Z,Hq,Hkv,Sq,Skv,causal",
+    [
+        (1, 1, 1, 128, 128, False),
+        (1, 2, 2, 256, 512, False),
+        (1, 2, 2, 512, 512, True),
+        (2, 8, 2, 384, 640, False),   # grouped-query heads, sizes that are not powers of two
+        (1, 4, 1, 256, 256, True),
+    ],
+)
+def test_attention_matches_oracle(Z, Hq, Hkv, Sq, Skv, causal):
+    from syncopate_b200.computation.attn import attention_forward
+
+    q, k, v = _seeded(1, (Z, Hq, Sq, 128)), _seeded(2, (Z, Hkv, Skv, 128)), _seeded(3, (Z, Hkv, Skv, 128))
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    o = attention_forward(q.cuda(), k.cuda(), v.cuda(), 128 ** -0.5, causal=causal, status=status,
+                          timeout_ns=300_000_000)
+    torch.cuda.synchronize()
+    assert status.tolist() == [0, 0, 0, 0]
+    assert (o.float().cpu() - _dense(q, k, v, causal)).abs().max().item() < TOL
+
+
+def test_waves_merge_partial_results_and_lse():
+    """Four (Q half, KV half) waves in a scrambled order: rows visited twice are merged; the stored
+    LSE (log2 domain) matches the oracle's natural-log LSE."""
+    from syncopate_b200.computation.attn import AttentionState, attention_forward
+
+    Z, H, S = 1, 4, 1024
+    q, k, v = _seeded(4, (Z, H, S, 128)), _seeded(5, (Z, H, S, 128)), _seeded(6, (Z, H, S, 128))
+    offs = [[0, 0, 512, 512], [0, 0, 0, 0], [0, 0, 512, 0], [0, 0, 0, 512]]
+    sizes = [[1, 4, 512, 512]] * 4
+    st = AttentionState(Z, H, S, "cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    for causal in (False, True):
+        o = attention_forward(q.cuda(), k.cuda(), v.cuda(), 128 ** -0.5, wave_offsets=offs, wave_sizes=sizes,
+                              causal=causal, state=st, status=status, timeout_ns=300_000_000)
+        torch.cuda.synchronize()
+        assert status.tolist() == [0, 0, 0, 0]
+        want, lse = E.attention_dense(q[0], k[0], v[0], 128 ** -0.5, causal=causal)
+        assert (o[0].float().cpu() - want).abs().max().item() < TOL
+        assert torch.allclose(st.lse[0].cpu() * 0.6931471805599453, lse, atol=2e-3, rtol=1e-4)
+
+
+def test_strided_layouts_and_output_buffer():
+    """BSHD inputs (head stride < sequence stride) and a caller-provided BSHD output."""
+    from syncopate_b200.computation.attn import attention_forward
+
+    B, S, H = 2, 256, 3
+    qkv = _seeded(7, (3, B, S, H, 128)).cuda()
+    out = torch.zeros(B, S, H, 128, dtype=DT, device="cuda")
+    q, k, v = (qkv[i].permute(0, 2, 1, 3) for i in range(3))
+    res = attention_forward(q, k, v, 128 ** -0.5, out.permute(0, 2, 1, 3), causal=True, timeout_ns=300_000_000)
+    torch.cuda.synchronize()
+    assert res.data_ptr() == out.data_ptr()
+    want = _dense(q.cpu(), k.cpu(), v.cpu(), True)
+    assert (out.permute(0, 2, 1, 3).float().cpu() - want).abs().max().item() < TOL
+
+
+def test_flag_gated_wave_times_out_cleanly():
+    from syncopate_b200.computation.attn import attention_forward
+
+    q = torch.zeros(1, 1, 128, 128, dtype=DT, device="cuda")
+    flags = torch.zeros(1, dtype=torch.int64, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    attention_forward(q, q, q, 1.0, wave_offsets=[[0, 0, 0, 0]], wave_sizes=[[1, 1, 128, 128]], signal_ptr=flags,
+                      signal_offsets=[0], status=status, timeout_ns=1_000_000)
+    torch.cuda.synchronize()
+    assert status.tolist()[:3] == [1, 0, 0]   # flag timeout on wave 0 / flag 0, nothing hung
+
+
+def test_rejects_unsupported_shapes():
+    from syncopate_b200 import _lib as L
+    from syncopate_b200.computation.attn import attention_forward
+
+    q = torch.zeros(1, 1, 128, 64, dtype=DT, device="cuda")
+    with pytest.raises(L.SynError, match="SYN_ERR_UNSUPPORTED"):
+        attention_forward(q, q, q, 1.0)
+    q = torch.zeros(1, 1, 256, 128, dtype=DT, device="cuda")
+    with pytest.raises(L.SynError, match="SYN_ERR_SHAPE"):
+        attention_forward(q, q, q, 1.0, wave_offsets=[[0, 0, 64, 0]], wave_sizes=[[1, 1, 128, 256]])
+
+
+@pytest.mark.parametrize("world,B,H,S_local,causal", [(2, 1, 4, 256, True), (4, 2, 4, 128, False)])
+def test_ulysses_operator_emulated_ranks(world, B, H, S_local, causal):
+    """All ranks on one GPU: inbound all-to-all inside the attention kernel, outbound by the SM
+    copy kernel; every rank's [B, S/W, H, D] result equals dense attention over the full sequence."""
+    from syncopate_b200.operators import UlyssesAttention
+    from syncopate_b200.runtime import EmulatedWorld
+
+    ew = EmulatedWorld(world)
+    ops = [UlyssesAttention(c, B, H, S_local, 128, DT, causal=causal, timeout_ns=500_000_000) for c in ew.contexts]
+    qkv = [_seeded(20 + r, (3, B, H, S_local, 128)) for r in range(world)]
+    for r in range(world):
+        ops[r].qkv_src.local.copy_(qkv[r].cuda())
+    full = torch.cat(qkv, dim=3)
+    want = torch.stack([E.attention_dense(full[0, b], full[1, b], full[2, b], 128 ** -0.5, causal=causal)[0]
+                        for b in range(B)])  # [B, H, S, D]
+    for _it in range(2):
+        for op in ops:
+            op.launch_attention()
+        torch.cuda.synchronize()
+        for op in ops:
+            op.launch_scatter()
+        torch.cuda.synchronize()
+        for r, op in enumerate(ops):
+            op.wait_output()
+            op.ctx.check()
+            # the gathered Q/K/V of this rank's heads are bit-exact copies
+            heads = slice(r * (H // world), (r + 1) * (H // world))
+            assert torch.equal(op.qkv_dst.cpu(), full[:, :, heads])
+            got = op.out.local.float().cpu()  # [B, S/W, H, D]
+            ref = want[:, :, r * S_local : (r + 1) * S_local].permute(0, 2, 1, 3)
+            assert (got - ref).abs().max().item() < TOL
+            op.out.local.zero_()
+
+
+@pytest.mark.parametrize("world,Hq,Hkv,plan,zigzag", [(2, 4, 2, "swizzle", True), (4, 8, 2, "ring", True),
+                                                       (4, 4, 4, "double_ring", False)])
+def test_context_parallel_operator_emulated_ranks(world, Hq, Hkv, plan, zigzag):
+    from syncopate_b200.operators import ContextParallelAttention
+    from syncopate_b200.runtime import EmulatedWorld
+
+    B, S_local = 1, 256
+    ew = EmulatedWorld(world)
+    ops = [ContextParallelAttention(c, B, Hq, Hkv, S_local, 128, DT, causal=True, zigzag=zigzag, plan=plan,
+                                    timeout_ns=500_000_000) for c in ew.contexts]
+    kv = [_seeded(40 + r, (2, B, Hkv, S_local, 128)) for r in range(world)]
+    q = [_seeded(60 + r, (B, Hq, S_local, 128)) for r in range(world)]
+    full = torch.cat(kv, dim=3)
+    steps = torch.arange(128)
+    for _it in range(2):
+        for r, op in enumerate(ops):
+            op.kv.local.fill_(float("nan"))
+            op.kv_shard.copy_(kv[r].cuda())
+        outs = [op(q[r].cuda()) for r, op in enumerate(ops)]
+        torch.cuda.synchronize()
+        for r, op in enumerate(ops):
+            op.ctx.check()
+            assert torch.equal(op.kv.local.cpu(), full)   # gathered K/V: bit-exact
+            q_pos = (op.q_pos.cpu()[:, None] + steps[None, :]).reshape(-1)
+            k_pos = (op.kv_pos.cpu()[:, None] + steps[None, :]).reshape(-1) if op.kv_pos is not None else None
+            want = _dense(q[r], full[0], full[1], True, q_pos, k_pos)
+            assert (outs[r].float().cpu() - want).abs().max().item() < TOL
