@@ -315,6 +315,72 @@ def run_own_arm(args):
     rs_flop = 2.0 * RS_M * RS_N * rs_k
     rs_per_gpu = rs_flop / (rs_ms * 1e-3) / 1e12
 
+    # ---------------- attention operators at the benchmark shapes (reported, not the headline)
+    attn_results = {}
+    if not args.skip_attention:
+        from syncopate_b200.operators import ContextParallelAttention, UlyssesAttention
+        from syncopate_b200.runtime import EmulatedWorld
+
+        def time_op(fn, steps):
+            for _ in range(2):
+                fn()
+            sync_all()
+            e0.record()
+            for _ in range(steps):
+                fn()
+            e1.record()
+            sync_all()
+            t = max_over_ranks(e0.elapsed_time(e1) / steps)
+            ctx.check()
+            return t
+
+        a_steps = max(3, min(args.steps, 10))
+        # Ulysses: total sequence 32768, 32 heads, D 128, causal; per rank 4 heads over the full sequence
+        if world > 1:
+            uly = UlyssesAttention(ctx, 1, 32, 32768 // world, 128, dt, causal=True)
+            uly.qkv_src.local.copy_(seeded(7000 + rank, (3, 1, 32, 32768 // world, 128), 1.0, dt).to(dev))
+            sync_all()
+            u_ms = time_op(lambda: uly(), a_steps)
+            heads_local = 32 // world
+        else:
+            from syncopate_b200.computation.attn import AttentionState, attention_forward
+
+            heads_local = 4
+            uq = seeded(7000, (3, 1, heads_local, 32768, 128), 1.0, dt).to(dev)
+            uo = torch.empty(1, heads_local, 32768, 128, dtype=dt, device=dev)
+            ust = AttentionState(1, heads_local, 32768, dev)
+            u_ms = time_op(lambda: attention_forward(uq[0], uq[1], uq[2], 128 ** -0.5, uo, causal=True, state=ust,
+                                                     status=ctx.status), a_steps)
+        u_flop = 4.0 * 32768 * 32768 * 128 * heads_local / 2
+        attn_results["ulysses_attn"] = {
+            "workload": f"cfg3 Ulysses all2all+attention+all2all bf16: S=32768, 32 heads, D=128, causal; {heads_local} heads per rank"
+                        + (" (1 GPU: attention only)" if world == 1 else ""),
+            "ms_per_step": u_ms, "per_gpu_tflops_causal": u_flop / (u_ms * 1e-3) / 1e12}
+        # context parallel: total sequence 65536, 64 Q heads / 8 KV heads, causal zigzag
+        cp_world = world if world > 1 else 8
+        s_local = 65536 // cp_world
+        if world > 1:
+            cp = ContextParallelAttention(ctx, 1, 64, 8, s_local, 128, dt, causal=True, zigzag=True, plan="swizzle")
+            cp.kv_shard.copy_(seeded(8000 + rank, (2, 1, 8, s_local, 128), 1.0, dt).to(dev))
+        else:
+            ew = EmulatedWorld(cp_world)
+            cp = ContextParallelAttention(ew.contexts[0], 1, 64, 8, s_local, 128, dt, causal=True, zigzag=True)
+            cp.kv.local.copy_(seeded(8000, (2, 1, 8, 65536, 128), 1.0, dt).to(dev))
+            cp.ops, cp.comm = [], None  # one GPU: K/V already gathered, flags pre-set
+            cp.flags.local.fill_(1 << 40)
+        cq = seeded(9000 + rank, (1, 64, s_local, 128), 1.0, dt).to(dev)
+        co = torch.empty_like(cq)
+        sync_all()
+        c_ms = time_op(lambda: cp(cq, co), a_steps)
+        if world == 1:
+            if cp.ctx.status.tolist()[0] != 0:
+                raise RuntimeError(f"context-parallel attention status {cp.ctx.status.tolist()}")
+        c_flop = 4.0 * 65536 * 65536 * 128 * 64 / cp_world / 2
+        attn_results["cp_attn"] = {
+            "workload": f"cfg4 context-parallel all-gather-KV attention bf16: S=65536 ({s_local} Q tokens per rank), "
+                        "64 Q / 8 KV heads, D=128, causal zigzag" + (" (1 GPU: rank 0 of 8, K/V resident)" if world == 1 else ""),
+            "ms_per_step": c_ms, "per_gpu_tflops_causal": c_flop / (c_ms * 1e-3) / 1e12}
+
     line = None
     if rank == 0:
         cpu_val, cores, sample, _ = cpu_ag_gemm_sample(tp) if world == 1 else (None, None, None, None)
@@ -344,6 +410,7 @@ def run_own_arm(args):
                                         f"[{RS_M // world if world > 1 else RS_M},{RS_N}]"
                                         + (" (1 GPU: GEMM only)" if world == 1 else ""),
                             "ms_per_step": rs_ms, "per_gpu_tflops": rs_per_gpu, "frac_of_peak": rs_per_gpu / peak},
+                **attn_results,
             },
         }
         if cpu_val is not None:
@@ -363,6 +430,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-attention", action="store_true", help="leave the attention operators out of other_ops")
     ap.add_argument("--comm", default="ce", choices=["sm", "ce"],
                     help="who moves the all-gather chunks: the kernel's comm warps (sm) or copy engines (ce)")
     args = ap.parse_args()
