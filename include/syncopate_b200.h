@@ -26,6 +26,7 @@ extern "C" {
 #define SYN_MAX_WORLD 8
 #define SYN_MAX_WAVES 64
 #define SYN_MAX_COMM_OPS 64
+#define SYN_NUM_COUNTERS (SYN_MAX_WAVES + SYN_MAX_COMM_OPS + 2)
 
 /* ------------------------------------------------------------------ error codes */
 #define SYN_OK 0
@@ -95,6 +96,10 @@ typedef struct syn_gemm_args {
   uint64_t signal_value;   /* value waited for / written; 0 = 1 */
   uint64_t timeout_ns;     /* bound of every device-side wait; 0 = 2 s */
   int32_t* status;         /* device int32[4] {code, wave, flag, block}; may be NULL */
+  /* Optional device uint32[2], zero before the first call (every call leaves it zero): when given,
+   * CTAs take tiles from a grid-wide counter as they become free instead of round-robin, which
+   * hides the stall of the CTAs that reach a wave before its flag is up. */
+  uint32_t* sched_counter;
 } syn_gemm_args;
 
 /* Un-fused / flag-gated persistent GEMM on one GPU.  `sched` may be NULL (one wave = whole C);
@@ -171,7 +176,8 @@ int syn_flag_wait(const uint64_t* flag, uint64_t value, uint64_t timeout_ns, int
 /* ------------------------------------------------------------------ fused operators
  * The flag value of one fused call is `gemm.signal_value` (an epoch that the caller increases by
  * one per call; flags are never reset, waits are `>=`).  `counters` is device uint32
- * [SYN_MAX_WAVES + SYN_MAX_COMM_OPS], zero before the first call and left zero by every call.
+ * [SYN_NUM_COUNTERS], zero before the first call and left zero by every call (per-wave tile counts,
+ * per-copy CTA counts, and the two words of the dynamic tile scheduler).
  */
 
 /* All-gather + GEMM (replaces kernel_gemm_consumer + the copy-engine / SM-copy program,

@@ -82,6 +82,7 @@ class GemmArgs(C.Structure):
         ("signal_value", C.c_uint64),
         ("timeout_ns", C.c_uint64),
         ("status", C.c_void_p),
+        ("sched_counter", C.c_void_p),
     ]
 
 

@@ -98,6 +98,7 @@ def gemm(
     signal_value: int = 1,
     timeout_ns: int = 0,
     status=None,
+    sched_counter=None,
     stream=None,
 ) -> torch.Tensor:
     """``c = a @ b.T`` with fp32 accumulation.
@@ -112,6 +113,7 @@ def gemm(
     if BLOCK_SIZE_M not in (0, 128) or BLOCK_SIZE_K not in (0, 64):
         raise ValueError("this backend uses 128 x N x 64 tiles")
     g = _gemm_args(a, b, c, num_gemm_sms, BLOCK_SIZE_N, GROUP_SIZE_M, signal_value, timeout_ns, status)
+    g.sched_counter = _ptr(sched_counter)  # uint32[2], zero: dynamic tile scheduling
     keep = []
     cons = prod = None
     sizes, offs = _to_list(cur_wave_sizes), _to_list(wave_offsets)

@@ -94,6 +94,7 @@ int syn_ag_gemm(const syn_ag_gemm_args* args, const syn_schedule* a_sched, void*
   }
   p.num_comm_ops = n_ops;
   p.counters = args->counters;
+  if (args->counters != nullptr) p.sched = args->counters + SYN_MAX_WAVES + SYN_MAX_COMM_OPS;
   grid = std::min(grid, p.total_tiles);
   if (grid <= 0) return SYN_ERR_INVALID;
   return gemm_launch(p, bn, /*fused=*/n_ops > 0, grid, static_cast<cudaStream_t>(stream));
@@ -191,6 +192,7 @@ int syn_gemm_rs(const syn_gemm_rs_args* args, const syn_schedule* src_sched, con
   p.red_ld = g.N;
   p.red_row0 = rank * slab_rows;
   p.counters = args->counters;
+  p.sched = args->counters + SYN_MAX_WAVES + SYN_MAX_COMM_OPS;
   p.c = args->out;
   p.ldc = ldo;
   grid = std::min(grid, p.total_tiles);

@@ -99,6 +99,7 @@ int gemm_fill_common(GemmParams* p, const syn_gemm_args* a, const syn_schedule* 
   p->signal_value = a->signal_value ? a->signal_value : 1;
   p->timeout_ns = a->timeout_ns ? a->timeout_ns : 2000000000ull;
   p->status = a->status;
+  p->sched = a->sched_counter;
 
   int cum = 0;
   if (sched == nullptr) {

@@ -20,6 +20,7 @@ constexpr int GEMM_BK = 64;          // 64 x 16-bit = one 128-byte swizzle row
 constexpr int GEMM_UMMA_K = 16;
 constexpr int GEMM_MAX_WAVES = 64;
 constexpr int GEMM_MAX_COMM_OPS = 64;
+constexpr int TILE_Q = 4;             // depth of the in-CTA tile queue
 constexpr int GEMM_THREADS = 256;    // warp0 TMA, warp1 MMA, warp2 TMEM alloc, warp3 comm, warps4-7 epilogue
 #ifndef SYN_COMM_PIECE
 #define SYN_COMM_PIECE 8192
@@ -81,6 +82,7 @@ struct GemmParams {
   int32_t red_row0;       // global C row of the staged slabs' row 0
   const uint64_t* csig;   // consumer flags
   uint32_t* counters;     // [num_waves] producer counters then [num_comm_ops] comm counters, self-resetting
+  uint32_t* sched;        // [2] {next tile, CTAs finished}: dynamic tile scheduling when non-null (self-resetting)
   uint64_t signal_value;
   uint64_t timeout_ns;
   int32_t* status;
@@ -213,9 +215,12 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
   uint64_t* tfull_bar = bars + 2 * STAGES;
   uint64_t* tempty_bar = bars + 2 * STAGES + 2;
   uint64_t* comm_bar = bars + 2 * STAGES + 4;
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4 + COMM_NBUF);
+  uint64_t* tq_full = comm_bar + COMM_NBUF;   // tile queue: producer -> MMA issuer and epilogue
+  uint64_t* tq_empty = tq_full + TILE_Q;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tq_empty + TILE_Q);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_holder + 1);
   int* abort_info = const_cast<int*>(abort_word) + 1;  // {wave, flag}
+  volatile int* tile_q = reinterpret_cast<volatile int*>(abort_info + 2);  // [TILE_Q] tile ids, -1 = no more
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -232,6 +237,10 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
       mbar_init(&tempty_bar[i], 4);
     }
     for (int i = 0; i < COMM_NBUF; ++i) mbar_init(&comm_bar[i], 1);
+    for (int i = 0; i < TILE_Q; ++i) {
+      mbar_init(&tq_full[i], 1);
+      mbar_init(&tq_empty[i], 5);  // the MMA thread and one lane of each epilogue warp
+    }
     *abort_word = 0;
     abort_info[0] = -1;
     abort_info[1] = -1;
@@ -257,7 +266,17 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
       int stage = 0;
       uint32_t phase = 0;
       bool first = true;
-      for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
+      for (uint32_t n = 0;; ++n) {
+        // next tile: taken from the grid-wide counter (dynamic) or round-robin (static), then
+        // handed to the other roles through the tile queue
+        const int slot = n % TILE_Q;
+        mbar_wait(&tq_empty[slot], ((n / TILE_Q) & 1u) ^ 1u, abort_word, p.timeout_ns);
+        int tile = p.sched != nullptr ? static_cast<int>(atomicAdd(p.sched, 1u))
+                                      : static_cast<int>(blockIdx.x + n * gridDim.x);
+        if (tile >= p.total_tiles || *abort_word != 0) tile = -1;
+        tile_q[slot] = tile;
+        mbar_arrive(&tq_full[slot]);
+        if (tile < 0) break;
         int m_blk, n_blk;
         const bool moved = cur.seek(p, tile, m_blk, n_blk);
         if (moved || first) {
@@ -292,7 +311,12 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
-      for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
+      for (uint32_t n = 0;; ++n) {
+        const int slot = n % TILE_Q;
+        mbar_wait(&tq_full[slot], (n / TILE_Q) & 1u, abort_word, p.timeout_ns);
+        const int tile = tile_q[slot];
+        mbar_arrive(&tq_empty[slot]);
+        if (tile < 0 || *abort_word != 0) break;
         mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, abort_word, p.timeout_ns);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * ACC_STRIDE);
@@ -332,10 +356,47 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
     uint32_t acc_phase = 0;
     bool first = true;
     bool red_ready = false;
-    for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
+    int done_wave = -1;        // wave whose tiles this CTA has stored but not yet counted
+    uint32_t done_tiles = 0;
+    // counts this CTA's finished tiles of a wave once, when it leaves the wave: its TMA stores have
+    // been performed and its plain stores fenced before the count; the CTA that completes the
+    // wave's total raises the wave's flag
+    auto flush_wave = [&]() {
+      if constexpr (FUSED) {
+        if (done_wave >= 0 && done_tiles > 0) {
+          const GemmWave& dw = p.waves[done_wave];
+          if (warp == 4 && lane == 0) {
+            bulk_wait<0>();
+            fence_proxy_async();
+          }
+          __threadfence_system();
+          asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
+          if (warp == 4 && lane == 0) {
+            const uint32_t tiles_w = static_cast<uint32_t>(dw.tiles_m) * static_cast<uint32_t>(dw.tiles_n);
+            __threadfence_system();
+            const uint32_t old = atomicAdd(&p.counters[done_wave], done_tiles);
+            if (old + done_tiles == tiles_w) {
+              p.counters[done_wave] = 0;
+              __threadfence_system();
+              st_release_sys_u64(p.routes[dw.route].flag, p.signal_value);
+            }
+          }
+        }
+      }
+      done_wave = -1;
+      done_tiles = 0;
+    };
+    for (uint32_t n = 0;; ++n) {
+      const int slot = n % TILE_Q;
+      mbar_wait(&tq_full[slot], (n / TILE_Q) & 1u, abort_word, p.timeout_ns);
+      const int tile = tile_q[slot];
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tq_empty[slot]);
+      if (tile < 0 || tile >= p.total_tiles || *abort_word != 0) break;
       int m_blk, n_blk;
       const bool moved = cur.seek(p, tile, m_blk, n_blk);
       const GemmWave& wv = p.waves[cur.wave];
+      if (done_wave >= 0 && done_wave != cur.wave) flush_wave();
       // destination of this tile
       char* out_base = reinterpret_cast<char*>(p.c);
       int out_ld = p.ldc;
@@ -459,29 +520,13 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
       if (acc == 0) acc_phase ^= 1u;
 
       if constexpr (FUSED) {
-        // wave completion: count stored tiles; the last one raises the wave's flag
         if (wv.route >= 0 && p.routes[wv.route].flag != nullptr) {
-          if (tmap_idx >= 0) {
-            if (leader) {
-              bulk_wait<0>();  // this tile's TMA stores have been performed
-              fence_proxy_async();
-            }
-          }
-          __threadfence_system();
-          asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
-          if (warp == 4 && lane == 0) {
-            const uint32_t tiles_w = static_cast<uint32_t>(wv.tiles_m) * static_cast<uint32_t>(wv.tiles_n);
-            __threadfence_system();
-            const uint32_t old = atomicAdd(&p.counters[cur.wave], 1u);
-            if (old == tiles_w - 1) {
-              p.counters[cur.wave] = 0;
-              __threadfence_system();
-              st_release_sys_u64(p.routes[wv.route].flag, p.signal_value);
-            }
-          }
+          done_wave = cur.wave;
+          ++done_tiles;
         }
       }
     }
+    flush_wave();
   }
 
   if constexpr (FUSED) {
@@ -492,6 +537,14 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
   if (warp == 2) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && p.sched != nullptr) {
+    // the last CTA to get here (every CTA has stopped taking tiles by then) rewinds the scheduler
+    const uint32_t old = atomicAdd(&p.sched[1], 1u);
+    if (old == gridDim.x - 1) {
+      p.sched[0] = 0;
+      p.sched[1] = 0;
+    }
   }
   if (threadIdx.x == 0 && *abort_word != 0 && p.status != nullptr) {
     if (atomicCAS(p.status, 0, *abort_word) == 0) {

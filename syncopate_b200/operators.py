@@ -25,7 +25,7 @@ from .computation.gemm.plan import rs_remote_signals
 from .interface import lower_comm_plan_to_raw_schedules
 from .runtime import SymmetricContext
 
-NUM_COUNTERS = 128  # SYN_MAX_WAVES + SYN_MAX_COMM_OPS
+NUM_COUNTERS = 130  # SYN_NUM_COUNTERS: wave counters, copy counters, tile scheduler
 
 
 def plan_all_gather(world: int, rows_per_rank: int, K: int, dtype: torch.dtype, kind: str = "swizzle",
@@ -99,6 +99,7 @@ class AllGatherGemm:
             self._wave_offsets = [[o[0], 0] for o in self.schedule.gen_block_offset_lists()]
             self._wave_sizes = [[s[0], N] for s in self.schedule.gen_block_shape_lists()]
             self._signals = self.schedule.gen_signal_lists()
+            self._sched = torch.zeros(2, dtype=torch.int32, device=ctx.device)
             return
         self.a = ctx.alloc((self.M, K), dtype)
         self.flags = ctx.alloc((max(self.info.recv_signal_num, 1),), torch.int64)
@@ -124,7 +125,7 @@ class AllGatherGemm:
             gemm(self.a.local, b, c, self.world, self.num_sms, BLOCK_SIZE_N=self.block_n,
                  cur_wave_sizes=self._wave_sizes, wave_offsets=self._wave_offsets, signal_ptr=self.flags.local,
                  signal_offsets=self._signals, signal_value=self.epoch, status=self.ctx.status,
-                 timeout_ns=self.timeout_ns, stream=cur)
+                 timeout_ns=self.timeout_ns, sched_counter=self._sched, stream=cur)
             self.comm_ctx.end_before(cur)
             return c
         return ag_gemm(self.a.symm, self.a.local, b, c, self.schedule, self.flags.local, self.counters,

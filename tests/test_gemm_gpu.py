@@ -114,7 +114,7 @@ def test_producer_flags_are_raised_after_each_wave(status):
     a, b = _seeded(5, (M, K), 1.0, torch.bfloat16), _seeded(6, (N, K), 0.02, torch.bfloat16)
     c = torch.zeros(M, N, dtype=torch.bfloat16, device="cuda")
     flags = torch.zeros(4, dtype=torch.int64, device="cuda")
-    counters = torch.zeros(128, dtype=torch.int32, device="cuda")
+    counters = torch.zeros(130, dtype=torch.int32, device="cuda")
     offs = [[128, 0], [256, 0], [384, 0], [0, 0]]
     for epoch in (1, 2):
         gemm(a.cuda(), b.cuda(), c, cur_wave_sizes=[[128, N]] * 4, wave_offsets=offs, signal_offsets=[-1] * 4,
@@ -164,7 +164,7 @@ def test_fused_ag_gemm_emulated_ranks(world, rows, K, N, kind, status):
                                   shards, b)
         c = torch.zeros(world * rows, N, dtype=dt, device="cuda")
         flags = torch.zeros(max(info.recv_signal_num, 1), dtype=torch.int64, device="cuda")
-        counters = torch.zeros(128, dtype=torch.int32, device="cuda")
+        counters = torch.zeros(130, dtype=torch.int32, device="cuda")
         symm = L.Symm.of(r, [x.data_ptr() for x in bufs])
         for epoch in (1, 2):
             if epoch == 2:  # forget the gathered chunks: the second call must fetch them again
@@ -203,7 +203,7 @@ def test_fused_gemm_rs_emulated_ranks(world, M, N, Kl, kind, status):
     stages = [torch.full((2, world, slab, N), float("nan"), dtype=dt, device="cuda") for _ in range(world)]
     flags = [torch.zeros(max(info.recv_signal_num, 1), dtype=torch.int64, device="cuda") for _ in range(world)]
     outs = [torch.zeros(slab, N, dtype=dt, device="cuda") for _ in range(world)]
-    counters = torch.zeros(128, dtype=torch.int32, device="cuda")
+    counters = torch.zeros(130, dtype=torch.int32, device="cuda")
     for epoch in (1, 2):
         for phase in (0, 1):
             for r in range(world):
