@@ -258,6 +258,28 @@ def run_own_arm(args):
     per_gpu = flop / (ms * 1e-3) / 1e12
     value = per_gpu * world
 
+    # ---------------- the same GEMM with every chunk already resident (flags pre-set, no transfers),
+    # timed while all ranks compute: the non-overlapped share of the fused step is the difference
+    compute_only_ms = None
+    if world > 1:
+        from syncopate_b200.computation.gemm import gemm as _plain_gemm
+
+        ones = torch.full((max(op.info.recv_signal_num, 1),), 1 << 40, dtype=torch.int64, device=dev)
+        offs = [[o[0], 0] for o in op.schedule.gen_block_offset_lists()]
+        sizes = [[s_[0], n_local] for s_ in op.schedule.gen_block_shape_lists()]
+        sigs = op.schedule.gen_signal_lists()
+        co_step = lambda: _plain_gemm(op.a.local, b, c, cur_wave_sizes=sizes, wave_offsets=offs, signal_ptr=ones,
+                                      signal_offsets=sigs, status=ctx.status)
+        for _ in range(3):
+            co_step()
+        sync_all()
+        e0.record()
+        for _ in range(args.steps):
+            co_step()
+        e1.record()
+        sync_all()
+        compute_only_ms = max_over_ranks(e0.elapsed_time(e1) / args.steps)
+
     # ---------------- e2e: host buffers in, host result out, through the operator API
     a_host = seeded(1000 + rank, (ROWS, K_DIM), 1.0, dt).pin_memory() if world > 1 else a_full.cpu().pin_memory()
     c_host = torch.empty(M, n_local, dtype=dt).pin_memory()
@@ -314,6 +336,19 @@ def run_own_arm(args):
     ctx.check()
     rs_flop = 2.0 * RS_M * RS_N * rs_k
     rs_per_gpu = rs_flop / (rs_ms * 1e-3) / 1e12
+    rs_compute_only_ms = None
+    if world > 1:
+        rfull = torch.empty(RS_M, RS_N, dtype=dt, device=dev)
+        for _ in range(3):
+            _plain_gemm(ra, rb, rfull, status=ctx.status)
+        sync_all()
+        e0.record()
+        for _ in range(args.steps):
+            _plain_gemm(ra, rb, rfull, status=ctx.status)
+        e1.record()
+        sync_all()
+        rs_compute_only_ms = max_over_ranks(e0.elapsed_time(e1) / args.steps)
+        del rfull
 
     # ---------------- attention operators at the benchmark shapes (reported, not the headline)
     attn_results = {}
@@ -393,6 +428,8 @@ def run_own_arm(args):
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": workload_config(world),
             "per_gpu_tflops": per_gpu,
+            "compute_only_ms": compute_only_ms,
+            "non_overlapped_ms": (ms - compute_only_ms) if compute_only_ms is not None else 0.0,
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms,
@@ -409,7 +446,8 @@ def run_own_arm(args):
                 "gemm_rs": {"workload": f"cfg2 GEMM+RS bf16 TP={tp}: A [{RS_M},{rs_k}], B [{RS_N},{rs_k}], out "
                                         f"[{RS_M // world if world > 1 else RS_M},{RS_N}]"
                                         + (" (1 GPU: GEMM only)" if world == 1 else ""),
-                            "ms_per_step": rs_ms, "per_gpu_tflops": rs_per_gpu, "frac_of_peak": rs_per_gpu / peak},
+                            "ms_per_step": rs_ms, "per_gpu_tflops": rs_per_gpu, "frac_of_peak": rs_per_gpu / peak,
+                            "compute_only_ms": rs_compute_only_ms},
                 **attn_results,
             },
         }

@@ -100,6 +100,11 @@ typedef struct syn_gemm_args {
    * CTAs take tiles from a grid-wide counter as they become free instead of round-robin, which
    * hides the stall of the CTAs that reach a wave before its flag is up. */
   uint32_t* sched_counter;
+  /* Optional device uint64[2 + 3 * num_waves] of %globaltimer stamps (ns) for the non-overlapped-time
+   * breakdown: [0] earliest CTA start (initialise to UINT64_MAX), [1] latest CTA end (0); per wave w:
+   * [2+3w] earliest flag-wait begin (UINT64_MAX), [3+3w] latest flag-wait end (0), [4+3w] summed wait
+   * over CTAs (0). */
+  uint64_t* trace;
 } syn_gemm_args;
 
 /* Un-fused / flag-gated persistent GEMM on one GPU.  `sched` may be NULL (one wave = whole C);

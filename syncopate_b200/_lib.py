@@ -83,6 +83,7 @@ class GemmArgs(C.Structure):
         ("timeout_ns", C.c_uint64),
         ("status", C.c_void_p),
         ("sched_counter", C.c_void_p),
+        ("trace", C.c_void_p),
     ]
 
 

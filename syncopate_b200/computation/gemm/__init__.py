@@ -99,6 +99,7 @@ def gemm(
     timeout_ns: int = 0,
     status=None,
     sched_counter=None,
+    trace=None,
     stream=None,
 ) -> torch.Tensor:
     """``c = a @ b.T`` with fp32 accumulation.
@@ -114,6 +115,7 @@ def gemm(
         raise ValueError("this backend uses 128 x N x 64 tiles")
     g = _gemm_args(a, b, c, num_gemm_sms, BLOCK_SIZE_N, GROUP_SIZE_M, signal_value, timeout_ns, status)
     g.sched_counter = _ptr(sched_counter)  # uint32[2], zero: dynamic tile scheduling
+    g.trace = _ptr(trace)                  # uint64[2 + 3 * waves] timer stamps (see the header)
     keep = []
     cons = prod = None
     sizes, offs = _to_list(cur_wave_sizes), _to_list(wave_offsets)

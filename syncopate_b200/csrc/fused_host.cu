@@ -5,7 +5,19 @@
 
 #include "gemm_host.h"
 
+#include <stdlib.h>
+
 namespace syn {
+
+// SYNCOPATE_B200_STATIC_SCHED=1 keeps the round-robin tile order in the fused kernels (tuning aid).
+static bool dynamic_sched() {
+  static int cached = -1;
+  if (cached < 0) {
+    const char* e = getenv("SYNCOPATE_B200_STATIC_SCHED");
+    cached = (e != nullptr && e[0] == '1') ? 0 : 1;
+  }
+  return cached == 1;
+}
 
 static int check_symm(const syn_symm& s) {
   if (s.world <= 0 || s.world > SYN_MAX_WORLD || s.rank < 0 || s.rank >= s.world) return SYN_ERR_INVALID;
@@ -94,7 +106,7 @@ int syn_ag_gemm(const syn_ag_gemm_args* args, const syn_schedule* a_sched, void*
   }
   p.num_comm_ops = n_ops;
   p.counters = args->counters;
-  if (args->counters != nullptr) p.sched = args->counters + SYN_MAX_WAVES + SYN_MAX_COMM_OPS;
+  if (args->counters != nullptr && dynamic_sched()) p.sched = args->counters + SYN_MAX_WAVES + SYN_MAX_COMM_OPS;
   grid = std::min(grid, p.total_tiles);
   if (grid <= 0) return SYN_ERR_INVALID;
   return gemm_launch(p, bn, /*fused=*/n_ops > 0, grid, static_cast<cudaStream_t>(stream));
@@ -192,7 +204,7 @@ int syn_gemm_rs(const syn_gemm_rs_args* args, const syn_schedule* src_sched, con
   p.red_ld = g.N;
   p.red_row0 = rank * slab_rows;
   p.counters = args->counters;
-  p.sched = args->counters + SYN_MAX_WAVES + SYN_MAX_COMM_OPS;
+  if (dynamic_sched()) p.sched = args->counters + SYN_MAX_WAVES + SYN_MAX_COMM_OPS;
   p.c = args->out;
   p.ldc = ldo;
   grid = std::min(grid, p.total_tiles);

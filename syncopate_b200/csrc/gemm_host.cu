@@ -100,6 +100,7 @@ int gemm_fill_common(GemmParams* p, const syn_gemm_args* a, const syn_schedule* 
   p->timeout_ns = a->timeout_ns ? a->timeout_ns : 2000000000ull;
   p->status = a->status;
   p->sched = a->sched_counter;
+  p->trace = reinterpret_cast<unsigned long long*>(a->trace);
 
   int cum = 0;
   if (sched == nullptr) {

@@ -83,6 +83,8 @@ struct GemmParams {
   const uint64_t* csig;   // consumer flags
   uint32_t* counters;     // [num_waves] producer counters then [num_comm_ops] comm counters, self-resetting
   uint32_t* sched;        // [2] {next tile, CTAs finished}: dynamic tile scheduling when non-null (self-resetting)
+  unsigned long long* trace;  // optional [2 + 3 * num_waves] globaltimer stamps: kernel first start / last end,
+                              // per wave: earliest flag-wait begin, latest flag-wait end, summed wait ns
   uint64_t signal_value;
   uint64_t timeout_ns;
   int32_t* status;
@@ -258,6 +260,7 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  if (p.trace != nullptr && threadIdx.x == 0) atomicMin(&p.trace[0], globaltimer_ns());
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
@@ -282,6 +285,7 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
         if (moved || first) {
           const int sig = p.waves[cur.wave].csig;
           if (sig >= 0 && p.csig != nullptr) {
+            const unsigned long long t_wait0 = p.trace != nullptr ? globaltimer_ns() : 0ull;
             if (!flag_wait_ge(p.csig + sig, p.signal_value, abort_word, p.timeout_ns)) {
               if (abort_info[0] < 0) {
                 abort_info[0] = cur.wave;
@@ -289,6 +293,12 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
               }
             }
             fence_proxy_async();  // order the flag read before async-proxy (TMA) reads of the chunk
+            if (p.trace != nullptr) {
+              const unsigned long long t_wait1 = globaltimer_ns();
+              atomicMin(&p.trace[2 + 3 * cur.wave], t_wait0);
+              atomicMax(&p.trace[3 + 3 * cur.wave], t_wait1);
+              atomicAdd(&p.trace[4 + 3 * cur.wave], t_wait1 - t_wait0);
+            }
           }
           first = false;
         }
@@ -538,6 +548,7 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+  if (p.trace != nullptr && threadIdx.x == 0) atomicMax(&p.trace[1], globaltimer_ns());
   if (threadIdx.x == 0 && p.sched != nullptr) {
     // the last CTA to get here (every CTA has stopped taking tiles by then) rewinds the scheduler
     const uint32_t old = atomicAdd(&p.sched[1], 1u);

@@ -25,6 +25,12 @@ from .computation.gemm.plan import rs_remote_signals
 from .interface import lower_comm_plan_to_raw_schedules
 from .runtime import SymmetricContext
 
+def _raw_lib():
+    from . import _lib
+
+    return _lib.lib()
+
+
 NUM_COUNTERS = 130  # SYN_NUM_COUNTERS: wave counters, copy counters, tile scheduler
 
 
@@ -78,7 +84,8 @@ class AllGatherGemm:
     as in the reference's tests/test_ag_gemm_gen.py:44-77."""
 
     def __init__(self, ctx: SymmetricContext, rows_per_rank: int, K: int, N: int, dtype=torch.bfloat16,
-                 plan: str = "swizzle", num_sms: int = 0, block_n: int = 0, timeout_ns: int = 0, comm: str = "sm"):
+                 plan: str = "swizzle", num_sms: int = 0, block_n: int = 0, timeout_ns: int = 0, comm: str = "sm",
+                 copy_streams: int = 2):
         self.ctx = ctx
         self.world, self.rank = ctx.world, ctx.rank
         self.rows, self.K, self.N, self.dtype = rows_per_rank, K, N, dtype
@@ -89,6 +96,7 @@ class AllGatherGemm:
                                                              copy_engine=(comm == "ce"))
         self.schedule = lowered[self.rank]["a"]
         self.epoch = 0
+        self.trace = None  # optional uint64 stamp buffer handed to the kernel (see syn_gemm_args.trace)
         if comm == "ce":
             from .communication.comm_runtime.communication_context import CommContext
 
@@ -100,10 +108,43 @@ class AllGatherGemm:
             self._wave_sizes = [[s[0], N] for s in self.schedule.gen_block_shape_lists()]
             self._signals = self.schedule.gen_signal_lists()
             self._sched = torch.zeros(2, dtype=torch.int32, device=ctx.device)
+            # One chunk copy does not fill the link while the GEMM is running; consecutive chunks
+            # are therefore issued round-robin on a few streams so that several are in flight.
+            # Each (copy, flag) pair stays in order on its stream; chunks are independent.
+            self._copy_streams = [torch.cuda.Stream() for _ in range(max(1, copy_streams))]
+            self._chunks = self._chunk_program()
             return
         self.a = ctx.alloc((self.M, K), dtype)
         self.flags = ctx.alloc((max(self.info.recv_signal_num, 1),), torch.int64)
         self.counters = torch.zeros(NUM_COUNTERS, dtype=torch.int32, device=ctx.device)
+
+    def _chunk_program(self):
+        """``[(dst_ptr, src_ptr, nbytes, flag_ptr)]``: the rank's copy-engine program (copy ops
+        followed by the flag they publish), resolved to addresses once."""
+        out, pending = [], []
+        bufs = self.comm_ctx.comm_buffers
+        for op in self.info.operations[self.rank][0]:
+            kind = type(op).__name__
+            if kind == "CopyEngineOp":
+                if op.src_rank == op.dst_rank:
+                    continue
+                pending.append((bufs[op.dst][op.dst_rank].data_ptr() + op.dst_offset,
+                                bufs[op.src][op.src_rank].data_ptr() + op.src_offset, op.size))
+            elif kind == "IntraNodeSignal" and pending:
+                flag = self.comm_ctx.recv_signal_bufs[op.rank].data_ptr() + 8 * op.offset
+                out.append((pending, flag))
+                pending = []
+        return out
+
+    def _issue_copies(self, cur) -> None:
+        lib = _raw_lib()
+        for s in self._copy_streams:
+            s.wait_stream(cur)
+        for i, (copies, flag) in enumerate(self._chunks):
+            sp = self._copy_streams[i % len(self._copy_streams)].cuda_stream
+            for dst, src, nbytes in copies:
+                lib.syn_memcpy_async(dst, src, nbytes, sp)
+            lib.syn_flag_set(flag, self.epoch, sp)
 
     @property
     def shard(self) -> torch.Tensor:
@@ -119,14 +160,13 @@ class AllGatherGemm:
                         timeout_ns=self.timeout_ns, stream=stream)
         if self.comm == "ce":
             cur = stream or torch.cuda.current_stream()
-            self.comm_ctx.signal_value = self.epoch
-            self.comm_ctx.start_after(cur)
-            self.comm_ctx.execute(neglect_local=True)
+            self._issue_copies(cur)
             gemm(self.a.local, b, c, self.world, self.num_sms, BLOCK_SIZE_N=self.block_n,
                  cur_wave_sizes=self._wave_sizes, wave_offsets=self._wave_offsets, signal_ptr=self.flags.local,
                  signal_offsets=self._signals, signal_value=self.epoch, status=self.ctx.status,
-                 timeout_ns=self.timeout_ns, sched_counter=self._sched, stream=cur)
-            self.comm_ctx.end_before(cur)
+                 timeout_ns=self.timeout_ns, sched_counter=self._sched, trace=self.trace, stream=cur)
+            for s in self._copy_streams:
+                cur.wait_stream(s)
             return c
         return ag_gemm(self.a.symm, self.a.local, b, c, self.schedule, self.flags.local, self.counters,
                        epoch=self.epoch, num_sms=self.num_sms, block_n=self.block_n, timeout_ns=self.timeout_ns,
