@@ -1,0 +1,286 @@
+// CTA-pair form of the persistent GEMM: a cluster of two CTAs computes one 256 x BN tile with
+// tcgen05.mma.cta_group::2.  Each CTA stages its own 128 rows of A and its own half of the B tile,
+// so the shared-memory traffic per flop drops by a third against the one-CTA kernel and the
+// operand reads of the tensor cores no longer compete with a full B tile per CTA.
+//
+// Same schedule semantics as gemm_kernel (waves in order, consumer flags, grouped raster inside a
+// wave, here over 256-row tiles).  Plain local stores only: the routed epilogue and the comm warp
+// stay with the one-CTA kernel.  No TMA load carries a multicast qualifier; only tcgen05.commit
+// signals both CTAs' barriers.
+#pragma once
+#include "gemm_sm100.cuh"
+
+namespace syn {
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of `addr` (a shared::cta address of this CTA) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+  uint32_t out;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(addr), "r"(rank));
+  return out;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// 2-D tiled load into this CTA's shared memory whose completion is counted on the barrier at
+// cluster address `bar_cluster_addr` (the pair leader's barrier); no multicast.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr,
+                                                 int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_holder, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+               ::"r"(smem_u32(smem_holder)), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_f16_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on the barrier at this shared-memory offset in both CTAs of the pair once all MMAs issued
+// so far have completed.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  const uint16_t mask = 3;
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(smem_u32(bar)), "h"(mask)
+      : "memory");
+}
+
+constexpr int GEMM2_BM = 256;
+
+// Tile cursor over 256-row tiles (two 128-row tile rows of the wave table per tile).
+struct PairCursor {
+  int wave = 0;
+  int past = 0;
+  __device__ __forceinline__ bool seek(const GemmParams& p, int tile, int& m2_blk, int& n_blk) {
+    bool moved = false;
+    while (true) {
+      const int cnt = (p.waves[wave].tiles_m >> 1) * p.waves[wave].tiles_n;
+      if (tile < past + cnt) break;
+      past += cnt;
+      ++wave;
+      moved = true;
+    }
+    const int local = tile - past;
+    const int tm = p.waves[wave].tiles_m >> 1, tn = p.waves[wave].tiles_n;
+    const int in_group = p.group_m * tn;
+    const int group_id = local / in_group;
+    const int first_m = group_id * p.group_m;
+    const int gsz = min(tm - first_m, p.group_m);
+    const int r = local - group_id * in_group;
+    m2_blk = first_m + (r % gsz) + (p.waves[wave].off_m >> 1);
+    n_blk = (r / gsz) + p.waves[wave].off_n;
+    return moved;
+  }
+};
+
+template <int BN, int STAGES>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+gemm2_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap tmap_b_half,
+             const int total_pair_tiles) {
+  constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;         // this CTA's 128 rows of A
+  constexpr int B_BYTES = (BN / 2) * GEMM_BK * 2;        // this CTA's half of the B tile
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sA = smem;
+  uint8_t* sB = smem + STAGES * A_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* full_bar = bars;                    // leader's copy counts both CTAs' bytes
+  uint64_t* empty_bar = bars + STAGES;          // signalled in both CTAs by the leader's commits
+  uint64_t* tfull_bar = bars + 2 * STAGES;      // [2], signalled in both CTAs
+  uint64_t* tempty_bar = bars + 2 * STAGES + 2; // [2], leader's copy collects both CTAs' epilogue warps
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  int* abort_info = const_cast<int*>(abort_word) + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t cta_rank = cluster_ctarank();
+  const bool leader = cta_rank == 0;
+  const int pair_id = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  constexpr uint32_t TMEM_COLS = (2 * BN <= 256) ? 256 : 512;
+  constexpr int ACC_STRIDE = TMEM_COLS / 2;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull_bar[i], 1);
+      mbar_init(&tempty_bar[i], 8);  // four epilogue warps of each CTA
+    }
+    *abort_word = 0;
+    abort_info[0] = -1;
+    abort_info[1] = -1;
+    fence_mbar_init();
+  }
+  if (warp == 2) {
+    tmem_alloc_pair(tmem_holder, TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  if (warp == 0 && lane == 0) {
+    prefetch_tmap(&p.tmap_a);
+    prefetch_tmap(&tmap_b_half);
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers exist before anything signals them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      PairCursor cur;
+      int stage = 0;
+      uint32_t phase = 0;
+      bool first = true;
+      for (int tile = pair_id; tile < total_pair_tiles; tile += num_pairs) {
+        int m2_blk, n_blk;
+        const bool moved = cur.seek(p, tile, m2_blk, n_blk);
+        if (moved || first) {
+          const int sig = p.waves[cur.wave].csig;
+          if (sig >= 0 && p.csig != nullptr) {
+            if (!flag_wait_ge(p.csig + sig, p.signal_value, abort_word, p.timeout_ns)) {
+              if (abort_info[0] < 0) {
+                abort_info[0] = cur.wave;
+                abort_info[1] = sig;
+              }
+            }
+            fence_proxy_async();
+          }
+          first = false;
+        }
+        const int row0 = m2_blk * GEMM2_BM + static_cast<int>(cta_rank) * GEMM_BM;
+        const int col0 = n_blk * BN + static_cast<int>(cta_rank) * (BN / 2);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          mbar_wait(&empty_bar[stage], phase ^ 1u, abort_word, p.timeout_ns);
+          if (leader) mbar_expect_tx(&full_bar[stage], 2 * STAGE_BYTES);
+          const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
+          tma_load_2d_pair(sA + stage * A_BYTES, &p.tmap_a, bar, kb * GEMM_BK, row0);
+          tma_load_2d_pair(sB + stage * B_BYTES, &tmap_b_half, bar, kb * GEMM_BK, col0);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (pair leader only)
+    if (lane == 0 && leader) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      for (int tile = pair_id; tile < total_pair_tiles; tile += num_pairs) {
+        mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, abort_word, p.timeout_ns);
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * ACC_STRIDE);
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          mbar_wait(&full_bar[stage], phase, abort_word, p.timeout_ns);
+          tc_fence_after();
+          const uint64_t a_desc = make_smem_desc_sw128(smem_u32(sA + stage * A_BYTES), 16, 1024);
+          const uint64_t b_desc = make_smem_desc_sw128(smem_u32(sB + stage * B_BYTES), 16, 1024);
+#pragma unroll
+          for (int k = 0; k < GEMM_BK / GEMM_UMMA_K; ++k) {
+            umma_f16_ss_pair(d_tmem, a_desc + static_cast<uint64_t>(2 * k), b_desc + static_cast<uint64_t>(2 * k),
+                             p.idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit_pair(&empty_bar[stage]);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        umma_commit_pair(&tfull_bar[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
+    const int q = warp & 3;
+    PairCursor cur;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = pair_id; tile < total_pair_tiles; tile += num_pairs) {
+      int m2_blk, n_blk;
+      cur.seek(p, tile, m2_blk, n_blk);
+      mbar_wait(&tfull_bar[acc], acc_phase, abort_word, p.timeout_ns);
+      tc_fence_after();
+      const int grow = m2_blk * GEMM2_BM + static_cast<int>(cta_rank) * GEMM_BM + q * 32 + lane;
+      const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * ACC_STRIDE);
+      const int col0 = n_blk * BN;
+      const bool row_ok = grow < p.M;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c * 32, r);
+        tmem_ld_wait();
+        const int col = col0 + c * 32;
+        if (row_ok) {
+          uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.c) + (static_cast<size_t>(grow) * p.ldc + col) * 2);
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            if (col + v * 8 < p.N) {
+              uint4 u;
+              u.x = pack2(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]), p.dtype);
+              u.y = pack2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]), p.dtype);
+              u.z = pack2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]), p.dtype);
+              u.w = pack2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]), p.dtype);
+              dst[v] = u;
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[acc]), 0));
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // nobody leaves while the peer may still signal this CTA's barriers
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && *abort_word != 0 && p.status != nullptr) {
+    if (atomicCAS(p.status, 0, *abort_word) == 0) {
+      p.status[1] = abort_info[0];
+      p.status[2] = abort_info[1];
+      p.status[3] = static_cast<int>(blockIdx.x);
+    }
+  }
+}
+
+}  // namespace syn

@@ -2,7 +2,11 @@
 // tensor maps, block-size choice, launch.
 #include "gemm_host.h"
 
+#include <stdlib.h>
+
 #include <algorithm>
+
+#include "gemm2_sm100.cuh"
 
 namespace syn {
 
@@ -159,6 +163,66 @@ static int launch_bn(const GemmParams& p, int grid, cudaStream_t stream) {
   return SYN_OK;
 }
 
+template <int BN>
+static int launch_pair_bn(const GemmParams& p, const CUtensorMap& tmap_b_half, int pair_tiles, int grid,
+                          cudaStream_t stream) {
+  constexpr int kStage = GEMM_BM * GEMM_BK * 2 + (BN / 2) * GEMM_BK * 2;
+  constexpr int kStagesRaw = (232448 - 1024 - 512) / kStage;
+  constexpr int STAGES = kStagesRaw > 8 ? 8 : kStagesRaw;
+  constexpr int smem = STAGES * kStage + 1024 + 512;
+  auto kern = gemm2_kernel<BN, STAGES>;
+  static int configured_dev = -1;
+  int dev = 0;
+  SYN_CUDA_TRY(cudaGetDevice(&dev));
+  if (configured_dev != dev) {
+    SYN_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured_dev = dev;
+  }
+  kern<<<grid, GEMM_THREADS, smem, stream>>>(p, tmap_b_half, pair_tiles);
+  SYN_CUDA_TRY(cudaGetLastError());
+  return SYN_OK;
+}
+
+// CTA-pair kernel: 256-row tiles, plain local stores.  Usable when every wave starts and ends on a
+// 256-row boundary.  SYNCOPATE_B200_NO_PAIR=1 keeps the one-CTA kernel (tuning aid).
+static bool pair_eligible(const GemmParams& p, int bn, int grid) {
+  static int disabled = -1;
+  if (disabled < 0) {
+    const char* e = getenv("SYNCOPATE_B200_NO_PAIR");
+    disabled = (e != nullptr && e[0] == '1') ? 1 : 0;
+  }
+  if (disabled || grid < 2 || p.sched != nullptr) return false;
+  if (bn % 32 != 0 || bn < 64) return false;
+  for (int w = 0; w < p.num_waves; ++w) {
+    if (p.waves[w].route >= 0) return false;
+    if ((p.waves[w].tiles_m & 1) || (p.waves[w].off_m & 1)) return false;
+  }
+  return true;
+}
+
+static int gemm_launch_pair(const GemmParams& p_in, const syn_gemm_args* a, int bn, int grid, cudaStream_t stream) {
+  GemmParams p = p_in;
+  p.idesc = make_idesc_f16(GEMM2_BM, bn, a->dtype == SYN_DTYPE_BF16 ? 1u : 0u, 0, 0);
+  CUtensorMap tmap_b_half;
+  const int ldb = a->ldb ? a->ldb : a->K;
+  int rc = encode_tmap_2d_sw128(&tmap_b_half, a->b, a->N, a->K, ldb, bn / 2, GEMM_BK);
+  if (rc != SYN_OK) return rc;
+  int pair_tiles = 0;
+  for (int w = 0; w < p.num_waves; ++w) pair_tiles += (p.waves[w].tiles_m >> 1) * p.waves[w].tiles_n;
+  int g = std::min(grid & ~1, 2 * pair_tiles);
+  if (g < 2) return SYN_ERR_INVALID;
+  switch (bn) {
+    case 256: return launch_pair_bn<256>(p, tmap_b_half, pair_tiles, g, stream);
+    case 224: return launch_pair_bn<224>(p, tmap_b_half, pair_tiles, g, stream);
+    case 192: return launch_pair_bn<192>(p, tmap_b_half, pair_tiles, g, stream);
+    case 160: return launch_pair_bn<160>(p, tmap_b_half, pair_tiles, g, stream);
+    case 128: return launch_pair_bn<128>(p, tmap_b_half, pair_tiles, g, stream);
+    case 96: return launch_pair_bn<96>(p, tmap_b_half, pair_tiles, g, stream);
+    case 64: return launch_pair_bn<64>(p, tmap_b_half, pair_tiles, g, stream);
+    default: return SYN_ERR_UNSUPPORTED;
+  }
+}
+
 int gemm_launch(const GemmParams& p, int bn, bool fused, int grid, cudaStream_t stream) {
 #define SYN_BN_CASE(BN_)                                                     \
   case BN_:                                                                  \
@@ -236,6 +300,7 @@ int syn_gemm(const syn_gemm_args* args, const syn_schedule* sched, const syn_sch
       fused = true;
     }
   }
+  if (!fused && pair_eligible(p, bn, grid)) return gemm_launch_pair(p, args, bn, grid, static_cast<cudaStream_t>(stream));
   grid = std::min(grid, p.total_tiles);
   if (grid <= 0) return SYN_ERR_INVALID;
   return gemm_launch(p, bn, fused, grid, static_cast<cudaStream_t>(stream));
