@@ -105,6 +105,13 @@ typedef struct syn_gemm_args {
    * [2+3w] earliest flag-wait begin (UINT64_MAX), [3+3w] latest flag-wait end (0), [4+3w] summed wait
    * over CTAs (0). */
   uint64_t* trace;
+  /* Optional device scratch, 256-byte aligned, its first 256 bytes zero before the first call (every
+   * call leaves them zero): lets the CTA-pair kernel cut the few tiles left over after the last full
+   * persistent round along K over all CTA pairs (fp32 partial tiles in the scratch, summed in a
+   * fixed order) instead of giving them a round of their own.  256 + 74 * 256 * 256 * 4 bytes
+   * (about 19.4 MB) always suffice; with less, fewer shapes qualify. */
+  void* workspace;
+  size_t workspace_bytes;
 } syn_gemm_args;
 
 /* Un-fused / flag-gated persistent GEMM on one GPU.  `sched` may be NULL (one wave = whole C);

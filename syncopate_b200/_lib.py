@@ -84,6 +84,8 @@ class GemmArgs(C.Structure):
         ("status", C.c_void_p),
         ("sched_counter", C.c_void_p),
         ("trace", C.c_void_p),
+        ("workspace", C.c_void_p),
+        ("workspace_bytes", C.c_size_t),
     ]
 
 

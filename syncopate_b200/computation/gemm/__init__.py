@@ -51,6 +51,20 @@ def _check_mat(name: str, t: torch.Tensor) -> None:
         raise ValueError(f"{name}: unsupported dtype {t.dtype} (fp16 and bf16 only)")
 
 
+_WORKSPACES = {}
+
+
+def tail_workspace(device) -> torch.Tensor:
+    """Zeroed scratch (one per device, kept zero by the kernel) that lets the CTA-pair GEMM split the
+    tiles left over after the last full persistent round along K."""
+    key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
+    ws = _WORKSPACES.get(key)
+    if ws is None:
+        ws = torch.zeros(256 + 74 * 256 * 256 * 4, dtype=torch.uint8, device=torch.device("cuda", key))
+        _WORKSPACES[key] = ws
+    return ws
+
+
 def _gemm_args(a, b, c, num_sms, block_n, group_m, signal_value, timeout_ns, status) -> L.GemmArgs:
     _check_mat("a", a)
     _check_mat("b", b)
@@ -72,6 +86,8 @@ def _gemm_args(a, b, c, num_sms, block_n, group_m, signal_value, timeout_ns, sta
     g.signal_value = int(signal_value or 1)
     g.timeout_ns = int(timeout_ns or 0)
     g.status = _ptr(status)
+    ws = tail_workspace(a.device)
+    g.workspace, g.workspace_bytes = ws.data_ptr(), ws.numel()
     return g
 
 

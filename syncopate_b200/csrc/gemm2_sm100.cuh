@@ -72,6 +72,50 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
 
 constexpr int GEMM2_BM = 256;
 
+// Tail splitting.  When the tile count leaves a small remainder after the last full persistent
+// round, the remaining `tiles` tiles are not given a round of their own (which would idle most of
+// the GPU): each is cut along K into `slices` pieces, one per CTA pair.  A piece is written as an
+// fp32 partial tile to its own place in a workspace; when all 2 * slices CTAs of a tile have
+// arrived (they run at the same time, the grid being persistent), each of them sums a share of the
+// tile's rows over the slices in a fixed order, converts to 16 bit and stores.
+struct PairTail {
+  int tiles;            // 0 = no splitting
+  int slices;
+  int first_tile;       // tile id of the first tail tile (= full rounds * pairs)
+  float* ws;            // [tiles][slices][256][BN] fp32 partial tiles (contents need not be kept)
+  unsigned int* count;  // [2 * tiles] arrivals / departures, zero between launches
+};
+
+// Work item n of this pair: full-round tiles first, then (at most) one K slice of a tail tile.
+struct PairWork {
+  int tile, kb0, kb1;
+  bool is_slice;
+};
+__device__ __forceinline__ bool pair_work(const GemmParams& p, const PairTail& tail, int total, int pair_id, int num_pairs,
+                                          int n, PairWork& w) {
+  w.kb0 = 0;
+  w.kb1 = p.k_blocks;
+  w.is_slice = false;
+  if (tail.tiles == 0) {
+    w.tile = pair_id + n * num_pairs;
+    return w.tile < total;
+  }
+  const int rounds = tail.first_tile / num_pairs;  // the host makes first_tile a whole number of rounds
+  if (n < rounds) {
+    w.tile = pair_id + n * num_pairs;
+    return true;
+  }
+  if (n == rounds && pair_id < tail.tiles * tail.slices) {
+    w.tile = tail.first_tile + pair_id / tail.slices;
+    const int sl = pair_id % tail.slices;
+    w.kb0 = static_cast<int>(static_cast<long>(p.k_blocks) * sl / tail.slices);
+    w.kb1 = static_cast<int>(static_cast<long>(p.k_blocks) * (sl + 1) / tail.slices);
+    w.is_slice = true;
+    return w.kb1 > w.kb0;
+  }
+  return false;
+}
+
 // Tile cursor over 256-row tiles (two 128-row tile rows of the wave table per tile).
 struct PairCursor {
   int wave = 0;
@@ -101,7 +145,7 @@ struct PairCursor {
 template <int BN, int STAGES>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm2_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap tmap_b_half,
-             const int total_pair_tiles) {
+             const int total_pair_tiles, const PairTail tail) {
   constexpr int A_BYTES = GEMM_BM * GEMM_BK * 2;         // this CTA's 128 rows of A
   constexpr int B_BYTES = (BN / 2) * GEMM_BK * 2;        // this CTA's half of the B tile
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
@@ -160,9 +204,10 @@ gemm2_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUten
       int stage = 0;
       uint32_t phase = 0;
       bool first = true;
-      for (int tile = pair_id; tile < total_pair_tiles; tile += num_pairs) {
+      PairWork wk;
+      for (int n = 0; pair_work(p, tail, total_pair_tiles, pair_id, num_pairs, n, wk); ++n) {
         int m2_blk, n_blk;
-        const bool moved = cur.seek(p, tile, m2_blk, n_blk);
+        const bool moved = cur.seek(p, wk.tile, m2_blk, n_blk);
         if (moved || first) {
           const int sig = p.waves[cur.wave].csig;
           if (sig >= 0 && p.csig != nullptr) {
@@ -178,7 +223,7 @@ gemm2_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUten
         }
         const int row0 = m2_blk * GEMM2_BM + static_cast<int>(cta_rank) * GEMM_BM;
         const int col0 = n_blk * BN + static_cast<int>(cta_rank) * (BN / 2);
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        for (int kb = wk.kb0; kb < wk.kb1; ++kb) {
           mbar_wait(&empty_bar[stage], phase ^ 1u, abort_word, p.timeout_ns);
           if (leader) mbar_expect_tx(&full_bar[stage], 2 * STAGE_BYTES);
           const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
@@ -198,11 +243,12 @@ gemm2_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUten
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
-      for (int tile = pair_id; tile < total_pair_tiles; tile += num_pairs) {
+      PairWork wk;
+      for (int n = 0; pair_work(p, tail, total_pair_tiles, pair_id, num_pairs, n, wk); ++n) {
         mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, abort_word, p.timeout_ns);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * ACC_STRIDE);
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
+        for (int kb = wk.kb0; kb < wk.kb1; ++kb) {
           mbar_wait(&full_bar[stage], phase, abort_word, p.timeout_ns);
           tc_fence_after();
           const uint64_t a_desc = make_smem_desc_sw128(smem_u32(sA + stage * A_BYTES), 16, 1024);
@@ -210,7 +256,7 @@ gemm2_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUten
 #pragma unroll
           for (int k = 0; k < GEMM_BK / GEMM_UMMA_K; ++k) {
             umma_f16_ss_pair(d_tmem, a_desc + static_cast<uint64_t>(2 * k), b_desc + static_cast<uint64_t>(2 * k),
-                             p.idesc, (kb | k) != 0 ? 1u : 0u);
+                             p.idesc, ((kb - wk.kb0) | k) != 0 ? 1u : 0u);
           }
           umma_commit_pair(&empty_bar[stage]);
           if (++stage == STAGES) {
@@ -229,9 +275,10 @@ gemm2_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUten
     PairCursor cur;
     int acc = 0;
     uint32_t acc_phase = 0;
-    for (int tile = pair_id; tile < total_pair_tiles; tile += num_pairs) {
+    PairWork wk;
+    for (int n = 0; pair_work(p, tail, total_pair_tiles, pair_id, num_pairs, n, wk); ++n) {
       int m2_blk, n_blk;
-      cur.seek(p, tile, m2_blk, n_blk);
+      cur.seek(p, wk.tile, m2_blk, n_blk);
       mbar_wait(&tfull_bar[acc], acc_phase, abort_word, p.timeout_ns);
       tc_fence_after();
       const int grow = m2_blk * GEMM2_BM + static_cast<int>(cta_rank) * GEMM_BM + q * 32 + lane;
@@ -244,7 +291,17 @@ gemm2_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUten
         tmem_ld_32x32(t_row + c * 32, r);
         tmem_ld_wait();
         const int col = col0 + c * 32;
-        if (row_ok) {
+        if (wk.is_slice) {
+          // K slice of a tail tile: add into the fp32 workspace tile
+          const int sl = pair_id % tail.slices;
+          float4* w = reinterpret_cast<float4*>(
+              tail.ws + ((static_cast<size_t>(wk.tile - tail.first_tile) * tail.slices + sl) * GEMM2_BM +
+                         (static_cast<size_t>(cta_rank) * GEMM_BM + q * 32 + lane)) * BN + c * 32);
+#pragma unroll
+          for (int v = 0; v < 8; ++v)
+            __stcg(w + v, make_float4(__uint_as_float(r[v * 4 + 0]), __uint_as_float(r[v * 4 + 1]),
+                                      __uint_as_float(r[v * 4 + 2]), __uint_as_float(r[v * 4 + 3])));
+        } else if (row_ok) {
           uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.c) + (static_cast<size_t>(grow) * p.ldc + col) * 2);
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
@@ -264,6 +321,60 @@ gemm2_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUten
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[acc]), 0));
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
+      if (wk.is_slice) {
+        // arrive; wait (bounded) for the tile's other slices; reduce this CTA's share of the rows
+        const int tl = wk.tile - tail.first_tile;
+        const unsigned int parties = 2u * static_cast<unsigned int>(tail.slices);
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (warp == 4 && lane == 0) {
+          atomicAdd(&tail.count[2 * tl], 1u);
+          const uint64_t t0 = globaltimer_ns();
+          while (ld_acquire_gpu_u32(&tail.count[2 * tl]) < parties) {
+            if (*abort_word != 0) break;
+            if (globaltimer_ns() - t0 > p.timeout_ns) {
+              *abort_word = SYN_DEV_TIMEOUT_COUNTER;
+              break;
+            }
+            __nanosleep(32);
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        __threadfence();
+        const int me = (pair_id % tail.slices) * 2 + static_cast<int>(cta_rank);   // 0 .. parties-1
+        const int r_lo = GEMM2_BM * me / static_cast<int>(parties), r_hi = GEMM2_BM * (me + 1) / static_cast<int>(parties);
+        const int t128 = (warp - 4) * 32 + lane;
+        const size_t slice_stride = static_cast<size_t>(GEMM2_BM) * BN;
+        for (int idx = t128; idx < (r_hi - r_lo) * (BN / 8); idx += 128) {
+          const int rr = r_lo + idx / (BN / 8), cc = idx % (BN / 8);
+          const float* base = tail.ws + (static_cast<size_t>(tl) * tail.slices * GEMM2_BM + rr) * BN + cc * 8;
+          float acc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          for (int sidx = 0; sidx < tail.slices; ++sidx) {
+            const float4 x = __ldcg(reinterpret_cast<const float4*>(base + sidx * slice_stride));
+            const float4 y = __ldcg(reinterpret_cast<const float4*>(base + sidx * slice_stride) + 1);
+            acc8[0] += x.x; acc8[1] += x.y; acc8[2] += x.z; acc8[3] += x.w;
+            acc8[4] += y.x; acc8[5] += y.y; acc8[6] += y.z; acc8[7] += y.w;
+          }
+          const int out_row = m2_blk * GEMM2_BM + rr, col = col0 + cc * 8;
+          if (out_row < p.M && col < p.N) {
+            uint4 u;
+            u.x = pack2(acc8[0], acc8[1], p.dtype);
+            u.y = pack2(acc8[2], acc8[3], p.dtype);
+            u.z = pack2(acc8[4], acc8[5], p.dtype);
+            u.w = pack2(acc8[6], acc8[7], p.dtype);
+            *reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.c) + (static_cast<size_t>(out_row) * p.ldc + col) * 2) = u;
+          }
+        }
+        // the last CTA to finish reading rewinds the tile's counters for the next launch
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (warp == 4 && lane == 0) {
+          const unsigned int old = atomicAdd(&tail.count[2 * tl + 1], 1u);
+          if (old == parties - 1u) {
+            tail.count[2 * tl] = 0;
+            tail.count[2 * tl + 1] = 0;
+          }
+        }
+      }
     }
   }
 

@@ -32,22 +32,55 @@ static long count_tiles(const syn_schedule* s, int M, int N, int bn) {
   return t;
 }
 
-int pick_block_n(const syn_schedule* s, int M, int N, int num_sms, int multiple) {
+// Time of one 64-deep k-block of a tile, in ns, measured on B200 with M = 8192, K = 8192 under load
+// (one-CTA kernel / CTA-pair kernel).  Narrow tiles pay a fixed cost per MMA; the one-CTA kernel
+// at BN = 256 is limited by shared-memory operand traffic, which the pair form halves for B.
+static double kblock_ns(int bn, bool pair) {
+  switch (bn) {
+    case 256: return pair ? 385.0 : 427.0;
+    case 224: return 390.0;
+    case 192: return 344.0;
+    case 160: return 328.0;
+    case 128: return 320.0;
+    case 96: return 300.0;
+    default: return 290.0;
+  }
+}
+
+static bool pair_shape_ok(const syn_schedule* s, int M) {
+  if (s == nullptr) return M % 256 == 0;
+  for (int w = 0; w < s->num_waves; ++w)
+    if ((s->offsets[w * 2] % 256) || (s->shapes[w * 2] % 256)) return false;
+  return true;
+}
+
+// Chooses the tile width (and whether the CTA-pair kernel is used, when `pair_out` is given)
+// with the fewest persistent rounds weighted by the measured k-block time.
+int pick_block_n(const syn_schedule* s, int M, int N, int num_sms, int multiple, bool* pair_out) {
   int best = 0;
+  bool best_pair = false;
   double best_cost = 0;
-  for (int bn : kBlockN) {
-    if (bn % multiple != 0) continue;
-    if (!block_n_ok(s, N, bn)) continue;
-    const long tiles = count_tiles(s, M, N, bn);
-    const long rounds = (tiles + num_sms - 1) / num_sms;
-    // time of a round grows with the tile width; narrow tiles re-read A more often and pay a
-    // larger fixed cost per tile, hence the small bias towards wide tiles
-    const double cost = static_cast<double>(rounds) * (bn + 16);
-    if (best == 0 || cost < best_cost - 1e-9) {
-      best = bn;
-      best_cost = cost;
+  const bool may_pair = pair_out != nullptr && num_sms >= 2 && pair_shape_ok(s, M);
+  for (int use_pair = 0; use_pair <= (may_pair ? 1 : 0); ++use_pair) {
+    for (int bn : kBlockN) {
+      if (bn % multiple != 0) continue;
+      if (!block_n_ok(s, N, bn)) continue;
+      long tiles = count_tiles(s, M, N, bn);
+      long units = num_sms;
+      if (use_pair) {
+        tiles = (tiles + 1) / 2;  // 256-row tiles
+        units = num_sms / 2;
+      }
+      const long rounds = (tiles + units - 1) / units;
+      const double cost = static_cast<double>(rounds) * kblock_ns(bn, use_pair != 0);
+      if (best == 0 || cost < best_cost - 1e-9) {
+        best = bn;
+        best_pair = use_pair != 0;
+        best_cost = cost;
+      }
     }
   }
+  if (pair_out != nullptr) *pair_out = best_pair;
   return best;
 }
 
@@ -165,7 +198,7 @@ static int launch_bn(const GemmParams& p, int grid, cudaStream_t stream) {
 
 template <int BN>
 static int launch_pair_bn(const GemmParams& p, const CUtensorMap& tmap_b_half, int pair_tiles, int grid,
-                          cudaStream_t stream) {
+                          const PairTail& tail, cudaStream_t stream) {
   constexpr int kStage = GEMM_BM * GEMM_BK * 2 + (BN / 2) * GEMM_BK * 2;
   constexpr int kStagesRaw = (232448 - 1024 - 512) / kStage;
   constexpr int STAGES = kStagesRaw > 8 ? 8 : kStagesRaw;
@@ -178,7 +211,7 @@ static int launch_pair_bn(const GemmParams& p, const CUtensorMap& tmap_b_half, i
     SYN_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured_dev = dev;
   }
-  kern<<<grid, GEMM_THREADS, smem, stream>>>(p, tmap_b_half, pair_tiles);
+  kern<<<grid, GEMM_THREADS, smem, stream>>>(p, tmap_b_half, pair_tiles, tail);
   SYN_CUDA_TRY(cudaGetLastError());
   return SYN_OK;
 }
@@ -211,14 +244,31 @@ static int gemm_launch_pair(const GemmParams& p_in, const syn_gemm_args* a, int 
   for (int w = 0; w < p.num_waves; ++w) pair_tiles += (p.waves[w].tiles_m >> 1) * p.waves[w].tiles_n;
   int g = std::min(grid & ~1, 2 * pair_tiles);
   if (g < 2) return SYN_ERR_INVALID;
+  // Tail splitting: a small remainder after the last full round is cut along K over all pairs
+  // instead of occupying a round of its own.  Needs the caller's zeroed workspace.
+  PairTail tail;
+  memset(&tail, 0, sizeof(tail));
+  const int pairs = g / 2;
+  const int rem = pair_tiles % pairs, rounds = pair_tiles / pairs;
+  if (a->workspace != nullptr && rounds >= 1 && rem > 0 && rem * 4 <= pairs) {
+    const int slices = std::min(std::min(pairs / rem, p.k_blocks), 32);
+    const size_t need = 256 + static_cast<size_t>(rem) * slices * GEMM2_BM * bn * sizeof(float);
+    if (slices >= 2 && a->workspace_bytes >= need && (reinterpret_cast<uintptr_t>(a->workspace) & 255) == 0) {
+      tail.tiles = rem;
+      tail.slices = slices;
+      tail.first_tile = rounds * pairs;
+      tail.count = static_cast<unsigned int*>(a->workspace);
+      tail.ws = reinterpret_cast<float*>(static_cast<char*>(a->workspace) + 256);
+    }
+  }
   switch (bn) {
-    case 256: return launch_pair_bn<256>(p, tmap_b_half, pair_tiles, g, stream);
-    case 224: return launch_pair_bn<224>(p, tmap_b_half, pair_tiles, g, stream);
-    case 192: return launch_pair_bn<192>(p, tmap_b_half, pair_tiles, g, stream);
-    case 160: return launch_pair_bn<160>(p, tmap_b_half, pair_tiles, g, stream);
-    case 128: return launch_pair_bn<128>(p, tmap_b_half, pair_tiles, g, stream);
-    case 96: return launch_pair_bn<96>(p, tmap_b_half, pair_tiles, g, stream);
-    case 64: return launch_pair_bn<64>(p, tmap_b_half, pair_tiles, g, stream);
+    case 256: return launch_pair_bn<256>(p, tmap_b_half, pair_tiles, g, tail, stream);
+    case 224: return launch_pair_bn<224>(p, tmap_b_half, pair_tiles, g, tail, stream);
+    case 192: return launch_pair_bn<192>(p, tmap_b_half, pair_tiles, g, tail, stream);
+    case 160: return launch_pair_bn<160>(p, tmap_b_half, pair_tiles, g, tail, stream);
+    case 128: return launch_pair_bn<128>(p, tmap_b_half, pair_tiles, g, tail, stream);
+    case 96: return launch_pair_bn<96>(p, tmap_b_half, pair_tiles, g, tail, stream);
+    case 64: return launch_pair_bn<64>(p, tmap_b_half, pair_tiles, g, tail, stream);
     default: return SYN_ERR_UNSUPPORTED;
   }
 }
@@ -241,13 +291,15 @@ int gemm_launch(const GemmParams& p, int bn, bool fused, int grid, cudaStream_t 
 #undef SYN_BN_CASE
 }
 
-int gemm_resolve_grid_and_bn(const syn_gemm_args* a, const syn_schedule* sched, int* grid, int* bn, int multiple) {
+int gemm_resolve_grid_and_bn(const syn_gemm_args* a, const syn_schedule* sched, int* grid, int* bn, int multiple,
+                             bool* pair_out) {
   int sms = 0;
   int rc = device_sm_count(&sms);
   if (rc != SYN_OK) return rc;
   int g = a->num_sms > 0 ? std::min(a->num_sms, sms) : sms;
   int b = a->block_n;
-  if (b == 0) b = pick_block_n(sched, a->M, a->N, g, multiple);
+  if (pair_out != nullptr) *pair_out = true;  // an explicit tile width leaves the kernel choice to eligibility
+  if (b == 0) b = pick_block_n(sched, a->M, a->N, g, multiple, pair_out);
   if (b == 0 || b % multiple != 0) return SYN_ERR_SHAPE;
   *grid = g;
   *bn = b;
@@ -260,7 +312,7 @@ extern "C" {
 
 int syn_gemm_pick_block_n(int M, int N, int num_sms) {
   if (M <= 0 || N <= 0 || num_sms <= 0) return SYN_ERR_INVALID;
-  return syn::pick_block_n(nullptr, M, N, num_sms, 32);
+  return syn::pick_block_n(nullptr, M, N, num_sms, 32, nullptr);
 }
 
 int syn_gemm(const syn_gemm_args* args, const syn_schedule* sched, const syn_schedule* producer_sched,
@@ -268,7 +320,9 @@ int syn_gemm(const syn_gemm_args* args, const syn_schedule* sched, const syn_sch
   using namespace syn;
   if (args == nullptr) return SYN_ERR_INVALID;
   int grid = 0, bn = 0;
-  int rc = gemm_resolve_grid_and_bn(args, sched ? sched : producer_sched, &grid, &bn);
+  bool want_pair = false;
+  const bool plain = !(producer_sched != nullptr && args->producer_signal_ptr != nullptr) && args->sched_counter == nullptr;
+  int rc = gemm_resolve_grid_and_bn(args, sched ? sched : producer_sched, &grid, &bn, 32, plain ? &want_pair : nullptr);
   if (rc != SYN_OK) return rc;
   const syn_schedule* order = sched ? sched : producer_sched;
   GemmParams p;
@@ -300,7 +354,7 @@ int syn_gemm(const syn_gemm_args* args, const syn_schedule* sched, const syn_sch
       fused = true;
     }
   }
-  if (!fused && pair_eligible(p, bn, grid)) return gemm_launch_pair(p, args, bn, grid, static_cast<cudaStream_t>(stream));
+  if (!fused && want_pair && pair_eligible(p, bn, grid)) return gemm_launch_pair(p, args, bn, grid, static_cast<cudaStream_t>(stream));
   grid = std::min(grid, p.total_tiles);
   if (grid <= 0) return SYN_ERR_INVALID;
   return gemm_launch(p, bn, fused, grid, static_cast<cudaStream_t>(stream));

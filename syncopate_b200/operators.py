@@ -164,7 +164,7 @@ class AllGatherGemm:
             gemm(self.a.local, b, c, self.world, self.num_sms, BLOCK_SIZE_N=self.block_n,
                  cur_wave_sizes=self._wave_sizes, wave_offsets=self._wave_offsets, signal_ptr=self.flags.local,
                  signal_offsets=self._signals, signal_value=self.epoch, status=self.ctx.status,
-                 timeout_ns=self.timeout_ns, sched_counter=self._sched, trace=self.trace, stream=cur)
+                 timeout_ns=self.timeout_ns, trace=self.trace, stream=cur)
             for s in self._copy_streams:
                 cur.wait_stream(s)
             return c
