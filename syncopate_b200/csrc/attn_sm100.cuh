@@ -100,6 +100,12 @@ struct UnitCursor {
   }
 };
 
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // 0 = skip the block (no key visible to any row), 1 = no mask needed, 2 = mask by position.
 __device__ __forceinline__ int block_mode(const AttnParams& p, int qpos0, int kb) {
   if (!p.causal) return 1;
@@ -247,21 +253,24 @@ __global__ void __launch_bounds__(256, 1) attn_kernel(const __grid_constant__ At
         for (int j = 0; j < active; ++j) {
           const uint32_t gi = g + j;
           if (j + 1 < active) issue_qk(gi + 1, qb);
-          // P_j is in tensor memory and the partial-O buffer is free again
+          // P_j is in tensor memory (and O has been rescaled if the row maximum jumped)
           mbar_wait(&p_full[gi & 1u], (gi >> 1) & 1u, abort_word, p.timeout_ns);
-          mbar_wait(&o_empty[gi & 1u], ((gi >> 1) & 1u) ^ 1u, abort_word, p.timeout_ns);
+          if (j == 0) {
+            // the first product of a unit overwrites O: the previous unit's result must have been read
+            mbar_wait(&o_empty[0], (u & 1u) ^ 1u, abort_word, p.timeout_ns);
+          }
           const int st = gi % ATTN_KV_STAGES;
           mbar_wait(&v_full[st], (gi / ATTN_KV_STAGES) & 1u, abort_word, p.timeout_ns);
           tc_fence_after();
-          const uint32_t p_tmem = tmem_base + (gi & 1u) * 128u;         // bf16 pairs over the first 64 columns of S
-          const uint32_t o_tmem = tmem_base + 256u + (gi & 1u) * 128u;
+          const uint32_t p_tmem = tmem_base + (gi & 1u) * 128u;  // bf16 pairs over the first 64 columns of S
+          const uint32_t o_tmem = tmem_base + 256u;
 #pragma unroll
           for (int kk = 0; kk < ATTN_BN / 16; ++kk) {
             // V block in shared memory: [128 keys][64 d] per box, keys are the K axis (128 B apart),
             // d is the contiguous (MN) axis; the second box (d 64..127) lies 16 KB further
             const uint64_t b = make_smem_desc_sw128(smem_u32(sV + st * ATTN_TILE_BYTES + kk * 16 * 128),
                                                     ATTN_TILE_BYTES / 2, 1024);
-            umma_f16_ts(o_tmem, p_tmem + kk * 8, b, p.idesc_pv, kk != 0 ? 1u : 0u);
+            umma_f16_ts(o_tmem, p_tmem + kk * 8, b, p.idesc_pv, (j | kk) != 0 ? 1u : 0u);
           }
           umma_commit(&v_empty[st]);
           umma_commit(&o_full[gi & 1u]);
@@ -284,116 +293,106 @@ __global__ void __launch_bounds__(256, 1) attn_kernel(const __grid_constant__ At
     UnitCursor cur;
     int z, h, qt;
     uint32_t g = 0;
-    float o_acc[ATTN_D];
+    uint32_t u = 0;  // units processed (parity of the O hand-over barrier)
     while (cur.next(p, z, h, qt)) {
       const AttnWave& w = p.waves[cur.wave];
       const int qpos0 = p.q_pos ? __ldg(p.q_pos + qt) : qt * ATTN_BM;
       int active = 0;
       for (int kb = w.kb0; kb < w.kb1; ++kb) active += block_mode(p, qpos0, kb) != 0;
       if (active == 0) continue;
+      // m: maximum the stored P and O are scaled by; it follows the true row maximum lazily (only
+      // when that has grown by more than 2^8), so that O in tensor memory is rarely rescaled
       float m = -INFINITY, l = 0.f;
-#pragma unroll
-      for (int i = 0; i < ATTN_D; ++i) o_acc[i] = 0.f;
+      const uint32_t o_tmem = lane_base + 256u;
       int j = 0;
       for (int kb = w.kb0; kb < w.kb1; ++kb) {
         const int mode = block_mode(p, qpos0, kb);
         if (mode == 0) continue;
         const uint32_t gi = g + j;
         const uint32_t s_tmem = lane_base + (gi & 1u) * 128u;
-        // keys 0..lim of the block are visible to this row
-        int lim = ATTN_BN - 1;
+        int lim = ATTN_BN - 1;  // keys 0..lim of the block are visible to this row
         if (mode == 2) {
           const int kpos0 = p.kv_pos ? __ldg(p.kv_pos + kb) : kb * ATTN_BN;
           lim = min(ATTN_BN - 1, qpos0 + row - kpos0);
         }
         mbar_wait(&s_full[gi & 1u], (gi >> 1) & 1u, abort_word, p.timeout_ns);
         tc_fence_after();
-        // pass 1: row maximum
-        float mx = -INFINITY;
-#pragma unroll 1
+        // all of S for this row in one go: four loads in flight, one wait
+        uint32_t sr[ATTN_BN / 32][32];
+#pragma unroll
+        for (int c = 0; c < ATTN_BN / 32; ++c) tmem_ld_32x32(s_tmem + c * 32, sr[c]);
+        tmem_ld_wait();
+        float mx_raw = -INFINITY;
+#pragma unroll
         for (int c = 0; c < ATTN_BN / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(s_tmem + c * 32, r);
-          tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            const float s = __uint_as_float(r[i]);
-            if (c * 32 + i <= lim) mx = fmaxf(mx, s);
+            if (mode == 2 && c * 32 + i > lim) sr[c][i] = 0xff800000u;  // -inf
+            mx_raw = fmaxf(mx_raw, __uint_as_float(sr[c][i]));
           }
         }
-        const float m_new = fmaxf(m, mx * p.scale_log2);
-        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-        const float alpha = exp2f(m - m_use);  // 0 when nothing was accumulated yet
-        // pass 2: probabilities, written over S as 16-bit pairs
-        float l_part = 0.f;
+        const float mx = mx_raw * p.scale_log2;  // the scale is positive
+        // the previous product must be complete before O may be rescaled and P overwritten
+        if (j > 0) {
+          const uint32_t gp = gi - 1;
+          mbar_wait(&o_full[gp & 1u], (gp >> 1) & 1u, abort_word, p.timeout_ns);
+          tc_fence_after();
+        }
+        if (mx > m + 8.f) {
+          // (first block, or the maximum jumped) move the reference point and rescale O and l
+          if (j > 0 && m != -INFINITY) {
+            const float alpha = exp2f(m - mx);
 #pragma unroll 1
+            for (int c = 0; c < ATTN_D / 32; ++c) {
+              uint32_t r[32];
+              tmem_ld_32x32(o_tmem + c * 32, r);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+              tmem_st_32x32(o_tmem + c * 32, r);
+            }
+            tmem_st_wait();
+            l *= alpha;
+          }
+          m = mx;
+        }
+        const float neg_m = (m == -INFINITY) ? 0.f : -m;
+        float l_part = 0.f;
+#pragma unroll
         for (int c = 0; c < ATTN_BN / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(s_tmem + c * 32, r);
-          tmem_ld_wait();
           uint32_t pk[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
-            float p0 = exp2f(__uint_as_float(r[2 * i]) * p.scale_log2 - m_use);
-            float p1 = exp2f(__uint_as_float(r[2 * i + 1]) * p.scale_log2 - m_use);
-            if (c * 32 + 2 * i > lim) p0 = 0.f;
-            if (c * 32 + 2 * i + 1 > lim) p1 = 0.f;
+            const float p0 = ex2_approx(fmaf(__uint_as_float(sr[c][2 * i]), p.scale_log2, neg_m));
+            const float p1 = ex2_approx(fmaf(__uint_as_float(sr[c][2 * i + 1]), p.scale_log2, neg_m));
             l_part += p0 + p1;
             pk[i] = pack2(p0, p1, p.dtype);
           }
           tmem_st_32x16(s_tmem + c * 16, pk);
         }
+        l += l_part;
         tmem_st_wait();
         tc_fence_before();
         mbar_arrive(&p_full[gi & 1u]);
-        // fold in the partial O of the previous block (computed relative to the old maximum)
-        if (j > 0) {
-          const uint32_t gp = gi - 1;
-          mbar_wait(&o_full[gp & 1u], (gp >> 1) & 1u, abort_word, p.timeout_ns);
-          tc_fence_after();
-          const uint32_t o_tmem = lane_base + 256u + (gp & 1u) * 128u;
-#pragma unroll
-          for (int c = 0; c < ATTN_D / 32; ++c) {
-            uint32_t r[32];
-            tmem_ld_32x32(o_tmem + c * 32, r);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] += __uint_as_float(r[i]);
-          }
-          tc_fence_before();
-          mbar_arrive(&o_empty[gp & 1u]);
-        }
-#pragma unroll
-        for (int i = 0; i < ATTN_D; ++i) o_acc[i] *= alpha;
-        l = l * alpha + l_part;
-        m = m_new;
         ++j;
       }
+      // the unit's last product
       {
         const uint32_t gp = g + active - 1;
         mbar_wait(&o_full[gp & 1u], (gp >> 1) & 1u, abort_word, p.timeout_ns);
         tc_fence_after();
-        const uint32_t o_tmem = lane_base + 256u + (gp & 1u) * 128u;
-#pragma unroll
-        for (int c = 0; c < ATTN_D / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32(o_tmem + c * 32, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o_acc[c * 32 + i] += __uint_as_float(r[i]);
-        }
-        tc_fence_before();
-        mbar_arrive(&o_empty[gp & 1u]);
       }
       g += active;
 
-      // ---- finalise this visit and merge with what earlier waves left for the row
-      const int srow = qt * ATTN_BM + row;
-      if (srow < p.Sq) {
-        const size_t stat_idx = (static_cast<size_t>(z) * p.Hq + h) * p.Sq + srow;
+      // ---- finalise this visit and merge with what earlier waves left for the row.  Every lane runs
+      // the loop (the tensor-memory loads are warp-wide); rows past the end only skip memory accesses.
+      {
+        const int srow = qt * ATTN_BM + row;
+        const bool valid = srow < p.Sq;
+        const size_t stat_idx = (static_cast<size_t>(z) * p.Hq + h) * p.Sq + (valid ? srow : 0);
         uint4* o_ptr = reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.o) +
-                                                (z * p.o_sz + h * p.o_sh + static_cast<int64_t>(srow) * p.o_ss) * 2);
-        const bool seen = p.visit[stat_idx] == p.epoch;
+                                                (z * p.o_sz + h * p.o_sh + static_cast<int64_t>(valid ? srow : 0) * p.o_ss) * 2);
+        const bool seen = valid && p.visit[stat_idx] == p.epoch;
         float lse_new = (l > 0.f) ? m + log2f(l) : -INFINITY;
         const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
         float w_new = inv_l, w_old = 0.f;
@@ -411,31 +410,45 @@ __global__ void __launch_bounds__(256, 1) attn_kernel(const __grid_constant__ At
             lse_new = mm + log2f(tot);
           }
         }
+#pragma unroll 1
+        for (int v = 0; v < ATTN_D / 32; ++v) {
+          uint32_t r[32];
+          tmem_ld_32x32(o_tmem + v * 32, r);
+          tmem_ld_wait();
+          if (valid) {
 #pragma unroll
-        for (int v = 0; v < ATTN_D / 8; ++v) {
-          float f[8];
+            for (int c4 = 0; c4 < 4; ++c4) {
+              float f[8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) f[i] = o_acc[v * 8 + i] * w_new;
-          if (seen) {
-            const uint4 old = o_ptr[v];
-            const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
+              for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(r[c4 * 8 + i]) * w_new;
+              if (seen) {
+                const uint4 old = o_ptr[v * 4 + c4];
+                const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float2 t = unpack2(ow[i], p.dtype);
-              f[2 * i] += t.x * w_old;
-              f[2 * i + 1] += t.y * w_old;
+                for (int i = 0; i < 4; ++i) {
+                  const float2 t = unpack2(ow[i], p.dtype);
+                  f[2 * i] += t.x * w_old;
+                  f[2 * i + 1] += t.y * w_old;
+                }
+              }
+              uint4 out;
+              out.x = pack2(f[0], f[1], p.dtype);
+              out.y = pack2(f[2], f[3], p.dtype);
+              out.z = pack2(f[4], f[5], p.dtype);
+              out.w = pack2(f[6], f[7], p.dtype);
+              o_ptr[v * 4 + c4] = out;
             }
           }
-          uint4 out;
-          out.x = pack2(f[0], f[1], p.dtype);
-          out.y = pack2(f[2], f[3], p.dtype);
-          out.z = pack2(f[4], f[5], p.dtype);
-          out.w = pack2(f[6], f[7], p.dtype);
-          o_ptr[v] = out;
         }
-        p.lse[stat_idx] = lse_new;
-        p.visit[stat_idx] = p.epoch;
+        if (valid) {
+          p.lse[stat_idx] = lse_new;
+          p.visit[stat_idx] = p.epoch;
+        }
       }
+      // O has been read: the next unit's first product may overwrite it
+      tc_fence_before();
+      mbar_arrive(&o_empty[0]);
+      ++u;
     }
   }
 
