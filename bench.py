@@ -436,7 +436,11 @@ def run_own_arm(args):
                     "path": "pinned host A -> device shard, device barrier, fused op, C -> pinned host"},
             "gpu_launches": args.steps,
             "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peak, "unit": "TFLOP/s",
-                         "frac": per_gpu / peak, "traffic": None,
+                         "frac": per_gpu / peak,
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this
+                         # workload (ncu capture summarised in profiles/gemm2_kernel_bn256_cfg1_tp8_local.md)
+                         "traffic": 605.4e6 if world == 1 else None,
+                         "algorithmic_bytes": (M * K_DIM + n_local * K_DIM + M * n_local) * 2,
                          "peak_source": f"{peaks['source']} cuBLAS bf16 burst (MEASURED_PEAKS.json)",
                          "frac_of_sustained": per_gpu / peaks["bf16_tflops_sustained"] if peaks["bf16_tflops_sustained"] else None,
                          "frac_of_nominal_2250": per_gpu / 2250.0,
