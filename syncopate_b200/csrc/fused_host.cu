@@ -19,6 +19,16 @@ static bool dynamic_sched() {
   return cached == 1;
 }
 
+// SYNCOPATE_B200_RS_WIDE=0 keeps the 64-column (128-byte segment) store boxes in GEMM + reduce-scatter.
+static bool rs_wide_store() {
+  static int cached = -1;
+  if (cached < 0) {
+    const char* e = getenv("SYNCOPATE_B200_RS_WIDE");
+    cached = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return cached == 1;
+}
+
 static int check_symm(const syn_symm& s) {
   if (s.world <= 0 || s.world > SYN_MAX_WORLD || s.rank < 0 || s.rank >= s.world) return SYN_ERR_INVALID;
   for (int r = 0; r < s.world; ++r)
@@ -140,6 +150,8 @@ int syn_gemm_rs(const syn_gemm_rs_args* args, const syn_schedule* src_sched, con
   rc = gemm_fill_common(&p, &g, src_sched, bn);
   if (rc != SYN_OK) return rc;
   const uint64_t epoch = p.signal_value;
+  const bool wide = rs_wide_store() && bn % 128 == 0;
+  p.wide_store = wide ? 1 : 0;
   int tmap_of_rank[SYN_MAX_WORLD];
   for (int r = 0; r < SYN_MAX_WORLD; ++r) tmap_of_rank[r] = -1;
   int n_maps = 0;
@@ -177,7 +189,8 @@ int syn_gemm_rs(const syn_gemm_rs_args* args, const syn_schedule* src_sched, con
     rt.ld = slab_ld;
     // tiles leave through shared memory and TMA stores: one output map per destination slab
     if (tmap_of_rank[tgt] < 0) {
-      rc = encode_tmap_2d_sw128(&p.tmap_out[n_maps], slab0, slab_rows, g.N, slab_ld, GEMM_BM, 64);
+      rc = wide ? encode_tmap_2d_plain(&p.tmap_out[n_maps], slab0, slab_rows, g.N, slab_ld, 64, 128)
+                : encode_tmap_2d_sw128(&p.tmap_out[n_maps], slab0, slab_rows, g.N, slab_ld, GEMM_BM, 64);
       if (rc != SYN_OK) return rc;
       tmap_of_rank[tgt] = n_maps++;
     }

@@ -77,6 +77,7 @@ struct GemmParams {
   int32_t total_tiles;
   int32_t num_waves;
   int32_t num_comm_ops;
+  int32_t wide_store;     // 1: TMA-store routes send 64-row x 128-column boxes (256-byte row segments)
   int32_t num_red;        // staged partial slabs to add in `reduce` routes
   int32_t red_ld;
   int32_t red_row0;       // global C row of the staged slabs' row 0
@@ -490,7 +491,29 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
         }
         bool staged = false;
         if constexpr (FUSED) {
-          if (tmap_idx >= 0) {
+          if (tmap_idx >= 0 && p.wide_store) {
+            staged = true;
+            // 128-column groups leave as two 64-row boxes with 256-byte row segments (longer
+            // segments travel better over NVLink); rows 0-63 use the first 16 KB of the staging
+            // space, rows 64-127 the second, no swizzle
+            uint8_t* sbuf = ring + (srow >> 6) * (64 * 256);
+            if ((c & 3) == 0) {
+              if (leader) bulk_wait_read<0>();
+              asm volatile("bar.sync 1, 128;" ::: "memory");
+            }
+#pragma unroll
+            for (int v = 0; v < 4; ++v)
+              *reinterpret_cast<uint4*>(sbuf + (srow & 63) * 256 + (c & 3) * 64 + v * 16) = packed[v];
+            if ((c & 3) == 3) {
+              fence_proxy_async_smem();
+              asm volatile("bar.sync 1, 128;" ::: "memory");
+              if (leader) {
+                tma_store_2d(&p.tmap_out[tmap_idx], ring, col0 + (c >> 2) * 128, tmap_y);
+                tma_store_2d(&p.tmap_out[tmap_idx], ring + 64 * 256, col0 + (c >> 2) * 128, tmap_y + 64);
+                bulk_commit();
+              }
+            }
+          } else if (tmap_idx >= 0) {
             staged = true;
             // 64-column halves of the tile go through two 16 KB staging buffers (the comm ring's
             // space, which a routed epilogue does not otherwise use), laid out with the 128-byte

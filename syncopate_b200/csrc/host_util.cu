@@ -67,6 +67,29 @@ int encode_tmap_2d_sw128(CUtensorMap* out, const void* base, uint64_t rows, uint
   return SYN_OK;
 }
 
+int encode_tmap_2d_plain(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                         uint32_t box_rows, uint32_t box_cols) {
+  encode_tiled_fn fn = get_encode_tiled();
+  if (fn == nullptr) {
+    set_cuda_error("cudaGetDriverEntryPoint(cuTensorMapEncodeTiled)", "not available");
+    return SYN_ERR_CUDA;
+  }
+  cuuint64_t gdim[2] = {cols, rows};
+  cuuint64_t gstride[1] = {ld * 2};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim, gstride, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    char buf[64];
+    snprintf(buf, sizeof(buf), "CUresult %d", static_cast<int>(r));
+    set_cuda_error("cuTensorMapEncodeTiled(2d plain)", buf);
+    return SYN_ERR_CUDA;
+  }
+  return SYN_OK;
+}
+
 int encode_tmap_3d_sw128(CUtensorMap* out, const void* base, uint64_t d2, uint64_t rows, uint64_t cols,
                          uint64_t stride2, uint64_t ld, uint32_t box_rows, uint32_t box_cols) {
   encode_tiled_fn fn = get_encode_tiled();

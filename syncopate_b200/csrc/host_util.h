@@ -27,6 +27,9 @@ int device_sm_count(int* out);
 // elements with the 128-byte swizzle the UMMA shared-memory descriptors expect.
 int encode_tmap_2d_sw128(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
                          uint32_t box_rows, uint32_t box_cols);
+// Same tensor without swizzle (rows of box_cols elements laid out back to back in shared memory).
+int encode_tmap_2d_plain(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
+                         uint32_t box_rows, uint32_t box_cols);
 // 3-D variant: [d2, rows, cols] with strides (stride2, ld, 1) in elements.
 int encode_tmap_3d_sw128(CUtensorMap* out, const void* base, uint64_t d2, uint64_t rows, uint64_t cols,
                          uint64_t stride2, uint64_t ld, uint32_t box_rows, uint32_t box_cols);

@@ -53,6 +53,23 @@ def test_local_gemm_matches_oracle(M, N, K, bn, dtype, status):
     assert _rel(c, ref) < TOL
 
 
+def test_pair_kernel_with_split_tail(status):
+    """76 tiles of 256 x 256 on 74 CTA pairs: one full round, the two left-over tiles are cut along K
+    over all pairs and reduced through the fp32 workspace; twice, to see the workspace counters rewind."""
+    from syncopate_b200.computation.gemm import gemm
+
+    M, N, K = 4864, 1024, 2048
+    a, b = _seeded(7, (M, K), 1.0, torch.bfloat16), _seeded(8, (N, K), 0.02, torch.bfloat16)
+    ref = a.float() @ b.float().t()
+    ad, bd = a.cuda(), b.cuda()
+    for _ in range(2):
+        c = torch.zeros(M, N, dtype=torch.bfloat16, device="cuda")
+        gemm(ad, bd, c, BLOCK_SIZE_N=256, status=status)
+        torch.cuda.synchronize()
+        assert status.tolist() == [0, 0, 0, 0]
+        assert _rel(c, ref) < TOL
+
+
 def test_gemm_rejects_bad_arguments(status):
     from syncopate_b200 import _lib as L
     from syncopate_b200.computation.gemm import gemm
