@@ -147,6 +147,8 @@ extern "C" int syn_attention(const syn_attn_args* a, const syn_schedule* sched, 
   rc = device_sm_count(&sms);
   if (rc != SYN_OK) return rc;
   const int grid = a->num_sms > 0 ? (a->num_sms < sms ? a->num_sms : sms) : sms;
+  const long pairs = static_cast<long>(a->Z) * a->Hq * ((p.q_tiles + 1) / 2);
+  p.own_pairs = (p.causal && pairs >= 2L * grid) ? 1 : 0;
   return fused ? launch_attn<true>(p, grid, static_cast<cudaStream_t>(stream))
                : launch_attn<false>(p, grid, static_cast<cudaStream_t>(stream));
 }

@@ -42,6 +42,7 @@ struct AttnParams {
   int32_t Z, Hq, Hkv, Sq, Skv;
   int32_t q_tiles;         // ceil(Sq / 128)
   int32_t causal;
+  int32_t own_pairs;       // causal runs with enough tiles: query tiles are owned in balanced pairs
   int32_t dtype;
   int32_t epoch;
   int32_t num_waves;
@@ -60,33 +61,45 @@ struct AttnParams {
 };
 
 // Enumerates, in wave order, the units this CTA owns.  All roles run the same enumeration.
+// Ownership is fixed for the whole launch.  Non-causal: query tile qt of head (z, h) belongs to CTA
+// ((z * Hq + h) * T + qt) mod grid.  Causal: tiles are owned in pairs {j, T-1-j} (tile t has about
+// t + 1 visible key blocks, so every pair carries the same work) and pair j of head (z, h)
+// belongs to CTA ((z * Hq + h) * ceil(T / 2) + j) mod grid (only when there are at least two pairs per CTA).
 struct UnitCursor {
-  int wave = 0, zi = 0, hi = 0, qt = -1;
-  bool wave_started = false;
-  bool new_wave = false;  // set when the returned unit is the CTA's first of its wave
+  int wave = 0, zi = 0, hi = 0, slot = -1, half = 0;
   __device__ __forceinline__ bool next(const AttnParams& p, int& z, int& h, int& qtile) {
-    const int G = gridDim.x, c = blockIdx.x;
+    const int G = gridDim.x, c = blockIdx.x, T = p.q_tiles;
+    const int slots = p.own_pairs ? (T + 1) / 2 : T;
     while (wave < p.num_waves) {
       const AttnWave& w = p.waves[wave];
       while (zi < w.nz) {
         while (hi < w.nh) {
           const int zz = w.z0 + zi, hh = w.h0 + hi;
-          if (qt < 0) {
-            const long base = (static_cast<long>(zz) * p.Hq + hh) * p.q_tiles;
-            const int r = static_cast<int>(((c - base) % G + G) % G);  // residue the tile index must have
-            qt = w.q0t + ((r - w.q0t) % G + G) % G;
-          } else {
-            qt += G;
+          while (true) {
+            if (slot < 0) {
+              const long base = (static_cast<long>(zz) * p.Hq + hh) * slots;
+              slot = static_cast<int>(((c - base) % G + G) % G);  // first slot of this head owned by the CTA
+              half = 0;
+            } else if (p.own_pairs && half == 0) {
+              half = 1;
+            } else {
+              slot += G;
+              half = 0;
+            }
+            if (slot >= slots) break;
+            int qt = slot;
+            if (p.own_pairs && half == 1) {
+              qt = T - 1 - slot;
+              if (qt == slot) continue;  // the middle tile of an odd count is its own partner
+            }
+            if (qt >= w.q0t && qt < w.q0t + w.nqt) {
+              z = zz;
+              h = hh;
+              qtile = qt;
+              return true;
+            }
           }
-          if (qt < w.q0t + w.nqt) {
-            z = zz;
-            h = hh;
-            qtile = qt;
-            new_wave = !wave_started;
-            wave_started = true;
-            return true;
-          }
-          qt = -1;
+          slot = -1;
           ++hi;
         }
         hi = 0;
@@ -94,7 +107,6 @@ struct UnitCursor {
       }
       zi = 0;
       ++wave;
-      wave_started = false;
     }
     return false;
   }
