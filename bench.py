@@ -287,8 +287,8 @@ def run_own_arm(args):
     def e2e_step():
         if world > 1:
             op.shard.copy_(a_host, non_blocking=True)
-            # peers may only pull the new shard once it has landed: device-side barrier, then the op
-            ctx.barrier()
+            # peers may only pull the new shard once it has landed: the operator's own device-side
+            # barrier at the start of the call takes care of that
         else:
             a_full.copy_(a_host, non_blocking=True)
         step()

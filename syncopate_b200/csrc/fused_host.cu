@@ -19,12 +19,13 @@ static bool dynamic_sched() {
   return cached == 1;
 }
 
-// SYNCOPATE_B200_RS_WIDE=0 keeps the 64-column (128-byte segment) store boxes in GEMM + reduce-scatter.
+// SYNCOPATE_B200_RS_WIDE=1 sends 128-column (256-byte segment) store boxes in GEMM + reduce-scatter
+// instead of the 64-column swizzled ones; measured no faster at 8 GPUs, so it is off by default.
 static bool rs_wide_store() {
   static int cached = -1;
   if (cached < 0) {
     const char* e = getenv("SYNCOPATE_B200_RS_WIDE");
-    cached = (e != nullptr && e[0] == '0') ? 0 : 1;
+    cached = (e != nullptr && e[0] == '1') ? 1 : 0;
   }
   return cached == 1;
 }

@@ -85,13 +85,18 @@ class AllGatherGemm:
 
     def __init__(self, ctx: SymmetricContext, rows_per_rank: int, K: int, N: int, dtype=torch.bfloat16,
                  plan: str = "swizzle", num_sms: int = 0, block_n: int = 0, timeout_ns: int = 0, comm: str = "sm",
-                 copy_streams: int = 2):
+                 copy_streams: int = 2, lockstep: bool = True):
         self.ctx = ctx
         self.world, self.rank = ctx.world, ctx.rank
         self.rows, self.K, self.N, self.dtype = rows_per_rank, K, N, dtype
         self.M = rows_per_rank * self.world
         self.num_sms, self.block_n, self.timeout_ns = num_sms, block_n, timeout_ns
         self.comm = comm
+        # The swizzled order gives every rank a different peer at every step only while the ranks
+        # move in step; free-running ranks drift, two of them then load the same peer's link and
+        # the transfers slow down.  A device-side barrier (about 11 us) at the start of each call
+        # keeps them aligned and costs less than it saves at 8 GPUs.
+        self.lockstep = lockstep
         self.generator, self.info, lowered = plan_all_gather(self.world, rows_per_rank, K, dtype, plan,
                                                              copy_engine=(comm == "ce"))
         self.schedule = lowered[self.rank]["a"]
@@ -158,6 +163,8 @@ class AllGatherGemm:
         if self.world == 1:
             return gemm(self.a.local, b, c, 1, self.num_sms, BLOCK_SIZE_N=self.block_n, status=self.ctx.status,
                         timeout_ns=self.timeout_ns, stream=stream)
+        if self.lockstep:
+            self.ctx.barrier(stream)
         if self.comm == "ce":
             cur = stream or torch.cuda.current_stream()
             self._issue_copies(cur)
@@ -177,8 +184,9 @@ class GemmReduceScatter:
     """``out[M / world, N] = sum over ranks of (A_r[M, K_r] @ B_r[N, K_r]^T)[own rows]``."""
 
     def __init__(self, ctx: SymmetricContext, M: int, N: int, dtype=torch.bfloat16, plan: str = "direct",
-                 num_sms: int = 0, block_n: int = 0, timeout_ns: int = 0):
+                 num_sms: int = 0, block_n: int = 0, timeout_ns: int = 0, lockstep: bool = True):
         self.ctx = ctx
+        self.lockstep = lockstep  # see AllGatherGemm: keeps the ranks' push targets disjoint in time
         self.world, self.rank = ctx.world, ctx.rank
         self.M, self.N, self.dtype = M, N, dtype
         self.slab = M // self.world
@@ -201,6 +209,8 @@ class GemmReduceScatter:
         if self.world == 1:
             return gemm(a, b, out, 1, self.num_sms, BLOCK_SIZE_N=self.block_n, status=self.ctx.status,
                         timeout_ns=self.timeout_ns, stream=stream)
+        if self.lockstep:
+            self.ctx.barrier(stream)
         return gemm_rs(a, b, out, self.src_schedule, self.dst_schedule, self.remote_signals, self.stage.symm,
                        self.flags.symm, self.counters, epoch=self.epoch, num_sms=self.num_sms,
                        block_n=self.block_n, timeout_ns=self.timeout_ns, status=self.ctx.status, stream=stream)
