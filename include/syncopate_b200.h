@@ -272,7 +272,34 @@ typedef struct syn_attn_args {
   uint64_t signal_value; /* 0 = 1 */
   uint64_t timeout_ns;   /* 0 = 2 s */
   int32_t* status;
+  const struct syn_attn_plan* plan; /* NULL, or a work-balanced ownership made by syn_attention_plan for
+                                       exactly these shapes, waves, positions and num_sms */
 } syn_attn_args;
+
+/* Which CTA owns which unit of query rows for a whole launch (fixed ownership is what makes the
+ * merge over waves lock-free).  Without a plan ownership is arithmetic (unit id modulo grid, or
+ * balanced pairs for causal runs); that leaves CTAs unevenly loaded when each holds only a few
+ * units of different length.  A plan assigns units longest-first to the least loaded CTA, the
+ * weight of a unit being the key blocks it visits over all waves.  The reference balances the same
+ * work dynamically with a tile counter and a lock per query tile
+ * (syncopate/computation/attn/template.py:80-121, :339-349). */
+#define SYN_ATTN_PLAN_MAX_GRID 160
+#define SYN_ATTN_PLAN_MAX_UNITS 1024
+typedef struct syn_attn_plan {
+  int32_t grid;       /* CTAs the plan was made for */
+  int32_t unit_rows;  /* query rows per unit (128 or 256) */
+  int32_t num_units;  /* Z * Hq * ceil(Sq / unit_rows) */
+  uint16_t start[SYN_ATTN_PLAN_MAX_GRID + 1]; /* CTA c owns units[start[c] .. start[c + 1]) */
+  uint16_t units[SYN_ATTN_PLAN_MAX_UNITS];    /* unit id = (z * Hq + h) * units_per_head + index */
+} syn_attn_plan;
+
+/* Fills `out` for the launch that `args` + `sched` describe (pointers to tensors are not used).
+ * `q_pos_host` / `kv_pos_host` are host copies of args->q_pos / args->kv_pos (NULL where those are
+ * NULL).  Host work proportional to units x waves x key blocks: call once per configuration and
+ * keep the result.  SYN_ERR_TOO_LARGE when there are more units than the plan holds (arithmetic
+ * ownership balances such launches well enough). */
+int syn_attention_plan(const syn_attn_args* args, const syn_schedule* sched, const int32_t* q_pos_host,
+                       const int32_t* kv_pos_host, syn_attn_plan* out);
 
 /* One 2-D strided copy for the kernel's comm warps: `rows` rows of `row_bytes` bytes from
  * bufs[src_buf].ptrs[src_rank] + src_offset (pitch src_pitch) to bufs[dst_buf].ptrs[dst_rank] +

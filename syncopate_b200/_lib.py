@@ -16,6 +16,7 @@ LIB_PATH = os.environ.get("SYNCOPATE_B200_LIB") or os.path.join(_HERE, "libsynco
 SYN_MAX_WORLD = 8
 SYN_DTYPE_F16 = 0
 SYN_DTYPE_BF16 = 1
+SYN_ERR_TOO_LARGE = -9
 
 ERRORS = {
     0: "SYN_OK",
@@ -155,6 +156,23 @@ class AttnArgs(C.Structure):
         ("signal_value", C.c_uint64),
         ("timeout_ns", C.c_uint64),
         ("status", C.c_void_p),
+        ("plan", C.c_void_p),
+    ]
+
+
+ATTN_PLAN_MAX_GRID = 160
+ATTN_PLAN_MAX_UNITS = 1024
+
+
+class AttnPlan(C.Structure):
+    """``syn_attn_plan``."""
+
+    _fields_ = [
+        ("grid", C.c_int32),
+        ("unit_rows", C.c_int32),
+        ("num_units", C.c_int32),
+        ("start", C.c_uint16 * (ATTN_PLAN_MAX_GRID + 1)),
+        ("units", C.c_uint16 * ATTN_PLAN_MAX_UNITS),
     ]
 
 
@@ -244,6 +262,9 @@ def _declare(l: C.CDLL) -> None:
     l.syn_copy.argtypes = [C.POINTER(AttnComm), C.c_int, C.c_uint64, C.c_uint64, C.c_void_p, C.c_void_p]
     l.syn_attention.restype = C.c_int
     l.syn_attention.argtypes = [C.POINTER(AttnArgs), C.POINTER(Schedule), C.POINTER(AttnComm), C.c_void_p]
+    l.syn_attention_plan.restype = C.c_int
+    l.syn_attention_plan.argtypes = [C.POINTER(AttnArgs), C.POINTER(Schedule), C.c_void_p, C.c_void_p,
+                                     C.POINTER(AttnPlan)]
     l.syn_gemm_rs.restype = C.c_int
     l.syn_gemm_rs.argtypes = [C.POINTER(GemmRsArgs), C.POINTER(Schedule), C.POINTER(Schedule), C.c_void_p]
 

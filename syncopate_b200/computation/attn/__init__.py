@@ -5,11 +5,13 @@ a signal array with one flag index per wave, and an optional output buffer.
 
 Additions of this backend: ``causal`` with true-position tables (``q_pos`` / ``kv_pos`` per 128 rows /
 keys), grouped-query heads (``k`` / ``v`` may have fewer heads than ``q``), and an ``AttentionState``
-that keeps the LSE / visit scratch between calls.
+that keeps the LSE / visit scratch between calls.  The work-balanced ownership plans
+(``syn_attention_plan``) of the configurations seen so far are kept in a small module-level cache.
 """
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Optional, Sequence
 
 import torch
@@ -47,6 +49,29 @@ def _tolist(x):
     return x
 
 
+_PLANS: dict = {}  # configuration key -> AttnPlan, or None where the library declined to plan
+_PLANS_MAX = 256
+
+
+def _owner_plan(a: L.AttnArgs, sched, key, q_pos, kv_pos):
+    """The ownership plan for this configuration, made on first use (host work, one device-to-host
+    copy of the position tables) and kept."""
+    if key not in _PLANS:
+        if len(_PLANS) >= _PLANS_MAX:
+            _PLANS.pop(next(iter(_PLANS)))
+        qh = q_pos.detach().to("cpu", torch.int32).contiguous() if q_pos is not None else None
+        kh = kv_pos.detach().to("cpu", torch.int32).contiguous() if kv_pos is not None else None
+        plan = L.AttnPlan()
+        rc = L.lib().syn_attention_plan(C.byref(a), C.byref(sched), qh.data_ptr() if qh is not None else None,
+                                        kh.data_ptr() if kh is not None else None, C.byref(plan))
+        if rc == L.SYN_ERR_TOO_LARGE:
+            plan = None  # more units than a plan holds: arithmetic ownership
+        else:
+            L.check(rc, "syn_attention_plan")
+        _PLANS[key] = plan
+    return _PLANS[key]
+
+
 def attention_forward(
     q: torch.Tensor,
     k: torch.Tensor,
@@ -72,11 +97,14 @@ def attention_forward(
     timeout_ns: int = 0,
     status=None,
     stream=None,
+    balance: bool = True,
 ) -> torch.Tensor:
     """``softmax(q k^T * sm_scale) v`` over the given waves.  ``q`` ``[Z, Hq, Sq, 128]``, ``k`` / ``v``
     ``[Z, Hkv, Skv, 128]`` (any strides with the head dimension contiguous).  Without wave
     metadata one wave covers everything.  ``cum_wave_sizes``, ``NUM_WAVES``, ``cum_tiles`` and
     ``counter_ptr`` are accepted for signature compatibility (they follow from the waves).
+    ``balance`` plans a work-balanced ownership of the query tiles on the first call of a
+    configuration and reuses it afterwards.
     Returns the output (``output_buffer`` if given)."""
     for name, t in (("q", q), ("k", k), ("v", v)):
         if not t.is_cuda or t.dtype not in _DTYPES:
@@ -106,6 +134,12 @@ def attention_forward(
     if offs is None:
         offs, sizes = [[0, 0, 0, 0]], [[Z, Hq, Sq, Skv]]
     sched, keep = L.make_schedule(offs, sizes, _tolist(signal_offsets), ndim=4)
+    if balance:
+        key = (os.environ.get("SYNCOPATE_B200_ATTN_TWO_TILE"), Z, Hq, Hkv, Sq, Skv, bool(causal), num_sms, tuple(map(tuple, offs)), tuple(map(tuple, sizes)),
+               None if q_pos is None else (q_pos.data_ptr(), q_pos._version),
+               None if kv_pos is None else (kv_pos.data_ptr(), kv_pos._version))
+        plan = _owner_plan(a, sched, key, q_pos, kv_pos)
+        a.plan = C.addressof(plan) if plan is not None else None
     if stream is None:
         stream = torch.cuda.current_stream()
     rc = L.lib().syn_attention(C.byref(a), C.byref(sched), C.byref(comm) if comm is not None else None,

@@ -1,0 +1,511 @@
+// Two-tile form of the flash-attention forward kernel: a CTA works on two adjacent 128-row query
+// tiles (A = 2u, B = 2u + 1) at a time.  They share every K / V block brought into shared memory,
+// and each has a softmax warpgroup of its own, so two warps per scheduler overlap each other's
+// exponentials, conversions and tensor-memory traffic, and the tensor pipe runs one tile's
+// products while the other tile is in its softmax.
+//
+// Same semantics as attn_kernel (waves in order, flags, causal masking by true positions, grouped
+// heads, log-sum-exp merge over waves by fixed ownership); the ownership unit is the tile pair.
+//
+// Tensor memory (512 columns): S_A 0..127, S_B 128..255, O_A 256..383, O_B 384..511; P overwrites
+// the first 64 columns of its S.  A tile has ONE S buffer: its next S = Q K^T is issued right after
+// its P V, and the other tile's work fills the tensor pipe meanwhile.  Issue order per key block j:
+//   wait P_A(j); O_A += P_A(j) V(j); S_A = Q_A K(j+1)^T;   wait P_B(j); O_B += P_B(j) V(j); S_B = Q_B K(j+1)^T
+// The commit that publishes S_X(j+1) follows P_X(j) V(j) in issue order, so a softmax thread that
+// sees S full knows the previous product into O_X has completed and may rescale O_X at once.
+//
+// Roles (384 threads): warp 0 TMA producer, warp 1 MMA issuer, warp 2 TMEM allocator, warp 3 comm
+// warp (optional), warps 4-7 softmax of tile A, warps 8-11 softmax of tile B.  The first warpgroup
+// gives registers up (setmaxnreg) so that a softmax thread can hold a whole row of S.
+#pragma once
+#include "attn_sm100.cuh"
+
+namespace syn {
+
+constexpr int ATTN2_THREADS = 384;
+
+// What one tile of the pair does in one wave.
+struct TileRole {
+  bool in_wave;
+  int qt;      // query tile index
+  int qpos0;   // true position of its first row
+};
+__device__ __forceinline__ TileRole tile_role(const AttnParams& p, const AttnWave& w, int qt) {
+  TileRole t;
+  t.qt = qt;
+  t.in_wave = qt >= w.q0t && qt < w.q0t + w.nqt;
+  t.qpos0 = !t.in_wave ? 0 : (p.q_pos ? __ldg(p.q_pos + qt) : qt * ATTN_BM);
+  return t;
+}
+__device__ __forceinline__ int tile_mode(const AttnParams& p, const TileRole& t, int kb) {
+  return t.in_wave ? block_mode(p, t.qpos0, kb) : 0;
+}
+// First key block at or after `from` that either tile needs (-1 = none), with both tiles' modes.
+__device__ __forceinline__ int next_shared_block(const AttnParams& p, const AttnWave& w, const TileRole& a,
+                                                 const TileRole& b, int from, int& ma, int& mb) {
+  for (int kb = from; kb < w.kb1; ++kb) {
+    ma = tile_mode(p, a, kb);
+    mb = tile_mode(p, b, kb);
+    if ((ma | mb) != 0) return kb;
+  }
+  ma = mb = 0;
+  return -1;
+}
+
+// Packed pairs of fp32 (one 64-bit register) for the two-wide fp32 instructions of sm_100.
+__device__ __forceinline__ uint64_t f2_pack(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void f2_unpack(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t f2_fma(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
+  uint64_t d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+template <bool FUSED, bool BF16>
+__global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_constant__ AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;                                        // tile A, tile B
+  uint8_t* sK = sQ + 2 * ATTN_TILE_BYTES;                    // ATTN_KV_STAGES blocks
+  uint8_t* sV = sK + ATTN_KV_STAGES * ATTN_TILE_BYTES;       // ATTN_KV_STAGES blocks
+  uint8_t* ring = sV + ATTN_KV_STAGES * ATTN_TILE_BYTES;     // FUSED only
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ring + (FUSED ? COMM_NBUF * COMM_PIECE : 0));
+  uint64_t* q_full = bars;            // [2] per tile
+  uint64_t* q_empty = bars + 2;       // [2]
+  uint64_t* k_full = bars + 4;        // [KV_STAGES]
+  uint64_t* k_empty = bars + 6;
+  uint64_t* v_full = bars + 8;
+  uint64_t* v_empty = bars + 10;
+  uint64_t* s_full = bars + 12;       // [2] per tile, MMA -> softmax
+  uint64_t* p_full = bars + 14;       // [2][2] per tile and half of P (keys 0..63 / 64..127), softmax -> MMA
+  uint64_t* o_full = bars + 18;       // [2] per tile, MMA -> softmax, once per unit
+  uint64_t* o_empty = bars + 20;      // [2] per tile, softmax -> MMA, once per unit
+  uint64_t* comm_bar = bars + 22;     // [COMM_NBUF]
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 22 + COMM_NBUF);
+  volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_holder + 1);
+  int* abort_info = const_cast<int*>(abort_word) + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&q_full[i], 1);
+      mbar_init(&q_empty[i], 1);
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_full[2 * i], 128);
+      mbar_init(&p_full[2 * i + 1], 128);
+      mbar_init(&o_full[i], 1);
+      mbar_init(&o_empty[i], 128);
+    }
+    for (int i = 0; i < COMM_NBUF; ++i) mbar_init(&comm_bar[i], 1);
+    *abort_word = 0;
+    abort_info[0] = -1;
+    abort_info[1] = -1;
+    fence_mbar_init();
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_holder, 512);
+    tmem_relinquish();
+  }
+  if (warp == 0 && lane == 0) {
+    prefetch_tmap(&p.tmap_q);
+    prefetch_tmap(&p.tmap_k);
+    prefetch_tmap(&p.tmap_v);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  const int group = p.Hq / p.Hkv;
+
+  if (warp < 4) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      UnitCursor cur;
+      cur.shift = 1;
+      int z, h, un;
+      uint32_t uq[2] = {0, 0};  // units each tile has taken part in (parity of its Q barriers)
+      uint32_t g = 0;           // shared key blocks loaded so far (ring position)
+      int flag_wave = -1;
+      while (cur.next(p, z, h, un)) {
+        if (*abort_word != 0) break;
+        const AttnWave& w = p.waves[cur.wave];
+        const TileRole ta = tile_role(p, w, 2 * un), tb = tile_role(p, w, 2 * un + 1);
+        int act[2] = {0, 0};
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
+          act[0] += tile_mode(p, ta, kb) != 0;
+          act[1] += tile_mode(p, tb, kb) != 0;
+        }
+        if (act[0] + act[1] == 0) continue;
+        if (cur.wave != flag_wave && w.sig >= 0 && p.flags != nullptr) {
+          flag_wave = cur.wave;
+          if (!flag_wait_ge(p.flags + w.sig, p.signal_value, abort_word, p.timeout_ns)) {
+            if (abort_info[0] < 0) {
+              abort_info[0] = cur.wave;
+              abort_info[1] = w.sig;
+            }
+          }
+          fence_proxy_async();
+        }
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          if (act[x] == 0) continue;
+          const int qt = 2 * un + x;
+          mbar_wait(&q_empty[x], (uq[x] & 1u) ^ 1u, abort_word, p.timeout_ns);
+          mbar_expect_tx(&q_full[x], ATTN_TILE_BYTES);
+          tma_load_4d(sQ + x * ATTN_TILE_BYTES, &p.tmap_q, &q_full[x], 0, qt * ATTN_BM, h, z);
+          tma_load_4d(sQ + x * ATTN_TILE_BYTES + ATTN_TILE_BYTES / 2, &p.tmap_q, &q_full[x], 64, qt * ATTN_BM, h, z);
+          ++uq[x];
+        }
+        const int hk = h / group;
+        int ma, mb;
+        for (int kb = next_shared_block(p, w, ta, tb, w.kb0, ma, mb); kb >= 0;
+             kb = next_shared_block(p, w, ta, tb, kb + 1, ma, mb)) {
+          const int st = g % ATTN_KV_STAGES;
+          const uint32_t par = ((g / ATTN_KV_STAGES) & 1u) ^ 1u;
+          mbar_wait(&k_empty[st], par, abort_word, p.timeout_ns);
+          mbar_expect_tx(&k_full[st], ATTN_TILE_BYTES);
+          tma_load_4d(sK + st * ATTN_TILE_BYTES, &p.tmap_k, &k_full[st], 0, kb * ATTN_BN, hk, z);
+          tma_load_4d(sK + st * ATTN_TILE_BYTES + ATTN_TILE_BYTES / 2, &p.tmap_k, &k_full[st], 64, kb * ATTN_BN, hk, z);
+          mbar_wait(&v_empty[st], par, abort_word, p.timeout_ns);
+          mbar_expect_tx(&v_full[st], ATTN_TILE_BYTES);
+          tma_load_4d(sV + st * ATTN_TILE_BYTES, &p.tmap_v, &v_full[st], 0, kb * ATTN_BN, hk, z);
+          tma_load_4d(sV + st * ATTN_TILE_BYTES + ATTN_TILE_BYTES / 2, &p.tmap_v, &v_full[st], 64, kb * ATTN_BN, hk, z);
+          ++g;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      UnitCursor cur;
+      cur.shift = 1;
+      int z, h, un;
+      uint32_t uq[2] = {0, 0};  // units per tile (Q and O barriers)
+      uint32_t cb[2] = {0, 0};  // key blocks per tile (S and P barriers)
+      uint32_t g = 0;           // shared key blocks (K / V ring)
+      // S_x = Q_x K^T for the block in K stage `st`
+      auto issue_qk = [&](int x, int st) {
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(x) * 128u;
+#pragma unroll
+        for (int kk = 0; kk < ATTN_D / 16; ++kk) {
+          const uint32_t half = (kk >> 2) * (ATTN_TILE_BYTES / 2);
+          const uint64_t a = make_smem_desc_sw128(smem_u32(sQ + x * ATTN_TILE_BYTES + half), 16, 1024) + 2 * (kk & 3);
+          const uint64_t b = make_smem_desc_sw128(smem_u32(sK + st * ATTN_TILE_BYTES + half), 16, 1024) + 2 * (kk & 3);
+          umma_f16_ss(d_tmem, a, b, p.idesc_qk, kk != 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[x]);
+      };
+      // O_x (+)= P_x V for one half (64 keys) of the block in V stage `st`
+      auto issue_pv = [&](int x, int st, int half, bool accumulate) {
+        const uint32_t p_tmem = tmem_base + static_cast<uint32_t>(x) * 128u;
+        const uint32_t o_tmem = tmem_base + 256u + static_cast<uint32_t>(x) * 128u;
+#pragma unroll
+        for (int k4 = 0; k4 < ATTN_BN / 32; ++k4) {
+          const int kk = half * (ATTN_BN / 32) + k4;
+          // V block: [128 keys][64 d] per box, keys are the K axis (128 B apart), d is the contiguous
+          // (MN) axis; the second box (d 64..127) lies 16 KB further
+          const uint64_t b = make_smem_desc_sw128(smem_u32(sV + st * ATTN_TILE_BYTES + kk * 16 * 128),
+                                                  ATTN_TILE_BYTES / 2, 1024);
+          umma_f16_ts(o_tmem, p_tmem + kk * 8, b, p.idesc_pv, (accumulate || kk != 0) ? 1u : 0u);
+        }
+      };
+      while (cur.next(p, z, h, un)) {
+        if (*abort_word != 0) break;
+        const AttnWave& w = p.waves[cur.wave];
+        const TileRole tr[2] = {tile_role(p, w, 2 * un), tile_role(p, w, 2 * un + 1)};
+        int act[2] = {0, 0};
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
+          act[0] += tile_mode(p, tr[0], kb) != 0;
+          act[1] += tile_mode(p, tr[1], kb) != 0;
+        }
+        if (act[0] + act[1] == 0) continue;
+#pragma unroll
+        for (int x = 0; x < 2; ++x)
+          if (act[x]) mbar_wait(&q_full[x], uq[x] & 1u, abort_word, p.timeout_ns);
+        int m[2], n[2];
+        int kb = next_shared_block(p, w, tr[0], tr[1], w.kb0, m[0], m[1]);
+        // the unit's first block: both tiles' S
+        {
+          const int st = g % ATTN_KV_STAGES;
+          mbar_wait(&k_full[st], (g / ATTN_KV_STAGES) & 1u, abort_word, p.timeout_ns);
+          tc_fence_after();
+          if (m[0]) issue_qk(0, st);
+          if (m[1]) issue_qk(1, st);
+          umma_commit(&k_empty[st]);
+        }
+        bool started[2] = {false, false};
+        while (kb >= 0) {
+          const int kn = next_shared_block(p, w, tr[0], tr[1], kb + 1, n[0], n[1]);
+          const int st = g % ATTN_KV_STAGES, st_n = (g + 1) % ATTN_KV_STAGES;
+          const uint32_t par = (g / ATTN_KV_STAGES) & 1u, par_n = ((g + 1) / ATTN_KV_STAGES) & 1u;
+          bool v_ready = false;
+#pragma unroll
+          for (int x = 0; x < 2; ++x) {
+            if (m[x]) {
+              mbar_wait(&p_full[2 * x], cb[x] & 1u, abort_word, p.timeout_ns);
+              if (!started[x]) {
+                // the first product of a unit overwrites O_x: the previous unit's result must have been read
+                mbar_wait(&o_empty[x], (uq[x] & 1u) ^ 1u, abort_word, p.timeout_ns);
+              }
+              if (!v_ready) {
+                mbar_wait(&v_full[st], par, abort_word, p.timeout_ns);
+                v_ready = true;
+              }
+              tc_fence_after();
+              issue_pv(x, st, 0, started[x]);
+              mbar_wait(&p_full[2 * x + 1], cb[x] & 1u, abort_word, p.timeout_ns);
+              tc_fence_after();
+              issue_pv(x, st, 1, true);
+              ++cb[x];
+              started[x] = true;
+            }
+            if (x == 1) umma_commit(&v_empty[st]);  // both tiles' products with this V block are issued
+            if (kn >= 0 && n[x]) {
+              mbar_wait(&k_full[st_n], par_n, abort_word, p.timeout_ns);
+              tc_fence_after();
+              issue_qk(x, st_n);
+            }
+            // the next K block is free once its last user has been issued: tile B if it takes part
+            if (kn >= 0 && ((x == 0 && !n[1]) || (x == 1 && n[1]))) umma_commit(&k_empty[st_n]);
+          }
+          kb = kn;
+          m[0] = n[0];
+          m[1] = n[1];
+          ++g;
+        }
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          if (act[x]) {
+            umma_commit(&o_full[x]);
+            umma_commit(&q_empty[x]);
+            ++uq[x];
+          }
+        }
+      }
+    }
+  } else if (warp == 3) {
+    if constexpr (FUSED) {
+      comm_warp_run(p.comm, p.num_comm_ops, p.counters, p.signal_value, reinterpret_cast<char*>(ring), comm_bar,
+                    abort_word, p.timeout_ns, lane);
+    }
+  }
+  } else {
+    // ------------------------------------------------------------ softmax / accumulate / merge / store
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+    const int x = (warp >= 8) ? 1 : 0;  // which tile of the pair
+    const int q = warp & 3;
+    const int row = q * 32 + lane;      // query row inside the tile, also the TMEM lane
+    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+    const uint32_t s_tmem = lane_base + static_cast<uint32_t>(x) * 128u;
+    const uint32_t o_tmem = lane_base + 256u + static_cast<uint32_t>(x) * 128u;
+    UnitCursor cur;
+    cur.shift = 1;
+    int z, h, un;
+    uint32_t cbx = 0;  // key blocks this tile has processed (S / P barrier parity)
+    uint32_t ux = 0;   // units this tile has taken part in
+    while (cur.next(p, z, h, un)) {
+      if (*abort_word != 0) break;
+      const AttnWave& w = p.waves[cur.wave];
+      const TileRole t = tile_role(p, w, 2 * un + x);
+      int active = 0;
+      for (int kb = w.kb0; kb < w.kb1; ++kb) active += tile_mode(p, t, kb) != 0;
+      if (active == 0) continue;
+      const int qt = t.qt, qpos0 = t.qpos0;
+      // m: maximum the stored P and O are scaled by; it follows the true row maximum lazily (only
+      // when that has grown by more than 2^8), so that O in tensor memory is rarely rescaled
+      float m = -INFINITY, l = 0.f;
+      int j = 0;
+      for (int kb = w.kb0; kb < w.kb1; ++kb) {
+        const int mode = block_mode(p, qpos0, kb);
+        if (mode == 0) continue;
+        int lim = ATTN_BN - 1;  // keys 0..lim of the block are visible to this row
+        if (mode == 2) {
+          const int kpos0 = p.kv_pos ? __ldg(p.kv_pos + kb) : kb * ATTN_BN;
+          lim = min(ATTN_BN - 1, qpos0 + row - kpos0);
+        }
+        mbar_wait(&s_full[x], cbx & 1u, abort_word, p.timeout_ns);
+        ++cbx;
+        tc_fence_after();
+        uint32_t sr[ATTN_BN / 32][32];
+#pragma unroll
+        for (int c = 0; c < ATTN_BN / 32; ++c) tmem_ld_32x32(s_tmem + c * 32, sr[c]);
+        tmem_ld_wait();
+        if (mode == 2) {
+#pragma unroll
+          for (int c = 0; c < ATTN_BN / 32; ++c) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (c * 32 + i > lim) sr[c][i] = 0xff800000u;  // -inf
+          }
+        }
+        // four independent chains of three-input maxima
+        float mxs[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int c = 0; c < ATTN_BN / 32; ++c) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            mxs[i & 3] = fmax3(mxs[i & 3], __uint_as_float(sr[c][2 * i]), __uint_as_float(sr[c][2 * i + 1]));
+        }
+        const float mx_raw = fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3]));
+        const float mx = mx_raw * p.scale_log2;  // the scale is positive
+        if (mx > m + 8.f) {
+          // (first block, or the maximum jumped) move the reference point and rescale O and l; the
+          // previous product into O has completed (its commit precedes the one that published S)
+          if (j > 0 && m != -INFINITY) {
+            const float alpha = exp2f(m - mx);
+#pragma unroll 1
+            for (int c = 0; c < ATTN_D / 32; ++c) {
+              uint32_t r[32];
+              tmem_ld_32x32(o_tmem + c * 32, r);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+              tmem_st_32x32(o_tmem + c * 32, r);
+            }
+            l *= alpha;
+          }
+          m = mx;
+        }
+        const float neg_m = (m == -INFINITY) ? 0.f : -m;
+        // P = 2^(S * scale - m), two elements per instruction where the hardware allows; the two
+        // halves of P (keys 0..63, 64..127) are handed over separately, so that the product with
+        // the first half of V runs while the second half is still being exponentiated
+        const uint64_t scale2 = f2_pack(p.scale_log2, p.scale_log2), negm2 = f2_pack(neg_m, neg_m);
+        uint64_t ls2[2] = {0ull, 0ull};  // packed (0.f, 0.f)
+#pragma unroll
+        for (int c = 0; c < ATTN_BN / 32; ++c) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            float x0, x1;
+            f2_unpack(f2_fma(f2_pack(__uint_as_float(sr[c][2 * i]), __uint_as_float(sr[c][2 * i + 1])), scale2, negm2),
+                      x0, x1);
+            const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+            ls2[i & 1] = f2_add(ls2[i & 1], f2_pack(p0, p1));
+            pk[i] = BF16 ? pack2_bf16(p0, p1) : pack2_f16(p0, p1);
+          }
+          tmem_st_32x16(s_tmem + c * 16, pk);
+          if (c & 1) {
+            tmem_st_wait();
+            tc_fence_before();
+            mbar_arrive(&p_full[2 * x + (c >> 1)]);
+          }
+        }
+        {
+          float a0, a1, b0, b1;
+          f2_unpack(ls2[0], a0, a1);
+          f2_unpack(ls2[1], b0, b1);
+          l += (a0 + a1) + (b0 + b1);
+        }
+        ++j;
+      }
+      // the unit's last product into O_x
+      mbar_wait(&o_full[x], ux & 1u, abort_word, p.timeout_ns);
+      tc_fence_after();
+
+      // ---- finalise this visit and merge with what earlier waves left for the row.  Every lane runs
+      // the loop (the tensor-memory loads are warp-wide); rows past the end only skip memory accesses.
+      {
+        const int srow = qt * ATTN_BM + row;
+        const bool valid = srow < p.Sq;
+        const size_t stat_idx = (static_cast<size_t>(z) * p.Hq + h) * p.Sq + (valid ? srow : 0);
+        uint4* o_ptr = reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.o) +
+                                                (z * p.o_sz + h * p.o_sh + static_cast<int64_t>(valid ? srow : 0) * p.o_ss) * 2);
+        const bool seen = valid && p.visit[stat_idx] == p.epoch;
+        float lse_new = (l > 0.f) ? m + log2f(l) : -INFINITY;
+        const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
+        float w_new = inv_l, w_old = 0.f;
+        if (seen) {
+          const float lse_old = p.lse[stat_idx];
+          const float mm = fmaxf(lse_old, lse_new);
+          if (mm == -INFINITY) {
+            w_new = 0.f;
+            w_old = 1.f;
+          } else {
+            const float e_old = exp2f(lse_old - mm), e_new = exp2f(lse_new - mm);
+            const float tot = e_old + e_new;
+            w_old = e_old / tot;
+            w_new = e_new / tot * inv_l;
+            lse_new = mm + log2f(tot);
+          }
+        }
+#pragma unroll 1
+        for (int v = 0; v < ATTN_D / 32; ++v) {
+          uint32_t r[32];
+          tmem_ld_32x32(o_tmem + v * 32, r);
+          tmem_ld_wait();
+          if (valid) {
+#pragma unroll
+            for (int c4 = 0; c4 < 4; ++c4) {
+              float f[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(r[c4 * 8 + i]) * w_new;
+              if (seen) {
+                const uint4 old = o_ptr[v * 4 + c4];
+                const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const float2 tt = unpack2(ow[i], p.dtype);
+                  f[2 * i] += tt.x * w_old;
+                  f[2 * i + 1] += tt.y * w_old;
+                }
+              }
+              uint4 out;
+              out.x = BF16 ? pack2_bf16(f[0], f[1]) : pack2_f16(f[0], f[1]);
+              out.y = BF16 ? pack2_bf16(f[2], f[3]) : pack2_f16(f[2], f[3]);
+              out.z = BF16 ? pack2_bf16(f[4], f[5]) : pack2_f16(f[4], f[5]);
+              out.w = BF16 ? pack2_bf16(f[6], f[7]) : pack2_f16(f[6], f[7]);
+              o_ptr[v * 4 + c4] = out;
+            }
+          }
+        }
+        if (valid) {
+          p.lse[stat_idx] = lse_new;
+          p.visit[stat_idx] = p.epoch;
+        }
+      }
+      // O_x has been read: the next unit's first product may overwrite it
+      tc_fence_before();
+      mbar_arrive(&o_empty[x]);
+      ++ux;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+  if (threadIdx.x == 0 && *abort_word != 0 && p.status != nullptr) {
+    if (atomicCAS(p.status, 0, *abort_word) == 0) {
+      p.status[1] = abort_info[0];
+      p.status[2] = abort_info[1];
+      p.status[3] = static_cast<int>(blockIdx.x);
+    }
+  }
+}
+
+}  // namespace syn

@@ -15,6 +15,7 @@
 // softmax / accumulate / merge / store (thread t owns query row t of the tile).
 #pragma once
 #include "gemm_sm100.cuh"  // CommOp, comm_warp_run, pack helpers
+#include "../../include/syncopate_b200.h"  // plan limits
 
 namespace syn {
 
@@ -58,6 +59,9 @@ struct AttnParams {
   uint32_t idesc_qk, idesc_pv;
   AttnWave waves[ATTN_MAX_WAVES];
   CommOp comm[ATTN_MAX_COMM_OPS];
+  int32_t use_lists;       // 1: ownership comes from the lists below instead of the arithmetic rule
+  uint16_t own_start[SYN_ATTN_PLAN_MAX_GRID + 1];
+  uint16_t own_units[SYN_ATTN_PLAN_MAX_UNITS];
 };
 
 // Enumerates, in wave order, the units this CTA owns.  All roles run the same enumeration.
@@ -65,10 +69,35 @@ struct AttnParams {
 // ((z * Hq + h) * T + qt) mod grid.  Causal: tiles are owned in pairs {j, T-1-j} (tile t has about
 // t + 1 visible key blocks, so every pair carries the same work) and pair j of head (z, h)
 // belongs to CTA ((z * Hq + h) * ceil(T / 2) + j) mod grid (only when there are at least two pairs per CTA).
+//
+// `shift` = 1 makes the unit a run of two adjacent query tiles (2 * unit, 2 * unit + 1), for the
+// kernel that works on two tiles at a time; a wave then touches every such run it overlaps.
 struct UnitCursor {
-  int wave = 0, zi = 0, hi = 0, slot = -1, half = 0;
+  int wave = 0, zi = 0, hi = 0, slot = -1, half = 0, shift = 0;
   __device__ __forceinline__ bool next(const AttnParams& p, int& z, int& h, int& qtile) {
-    const int G = gridDim.x, c = blockIdx.x, T = p.q_tiles;
+    const int G = gridDim.x, c = blockIdx.x, T = (p.q_tiles + (1 << shift) - 1) >> shift;
+    if (p.use_lists) {
+      // planned ownership: walk this CTA's list once per wave (`slot` is the list position)
+      const int first = p.own_start[c], last = p.own_start[c + 1];
+      if (slot < 0) slot = first;
+      while (wave < p.num_waves) {
+        const AttnWave& w = p.waves[wave];
+        const int lo = w.q0t >> shift, hi = (w.q0t + w.nqt - 1) >> shift;
+        while (slot < last) {
+          const int id = p.own_units[slot++];
+          const int u = id % T, zh = id / T, hh = zh % p.Hq, zz = zh / p.Hq;
+          if (u >= lo && u <= hi && hh >= w.h0 && hh < w.h0 + w.nh && zz >= w.z0 && zz < w.z0 + w.nz) {
+            z = zz;
+            h = hh;
+            qtile = u;
+            return true;
+          }
+        }
+        slot = first;
+        ++wave;
+      }
+      return false;
+    }
     const int slots = p.own_pairs ? (T + 1) / 2 : T;
     while (wave < p.num_waves) {
       const AttnWave& w = p.waves[wave];
@@ -92,7 +121,7 @@ struct UnitCursor {
               qt = T - 1 - slot;
               if (qt == slot) continue;  // the middle tile of an odd count is its own partner
             }
-            if (qt >= w.q0t && qt < w.q0t + w.nqt) {
+            if (qt >= (w.q0t >> shift) && qt <= ((w.q0t + w.nqt - 1) >> shift)) {
               z = zz;
               h = hh;
               qtile = qt;
@@ -127,7 +156,16 @@ __device__ __forceinline__ int block_mode(const AttnParams& p, int qpos0, int kb
   return 2;
 }
 
-template <bool FUSED>
+__device__ __forceinline__ uint32_t pack2_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ uint32_t pack2_f16(float lo, float hi) {
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <bool FUSED, bool BF16>
 __global__ void __launch_bounds__(256, 1) attn_kernel(const __grid_constant__ AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -334,25 +372,30 @@ __global__ void __launch_bounds__(256, 1) attn_kernel(const __grid_constant__ At
 #pragma unroll
         for (int c = 0; c < ATTN_BN / 32; ++c) tmem_ld_32x32(s_tmem + c * 32, sr[c]);
         tmem_ld_wait();
-        float mx_raw = -INFINITY;
+        // eight independent chains: a single running maximum would serialise 128 dependent operations
+        float mxs[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) mxs[i] = -INFINITY;
 #pragma unroll
         for (int c = 0; c < ATTN_BN / 32; ++c) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             if (mode == 2 && c * 32 + i > lim) sr[c][i] = 0xff800000u;  // -inf
-            mx_raw = fmaxf(mx_raw, __uint_as_float(sr[c][i]));
+            mxs[i & 7] = fmaxf(mxs[i & 7], __uint_as_float(sr[c][i]));
           }
         }
+        const float mx_raw = fmaxf(fmaxf(fmaxf(mxs[0], mxs[1]), fmaxf(mxs[2], mxs[3])),
+                                   fmaxf(fmaxf(mxs[4], mxs[5]), fmaxf(mxs[6], mxs[7])));
         const float mx = mx_raw * p.scale_log2;  // the scale is positive
-        // the previous product must be complete before O may be rescaled and P overwritten
-        if (j > 0) {
-          const uint32_t gp = gi - 1;
-          mbar_wait(&o_full[gp & 1u], (gp >> 1) & 1u, abort_word, p.timeout_ns);
-          tc_fence_after();
-        }
         if (mx > m + 8.f) {
           // (first block, or the maximum jumped) move the reference point and rescale O and l
           if (j > 0 && m != -INFINITY) {
+            // the previous product accumulates into O: it must be complete before O is touched.
+            // (Nothing else needs this wait: by the time S of this block is full, every product
+            // before the previous one has completed, and P of this block has a buffer of its own.)
+            const uint32_t gp = gi - 1;
+            mbar_wait(&o_full[gp & 1u], (gp >> 1) & 1u, abort_word, p.timeout_ns);
+            tc_fence_after();
             const float alpha = exp2f(m - mx);
 #pragma unroll 1
             for (int c = 0; c < ATTN_D / 32; ++c) {
@@ -369,7 +412,7 @@ __global__ void __launch_bounds__(256, 1) attn_kernel(const __grid_constant__ At
           m = mx;
         }
         const float neg_m = (m == -INFINITY) ? 0.f : -m;
-        float l_part = 0.f;
+        float ls[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int c = 0; c < ATTN_BN / 32; ++c) {
           uint32_t pk[16];
@@ -377,12 +420,12 @@ __global__ void __launch_bounds__(256, 1) attn_kernel(const __grid_constant__ At
           for (int i = 0; i < 16; ++i) {
             const float p0 = ex2_approx(fmaf(__uint_as_float(sr[c][2 * i]), p.scale_log2, neg_m));
             const float p1 = ex2_approx(fmaf(__uint_as_float(sr[c][2 * i + 1]), p.scale_log2, neg_m));
-            l_part += p0 + p1;
-            pk[i] = pack2(p0, p1, p.dtype);
+            ls[i & 3] += p0 + p1;
+            pk[i] = BF16 ? pack2_bf16(p0, p1) : pack2_f16(p0, p1);
           }
           tmem_st_32x16(s_tmem + c * 16, pk);
         }
-        l += l_part;
+        l += (ls[0] + ls[1]) + (ls[2] + ls[3]);
         tmem_st_wait();
         tc_fence_before();
         mbar_arrive(&p_full[gi & 1u]);
@@ -444,10 +487,10 @@ __global__ void __launch_bounds__(256, 1) attn_kernel(const __grid_constant__ At
                 }
               }
               uint4 out;
-              out.x = pack2(f[0], f[1], p.dtype);
-              out.y = pack2(f[2], f[3], p.dtype);
-              out.z = pack2(f[4], f[5], p.dtype);
-              out.w = pack2(f[6], f[7], p.dtype);
+              out.x = BF16 ? pack2_bf16(f[0], f[1]) : pack2_f16(f[0], f[1]);
+              out.y = BF16 ? pack2_bf16(f[2], f[3]) : pack2_f16(f[2], f[3]);
+              out.z = BF16 ? pack2_bf16(f[4], f[5]) : pack2_f16(f[4], f[5]);
+              out.w = BF16 ? pack2_bf16(f[6], f[7]) : pack2_f16(f[6], f[7]);
               o_ptr[v * 4 + c4] = out;
             }
           }

@@ -16,6 +16,14 @@ TOL = 2e-2
 DT = torch.bfloat16
 
 
+@pytest.fixture(autouse=True, params=["one_tile", "two_tile"])
+def kernel_choice(request, monkeypatch):
+    """Every test runs once with the one-tile kernel and once with the two-tile kernel forced
+    (the library would pick by problem size; the test shapes are small)."""
+    monkeypatch.setenv("SYNCOPATE_B200_ATTN_TWO_TILE", "0" if request.param == "one_tile" else "2")
+    return request.param
+
+
 def _seeded(seed, shape):
     g = torch.Generator().manual_seed(seed)
     return torch.randn(*shape, generator=g, dtype=torch.float32).to(DT)
@@ -35,6 +43,9 @@ def _dense(q, k, v, causal, q_pos=None, k_pos=None):
         (1, 2, 2, 512, 512, True),
         (2, 8, 2, 384, 640, False),   # grouped-query heads, sizes that are not powers of two
         (1, 4, 1, 256, 256, True),
+        (1, 2, 2, 384, 384, True),    # odd number of query tiles: the last pair has one tile
+        (1, 2, 1, 300, 256, False),   # ragged last tile
+        (1, 3, 3, 1280, 1280, True),  # several units per CTA at 148 SMs only when planned per unit
     ],
 )
 def test_attention_matches_oracle(Z, Hq, Hkv, Sq, Skv, causal):
@@ -70,6 +81,33 @@ def test_waves_merge_partial_results_and_lse():
         assert torch.allclose(st.lse[0].cpu() * 0.6931471805599453, lse, atol=2e-3, rtol=1e-4)
 
 
+def test_waves_that_start_on_odd_tiles():
+    """Waves whose query ranges start or end inside a tile pair: each tile of a pair takes part
+    only in the waves that cover it."""
+    from syncopate_b200.computation.attn import AttentionState, attention_forward
+
+    Z, H, S = 1, 2, 512
+    q, k, v = _seeded(14, (Z, H, S, 128)), _seeded(15, (Z, H, S, 128)), _seeded(16, (Z, H, S, 128))
+    offs = [[0, 0, 128, 0], [0, 0, 0, 0], [0, 0, 384, 0]]
+    sizes = [[1, 2, 256, 512], [1, 2, 128, 512], [1, 2, 128, 512]]
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    o = attention_forward(q.cuda(), k.cuda(), v.cuda(), 128 ** -0.5, wave_offsets=offs, wave_sizes=sizes,
+                          causal=True, state=AttentionState(Z, H, S, "cuda"), status=status, timeout_ns=300_000_000)
+    torch.cuda.synchronize()
+    assert status.tolist() == [0, 0, 0, 0]
+    assert (o.float().cpu() - _dense(q, k, v, True)).abs().max().item() < TOL
+
+
+def test_planned_and_arithmetic_ownership_agree():
+    from syncopate_b200.computation.attn import attention_forward
+
+    q, k, v = (_seeded(20 + i, (1, 4, 1024, 128)).cuda() for i in range(3))
+    a = attention_forward(q, k, v, 128 ** -0.5, causal=True, balance=True, timeout_ns=300_000_000)
+    b = attention_forward(q, k, v, 128 ** -0.5, causal=True, balance=False, timeout_ns=300_000_000)
+    torch.cuda.synchronize()
+    assert torch.equal(a, b)   # same arithmetic per row whoever owns the tile
+
+
 def test_strided_layouts_and_output_buffer():
     """BSHD inputs (head stride < sequence stride) and a caller-provided BSHD output."""
     from syncopate_b200.computation.attn import attention_forward
@@ -88,10 +126,10 @@ def test_strided_layouts_and_output_buffer():
 def test_flag_gated_wave_times_out_cleanly():
     from syncopate_b200.computation.attn import attention_forward
 
-    q = torch.zeros(1, 1, 128, 128, dtype=DT, device="cuda")
+    q = torch.zeros(1, 1, 256, 128, dtype=DT, device="cuda")
     flags = torch.zeros(1, dtype=torch.int64, device="cuda")
     status = torch.zeros(4, dtype=torch.int32, device="cuda")
-    attention_forward(q, q, q, 1.0, wave_offsets=[[0, 0, 0, 0]], wave_sizes=[[1, 1, 128, 128]], signal_ptr=flags,
+    attention_forward(q, q, q, 1.0, wave_offsets=[[0, 0, 0, 0]], wave_sizes=[[1, 1, 256, 256]], signal_ptr=flags,
                       signal_offsets=[0], status=status, timeout_ns=1_000_000)
     torch.cuda.synchronize()
     assert status.tolist()[:3] == [1, 0, 0]   # flag timeout on wave 0 / flag 0, nothing hung

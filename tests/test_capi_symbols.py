@@ -55,3 +55,25 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(L, "LIB_PATH", str(tmp_path / "nope.so"))
     with pytest.raises(RuntimeError, match="no CPU or PyTorch fallback"):
         L.lib()
+
+
+def test_attention_plan_balances_causal_units_without_a_gpu():
+    """The ownership planner is host code: for the per-rank Ulysses shape (4 heads, 32768 causal
+    tokens, 148 CTAs) every unit is owned exactly once and the heaviest CTA carries at most 8 %
+    more key blocks than the average."""
+    from syncopate_b200 import _lib as L
+
+    a = L.AttnArgs()
+    a.Z, a.Hq, a.Hkv, a.Sq, a.Skv, a.D = 1, 4, 4, 32768, 32768, 128
+    a.causal, a.dtype, a.num_sms = 1, L.SYN_DTYPE_BF16, 148
+    sched, keep = L.make_schedule([[0, 0, 0, 0]], [[1, 4, 32768, 32768]], None, ndim=4)
+    plan = L.AttnPlan()
+    assert L.lib().syn_attention_plan(ctypes.byref(a), ctypes.byref(sched), None, None, ctypes.byref(plan)) == 0
+    assert (plan.grid, plan.unit_rows, plan.num_units) == (148, 256, 512)
+    owned = sorted(plan.units[i] for i in range(plan.start[148]))
+    assert owned == list(range(512))
+    blocks = lambda u: min(2 * (u % 128) + 2, 256)  # noqa: E731  key blocks a causal tile pair visits
+    loads = [sum(blocks(plan.units[i]) for i in range(plan.start[c], plan.start[c + 1])) for c in range(148)]
+    assert max(loads) <= 1.08 * sum(loads) / 148
+    a.Hq = a.Hkv = 64  # 8192 units: more than a plan holds
+    assert L.lib().syn_attention_plan(ctypes.byref(a), ctypes.byref(sched), None, None, ctypes.byref(plan)) == L.SYN_ERR_TOO_LARGE
