@@ -9,20 +9,36 @@
 //
 // Tensor memory (512 columns): S_A 0..127, S_B 128..255, O_A 256..383, O_B 384..511; P overwrites
 // the first 64 columns of its S.  A tile has ONE S buffer: its next S = Q K^T is issued right after
-// its P V, and the other tile's work fills the tensor pipe meanwhile.  Issue order per key block j:
-//   wait P_A(j); O_A += P_A(j) V(j); S_A = Q_A K(j+1)^T;   wait P_B(j); O_B += P_B(j) V(j); S_B = Q_B K(j+1)^T
+// its P V, and the other tile's work fills the tensor pipe meanwhile.  Each tile has an issuing
+// warp of its own; per key block j it runs
+//   wait P_X(j) [first half]; O_X += P_X(j) V(j) [keys 0..63]; wait P_X(j) [second half];
+//   O_X += P_X(j) V(j) [keys 64..127]; S_X = Q_X K(j+1)^T
 // The commit that publishes S_X(j+1) follows P_X(j) V(j) in issue order, so a softmax thread that
 // sees S full knows the previous product into O_X has completed and may rescale O_X at once.
 //
-// Roles (384 threads): warp 0 TMA producer, warp 1 MMA issuer, warp 2 TMEM allocator, warp 3 comm
-// warp (optional), warps 4-7 softmax of tile A, warps 8-11 softmax of tile B.  The first warpgroup
+// Roles (384 threads): warp 0 TMA producer, warps 1 and 2 MMA issuers of tile A and tile B (warp 2
+// also allocates the tensor memory), warp 3 comm warp (optional), warps 4-7 softmax of tile A,
+// warps 8-11 softmax of tile B.  The first warpgroup
 // gives registers up (setmaxnreg) so that a softmax thread can hold a whole row of S.
 #pragma once
 #include "attn_sm100.cuh"
+#ifdef SYN_ATTN2_TRACE
+#include <cstdio>
+#endif
 
 namespace syn {
 
 constexpr int ATTN2_THREADS = 384;
+// Register split between the first warpgroup (producer, MMA issuer, allocator, comm warp) and the
+// two softmax warpgroups.  setmaxnreg only moves registers inside what the CTA was launched with
+// (168 per thread under __launch_bounds__(384, 1)); asking for more makes the increase wait for
+// ever, so the sum is checked here.
+#define SYN_ATTN2_REGS_LOW 88
+#define SYN_ATTN2_REGS_HIGH 208
+static_assert(128 * SYN_ATTN2_REGS_LOW + 256 * SYN_ATTN2_REGS_HIGH <= 168 * ATTN2_THREADS,
+              "setmaxnreg split exceeds the registers the CTA owns");
+#define SYN_STR2(x) #x
+#define SYN_STR(x) SYN_STR2(x)
 
 // What one tile of the pair does in one wave.
 struct TileRole {
@@ -71,14 +87,61 @@ __device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
   return d;
 }
+// tcgen05.mma forms that take a descriptor as its two 32-bit words.  The issuing warp stays
+// converged and computes these words as warp-uniform values (one add per instruction on the low
+// word, which holds the 16-byte-unit address); only the instruction itself is elected.
+__device__ __forceinline__ void umma_ss_words(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                              uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      ".reg .b64 da, db;\n"
+      "setp.ne.b32 p, %6, 0;\n"
+      "mov.b64 da, {%1, %2};\n"
+      "mov.b64 db, {%3, %4};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n"
+      "}\n"
+      ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_ts_words(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi,
+                                              uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      ".reg .b64 db;\n"
+      "setp.ne.b32 p, %5, 0;\n"
+      "mov.b64 db, {%2, %3};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n"
+      "}\n"
+      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
   return d;
 }
 
+// Build with -DSYN_ATTN2_TRACE to make CTA 0 print SM-clock stamps of its first hand-overs (a
+// tuning aid; never defined in the shipped library).
+#ifdef SYN_ATTN2_TRACE
+#define ATTN2_STAMP(role, blk, ev)                                                     \
+  do {                                                                                 \
+    if (blockIdx.x == 0 && (blk) < 24u) trace_buf[role][blk][ev] = static_cast<uint32_t>(clock64()); \
+  } while (0)
+#else
+#define ATTN2_STAMP(role, blk, ev) \
+  do {                             \
+  } while (0)
+#endif
+
 template <bool FUSED, bool BF16>
 __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_constant__ AttnParams p) {
+#ifdef SYN_ATTN2_TRACE
+  __shared__ uint32_t trace_buf[4][24][12];
+#endif
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;                                        // tile A, tile B
@@ -96,8 +159,9 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
   uint64_t* p_full = bars + 14;       // [2][2] per tile and half of P (keys 0..63 / 64..127), softmax -> MMA
   uint64_t* o_full = bars + 18;       // [2] per tile, MMA -> softmax, once per unit
   uint64_t* o_empty = bars + 20;      // [2] per tile, softmax -> MMA, once per unit
-  uint64_t* comm_bar = bars + 22;     // [COMM_NBUF]
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 22 + COMM_NBUF);
+  uint64_t* turn = bars + 22;         // [2] per tile: its softmax warpgroup may exponentiate
+  uint64_t* comm_bar = bars + 24;     // [COMM_NBUF]
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 24 + COMM_NBUF);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_holder + 1);
   int* abort_info = const_cast<int*>(abort_word) + 1;
 
@@ -107,14 +171,15 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
       mbar_init(&q_full[i], 1);
       mbar_init(&q_empty[i], 1);
       mbar_init(&k_full[i], 1);
-      mbar_init(&k_empty[i], 1);
+      mbar_init(&k_empty[i], 2);  // one release per MMA warp
       mbar_init(&v_full[i], 1);
-      mbar_init(&v_empty[i], 1);
+      mbar_init(&v_empty[i], 2);
       mbar_init(&s_full[i], 1);
       mbar_init(&p_full[2 * i], 128);
       mbar_init(&p_full[2 * i + 1], 128);
       mbar_init(&o_full[i], 1);
       mbar_init(&o_empty[i], 128);
+      mbar_init(&turn[i], 128);
     }
     for (int i = 0; i < COMM_NBUF; ++i) mbar_init(&comm_bar[i], 1);
     *abort_word = 0;
@@ -138,7 +203,7 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
   const int group = p.Hq / p.Hkv;
 
   if (warp < 4) {
-  asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 " SYN_STR(SYN_ATTN2_REGS_LOW) ";");
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -196,39 +261,67 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
         }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+  } else if (warp == 1 || warp == 2) {
+    // ------------------------------------------------------------ MMA issuers: warp 1 for tile A, warp 2 for tile B
+    // A warp walks the schedule and waits on the barriers as a whole; one elected lane issues each
+    // tcgen05 instruction.  (A single diverged lane that also computes the descriptors is several
+    // times slower per instruction, and one warp serving both tiles spends more time in its waits
+    // than the tensor pipe needs for the work.)  Both warps see every shared key block: the one
+    // whose tile skips a block releases its K / V stage with a plain arrive.
+    {
+      const int x = warp - 1;
       UnitCursor cur;
       cur.shift = 1;
       int z, h, un;
-      uint32_t uq[2] = {0, 0};  // units per tile (Q and O barriers)
-      uint32_t cb[2] = {0, 0};  // key blocks per tile (S and P barriers)
-      uint32_t g = 0;           // shared key blocks (K / V ring)
+      uint32_t uqx = 0;  // units of this tile (Q and O barriers)
+      uint32_t cbx = 0;  // key blocks of this tile (S and P barriers)
+      uint32_t g = 0;    // shared key blocks (K / V ring)
+      const uint64_t timeout_ns = p.timeout_ns;
+      // descriptor words: the low word carries the address in 16-byte units (and the leading
+      // offset), the high word the stride between 8-row groups, the version and the swizzle mode
+      constexpr uint32_t TILE_UNITS = ATTN_TILE_BYTES >> 4;
+      const uint32_t desc_hi = static_cast<uint32_t>(make_smem_desc_sw128(0, 16, 1024) >> 32);
+      const uint32_t q_lo = static_cast<uint32_t>(make_smem_desc_sw128(smem_u32(sQ), 16, 1024)) +
+                            static_cast<uint32_t>(x) * TILE_UNITS;
+      const uint32_t k_lo = static_cast<uint32_t>(make_smem_desc_sw128(smem_u32(sK), 16, 1024));
+      const uint32_t v_lo = static_cast<uint32_t>(make_smem_desc_sw128(smem_u32(sV), ATTN_TILE_BYTES / 2, 1024));
+      const uint32_t s_tmem = tmem_base + static_cast<uint32_t>(x) * 128u;  // S_x, then P_x
+      const uint32_t o_tmem = tmem_base + 256u + static_cast<uint32_t>(x) * 128u;
+      const uint32_t idesc_qk = p.idesc_qk, idesc_pv = p.idesc_pv;
       // S_x = Q_x K^T for the block in K stage `st`
-      auto issue_qk = [&](int x, int st) {
-        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(x) * 128u;
+      auto issue_qk = [&](int st) {
+        const uint32_t b0 = k_lo + static_cast<uint32_t>(st) * TILE_UNITS;
+        // (electing once around the whole group was measured slower: the descriptor words then
+        // live in per-lane registers of a diverged lane)
 #pragma unroll
         for (int kk = 0; kk < ATTN_D / 16; ++kk) {
-          const uint32_t half = (kk >> 2) * (ATTN_TILE_BYTES / 2);
-          const uint64_t a = make_smem_desc_sw128(smem_u32(sQ + x * ATTN_TILE_BYTES + half), 16, 1024) + 2 * (kk & 3);
-          const uint64_t b = make_smem_desc_sw128(smem_u32(sK + st * ATTN_TILE_BYTES + half), 16, 1024) + 2 * (kk & 3);
-          umma_f16_ss(d_tmem, a, b, p.idesc_qk, kk != 0 ? 1u : 0u);
+          // 16 elements along d are 32 bytes inside the 128-byte swizzle row; d 64..127 is the second box
+          const uint32_t off = static_cast<uint32_t>((kk >> 2) * (TILE_UNITS / 2) + 2 * (kk & 3));
+          if (elect_one()) umma_ss_words(s_tmem, q_lo + off, desc_hi, b0 + off, desc_hi, idesc_qk, kk != 0 ? 1u : 0u);
         }
-        umma_commit(&s_full[x]);
+        if (elect_one()) umma_commit(&s_full[x]);
       };
       // O_x (+)= P_x V for one half (64 keys) of the block in V stage `st`
-      auto issue_pv = [&](int x, int st, int half, bool accumulate) {
-        const uint32_t p_tmem = tmem_base + static_cast<uint32_t>(x) * 128u;
-        const uint32_t o_tmem = tmem_base + 256u + static_cast<uint32_t>(x) * 128u;
+      auto issue_pv = [&](int st, int half, bool accumulate) {
+        const uint32_t b0 = v_lo + static_cast<uint32_t>(st) * TILE_UNITS;
 #pragma unroll
         for (int k4 = 0; k4 < ATTN_BN / 32; ++k4) {
           const int kk = half * (ATTN_BN / 32) + k4;
           // V block: [128 keys][64 d] per box, keys are the K axis (128 B apart), d is the contiguous
-          // (MN) axis; the second box (d 64..127) lies 16 KB further
-          const uint64_t b = make_smem_desc_sw128(smem_u32(sV + st * ATTN_TILE_BYTES + kk * 16 * 128),
-                                                  ATTN_TILE_BYTES / 2, 1024);
-          umma_f16_ts(o_tmem, p_tmem + kk * 8, b, p.idesc_pv, (accumulate || kk != 0) ? 1u : 0u);
+          // (MN) axis; the second box (d 64..127) lies 16 KB further (the leading offset)
+          if (elect_one())
+            umma_ts_words(o_tmem, s_tmem + kk * 8, b0 + static_cast<uint32_t>(kk * 128), desc_hi, idesc_pv,
+                          (accumulate || kk != 0) ? 1u : 0u);
+        }
+      };
+      // stage release: after this warp's products if it issued any, at once otherwise
+      auto release = [&](uint64_t* bar, bool issued) {
+        if (elect_one()) {
+          if (issued) {
+            umma_commit(bar);
+          } else {
+            mbar_arrive(bar);
+          }
         }
       };
       while (cur.next(p, z, h, un)) {
@@ -241,67 +334,77 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
           act[1] += tile_mode(p, tr[1], kb) != 0;
         }
         if (act[0] + act[1] == 0) continue;
-#pragma unroll
-        for (int x = 0; x < 2; ++x)
-          if (act[x]) mbar_wait(&q_full[x], uq[x] & 1u, abort_word, p.timeout_ns);
+        if (act[x]) mbar_wait(&q_full[x], uqx & 1u, abort_word, timeout_ns);
         int m[2], n[2];
         int kb = next_shared_block(p, w, tr[0], tr[1], w.kb0, m[0], m[1]);
-        // the unit's first block: both tiles' S
+        // the unit's first block
         {
           const int st = g % ATTN_KV_STAGES;
-          mbar_wait(&k_full[st], (g / ATTN_KV_STAGES) & 1u, abort_word, p.timeout_ns);
-          tc_fence_after();
-          if (m[0]) issue_qk(0, st);
-          if (m[1]) issue_qk(1, st);
-          umma_commit(&k_empty[st]);
+          if (m[x]) {
+            mbar_wait(&k_full[st], (g / ATTN_KV_STAGES) & 1u, abort_word, timeout_ns);
+            tc_fence_after();
+            issue_qk(st);
+          }
+          release(&k_empty[st], m[x] != 0);
         }
-        bool started[2] = {false, false};
+        bool started = false;
         while (kb >= 0) {
           const int kn = next_shared_block(p, w, tr[0], tr[1], kb + 1, n[0], n[1]);
           const int st = g % ATTN_KV_STAGES, st_n = (g + 1) % ATTN_KV_STAGES;
           const uint32_t par = (g / ATTN_KV_STAGES) & 1u, par_n = ((g + 1) / ATTN_KV_STAGES) & 1u;
-          bool v_ready = false;
-#pragma unroll
-          for (int x = 0; x < 2; ++x) {
-            if (m[x]) {
-              mbar_wait(&p_full[2 * x], cb[x] & 1u, abort_word, p.timeout_ns);
-              if (!started[x]) {
-                // the first product of a unit overwrites O_x: the previous unit's result must have been read
-                mbar_wait(&o_empty[x], (uq[x] & 1u) ^ 1u, abort_word, p.timeout_ns);
-              }
-              if (!v_ready) {
-                mbar_wait(&v_full[st], par, abort_word, p.timeout_ns);
-                v_ready = true;
-              }
-              tc_fence_after();
-              issue_pv(x, st, 0, started[x]);
-              mbar_wait(&p_full[2 * x + 1], cb[x] & 1u, abort_word, p.timeout_ns);
-              tc_fence_after();
-              issue_pv(x, st, 1, true);
-              ++cb[x];
-              started[x] = true;
+          if (m[x]) {
+            if (lane == 0) ATTN2_STAMP(2 + x, cbx, 0);
+            mbar_wait(&p_full[2 * x], cbx & 1u, abort_word, timeout_ns);
+            if (lane == 0) ATTN2_STAMP(2 + x, cbx, 1);
+            if (!started) {
+              // the first product of a unit overwrites O_x: the previous unit's result must have been read
+              mbar_wait(&o_empty[x], (uqx & 1u) ^ 1u, abort_word, timeout_ns);
             }
-            if (x == 1) umma_commit(&v_empty[st]);  // both tiles' products with this V block are issued
+            mbar_wait(&v_full[st], par, abort_word, timeout_ns);
+            tc_fence_after();
+            if (lane == 0) ATTN2_STAMP(2 + x, cbx, 2);
+            issue_pv(st, 0, started);
+            if (lane == 0) ATTN2_STAMP(2 + x, cbx, 3);
+            // the next K block has long landed; looking now keeps this wait off the path from the
+            // second half of P to the next S
+            if (kn >= 0 && n[x]) mbar_wait(&k_full[st_n], par_n, abort_word, timeout_ns);
+            mbar_wait(&p_full[2 * x + 1], cbx & 1u, abort_word, timeout_ns);
+            if (lane == 0) ATTN2_STAMP(2 + x, cbx, 4);
+            tc_fence_after();
+            issue_pv(st, 1, true);
+            if (lane == 0) ATTN2_STAMP(2 + x, cbx, 6);
+            ++cbx;
+            started = true;
             if (kn >= 0 && n[x]) {
-              mbar_wait(&k_full[st_n], par_n, abort_word, p.timeout_ns);
-              tc_fence_after();
-              issue_qk(x, st_n);
+              issue_qk(st_n);
+              if (lane == 0) ATTN2_STAMP(2 + x, cbx - 1, 9);
             }
-            // the next K block is free once its last user has been issued: tile B if it takes part
-            if (kn >= 0 && ((x == 0 && !n[1]) || (x == 1 && n[1]))) umma_commit(&k_empty[st_n]);
+            // both stages are released by one commit each, after everything issued so far
+            release(&v_empty[st], true);
+            if (kn >= 0) release(&k_empty[st_n], n[x] != 0);
+          } else {
+            release(&v_empty[st], false);
+            if (kn >= 0) {
+              if (n[x]) {
+                mbar_wait(&k_full[st_n], par_n, abort_word, timeout_ns);
+                tc_fence_after();
+                issue_qk(st_n);
+              }
+              release(&k_empty[st_n], n[x] != 0);
+            }
           }
+          if (lane == 0) ATTN2_STAMP(2 + x, cbx - 1, 10);
           kb = kn;
           m[0] = n[0];
           m[1] = n[1];
           ++g;
         }
-#pragma unroll
-        for (int x = 0; x < 2; ++x) {
-          if (act[x]) {
+        if (act[x]) {
+          if (elect_one()) {
             umma_commit(&o_full[x]);
             umma_commit(&q_empty[x]);
-            ++uq[x];
           }
+          ++uqx;
         }
       }
     }
@@ -313,7 +416,7 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
   }
   } else {
     // ------------------------------------------------------------ softmax / accumulate / merge / store
-    asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 " SYN_STR(SYN_ATTN2_REGS_HIGH) ";");
     const int x = (warp >= 8) ? 1 : 0;  // which tile of the pair
     const int q = warp & 3;
     const int row = q * 32 + lane;      // query row inside the tile, also the TMEM lane
@@ -325,10 +428,11 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
     int z, h, un;
     uint32_t cbx = 0;  // key blocks this tile has processed (S / P barrier parity)
     uint32_t ux = 0;   // units this tile has taken part in
+    uint32_t turns = 0;  // blocks both tiles have worked on (parity of the turn barriers)
     while (cur.next(p, z, h, un)) {
       if (*abort_word != 0) break;
       const AttnWave& w = p.waves[cur.wave];
-      const TileRole t = tile_role(p, w, 2 * un + x);
+      const TileRole t = tile_role(p, w, 2 * un + x), other = tile_role(p, w, 2 * un + (x ^ 1));
       int active = 0;
       for (int kb = w.kb0; kb < w.kb1; ++kb) active += tile_mode(p, t, kb) != 0;
       if (active == 0) continue;
@@ -340,18 +444,21 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
       for (int kb = w.kb0; kb < w.kb1; ++kb) {
         const int mode = block_mode(p, qpos0, kb);
         if (mode == 0) continue;
+        const bool both = tile_mode(p, other, kb) != 0;  // the other tile works on this block too
         int lim = ATTN_BN - 1;  // keys 0..lim of the block are visible to this row
         if (mode == 2) {
           const int kpos0 = p.kv_pos ? __ldg(p.kv_pos + kb) : kb * ATTN_BN;
           lim = min(ATTN_BN - 1, qpos0 + row - kpos0);
         }
         mbar_wait(&s_full[x], cbx & 1u, abort_word, p.timeout_ns);
+        if (threadIdx.x % 128 == 0) ATTN2_STAMP(x, cbx, 0);
         ++cbx;
         tc_fence_after();
         uint32_t sr[ATTN_BN / 32][32];
 #pragma unroll
         for (int c = 0; c < ATTN_BN / 32; ++c) tmem_ld_32x32(s_tmem + c * 32, sr[c]);
         tmem_ld_wait();
+        if (threadIdx.x % 128 == 0) ATTN2_STAMP(x, cbx - 1, 1);
         if (mode == 2) {
 #pragma unroll
           for (int c = 0; c < ATTN_BN / 32; ++c) {
@@ -389,20 +496,35 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
           m = mx;
         }
         const float neg_m = (m == -INFINITY) ? 0.f : -m;
+        if (threadIdx.x % 128 == 0) ATTN2_STAMP(x, cbx - 1, 2);
         // P = 2^(S * scale - m), two elements per instruction where the hardware allows; the two
         // halves of P (keys 0..63, 64..127) are handed over separately, so that the product with
         // the first half of V runs while the second half is still being exponentiated
+        // The two warpgroups take turns at the exponentials (A, B, A, B ... over the blocks both
+        // work on): the special-function unit serves one of them at full rate instead of both at
+        // half, and the tiles settle half a period apart, so that one tile's products run on the
+        // tensor pipe during the other tile's softmax.
+        if (both) mbar_wait(&turn[x], x == 0 ? ((turns & 1u) ^ 1u) : (turns & 1u), abort_word, p.timeout_ns);
         const uint64_t scale2 = f2_pack(p.scale_log2, p.scale_log2), negm2 = f2_pack(neg_m, neg_m);
         uint64_t ls2[2] = {0ull, 0ull};  // packed (0.f, 0.f)
 #pragma unroll
         for (int c = 0; c < ATTN_BN / 32; ++c) {
-          uint32_t pk[16];
+          // in place, stage by stage over the 32 values of the chunk, so that the independent
+          // exponentials are issued back to back instead of one dependent chain per pair
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             float x0, x1;
             f2_unpack(f2_fma(f2_pack(__uint_as_float(sr[c][2 * i]), __uint_as_float(sr[c][2 * i + 1])), scale2, negm2),
                       x0, x1);
-            const float p0 = ex2_approx(x0), p1 = ex2_approx(x1);
+            sr[c][2 * i] = __float_as_uint(x0);
+            sr[c][2 * i + 1] = __float_as_uint(x1);
+          }
+#pragma unroll
+          for (int i = 0; i < 32; ++i) sr[c][i] = __float_as_uint(ex2_approx(__uint_as_float(sr[c][i])));
+          uint32_t pk[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float p0 = __uint_as_float(sr[c][2 * i]), p1 = __uint_as_float(sr[c][2 * i + 1]);
             ls2[i & 1] = f2_add(ls2[i & 1], f2_pack(p0, p1));
             pk[i] = BF16 ? pack2_bf16(p0, p1) : pack2_f16(p0, p1);
           }
@@ -411,7 +533,12 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
             tmem_st_wait();
             tc_fence_before();
             mbar_arrive(&p_full[2 * x + (c >> 1)]);
+            if (threadIdx.x % 128 == 0) ATTN2_STAMP(x, cbx - 1, 3 + (c >> 1));
           }
+        }
+        if (both) {
+          mbar_arrive(&turn[x ^ 1]);
+          ++turns;
         }
         {
           float a0, a1, b0, b1;
@@ -495,6 +622,23 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
 
   tc_fence_before();
   __syncthreads();
+#ifdef SYN_ATTN2_TRACE
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    const uint32_t t0 = trace_buf[0][8][0];
+    for (int b = 8; b < 16; ++b) {
+      printf("blk %2d A: s_full %u ld %u max %u p0 %u p1 %u | B: s_full %u ld %u max %u p0 %u p1 %u\n", b,
+             trace_buf[0][b][0] - t0, trace_buf[0][b][1] - t0, trace_buf[0][b][2] - t0, trace_buf[0][b][3] - t0,
+             trace_buf[0][b][4] - t0, trace_buf[1][b][0] - t0, trace_buf[1][b][1] - t0, trace_buf[1][b][2] - t0,
+             trace_buf[1][b][3] - t0, trace_buf[1][b][4] - t0);
+      for (int x = 0; x < 2; ++x)
+        printf("   MMA %c: top %u p0 %u fence %u pv0 %u p1 %u fence %u pv1 %u vcommit %u kwait %u qk %u kcommit %u\n", 'A' + x,
+               trace_buf[2 + x][b][0] - t0, trace_buf[2 + x][b][1] - t0, trace_buf[2 + x][b][2] - t0,
+               trace_buf[2 + x][b][3] - t0, trace_buf[2 + x][b][4] - t0, trace_buf[2 + x][b][5] - t0,
+               trace_buf[2 + x][b][6] - t0, trace_buf[2 + x][b][7] - t0, trace_buf[2 + x][b][8] - t0,
+               trace_buf[2 + x][b][9] - t0, trace_buf[2 + x][b][10] - t0);
+    }
+  }
+#endif
   if (warp == 2) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
