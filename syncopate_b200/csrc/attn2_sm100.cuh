@@ -87,37 +87,6 @@ __device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
   return d;
 }
-// tcgen05.mma forms that take a descriptor as its two 32-bit words.  The issuing warp stays
-// converged and computes these words as warp-uniform values (one add per instruction on the low
-// word, which holds the 16-byte-unit address); only the instruction itself is elected.
-__device__ __forceinline__ void umma_ss_words(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
-                                              uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      ".reg .b64 da, db;\n"
-      "setp.ne.b32 p, %6, 0;\n"
-      "mov.b64 da, {%1, %2};\n"
-      "mov.b64 db, {%3, %4};\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n"
-      "}\n"
-      ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_ts_words(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t b_hi,
-                                              uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      ".reg .b64 db;\n"
-      "setp.ne.b32 p, %5, 0;\n"
-      "mov.b64 db, {%2, %3};\n"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n"
-      "}\n"
-      ::"r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -340,8 +309,10 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
         // the unit's first block
         {
           const int st = g % ATTN_KV_STAGES;
+          // (a warp whose tile skips the block still waits for the stage to be full before it
+          // releases it: otherwise it could run ahead and arrive twice in one phase)
+          mbar_wait(&k_full[st], (g / ATTN_KV_STAGES) & 1u, abort_word, timeout_ns);
           if (m[x]) {
-            mbar_wait(&k_full[st], (g / ATTN_KV_STAGES) & 1u, abort_word, timeout_ns);
             tc_fence_after();
             issue_qk(st);
           }
@@ -367,7 +338,7 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
             if (lane == 0) ATTN2_STAMP(2 + x, cbx, 3);
             // the next K block has long landed; looking now keeps this wait off the path from the
             // second half of P to the next S
-            if (kn >= 0 && n[x]) mbar_wait(&k_full[st_n], par_n, abort_word, timeout_ns);
+            if (kn >= 0) mbar_wait(&k_full[st_n], par_n, abort_word, timeout_ns);
             mbar_wait(&p_full[2 * x + 1], cbx & 1u, abort_word, timeout_ns);
             if (lane == 0) ATTN2_STAMP(2 + x, cbx, 4);
             tc_fence_after();
@@ -383,10 +354,11 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
             release(&v_empty[st], true);
             if (kn >= 0) release(&k_empty[st_n], n[x] != 0);
           } else {
+            mbar_wait(&v_full[st], par, abort_word, timeout_ns);
             release(&v_empty[st], false);
             if (kn >= 0) {
+              mbar_wait(&k_full[st_n], par_n, abort_word, timeout_ns);
               if (n[x]) {
-                mbar_wait(&k_full[st_n], par_n, abort_word, timeout_ns);
                 tc_fence_after();
                 issue_qk(st_n);
               }

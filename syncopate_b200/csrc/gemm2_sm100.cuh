@@ -238,33 +238,42 @@ gemm2_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUten
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer (pair leader only)
-    if (lane == 0 && leader) {
+    // The whole warp walks the work items and waits on the barriers; one elected lane issues each
+    // tcgen05 instruction.
+    if (leader) {
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
+      const uint32_t desc_hi = static_cast<uint32_t>(make_smem_desc_sw128(0, 16, 1024) >> 32);
+      const uint32_t a_lo0 = static_cast<uint32_t>(make_smem_desc_sw128(smem_u32(sA), 16, 1024));
+      const uint32_t b_lo0 = static_cast<uint32_t>(make_smem_desc_sw128(smem_u32(sB), 16, 1024));
+      const uint32_t idesc = p.idesc;
+      const uint64_t timeout_ns = p.timeout_ns;
       PairWork wk;
       for (int n = 0; pair_work(p, tail, total_pair_tiles, pair_id, num_pairs, n, wk); ++n) {
-        mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, abort_word, p.timeout_ns);
+        if (*abort_word != 0) break;
+        mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, abort_word, timeout_ns);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * ACC_STRIDE);
         for (int kb = wk.kb0; kb < wk.kb1; ++kb) {
-          mbar_wait(&full_bar[stage], phase, abort_word, p.timeout_ns);
+          mbar_wait(&full_bar[stage], phase, abort_word, timeout_ns);
           tc_fence_after();
-          const uint64_t a_desc = make_smem_desc_sw128(smem_u32(sA + stage * A_BYTES), 16, 1024);
-          const uint64_t b_desc = make_smem_desc_sw128(smem_u32(sB + stage * B_BYTES), 16, 1024);
+          const uint32_t a_lo = a_lo0 + static_cast<uint32_t>(stage) * (A_BYTES >> 4);
+          const uint32_t b_lo = b_lo0 + static_cast<uint32_t>(stage) * (B_BYTES >> 4);
 #pragma unroll
           for (int k = 0; k < GEMM_BK / GEMM_UMMA_K; ++k) {
-            umma_f16_ss_pair(d_tmem, a_desc + static_cast<uint64_t>(2 * k), b_desc + static_cast<uint64_t>(2 * k),
-                             p.idesc, ((kb - wk.kb0) | k) != 0 ? 1u : 0u);
+            if (elect_one())
+              umma_ss_words_pair(d_tmem, a_lo + 2u * k, desc_hi, b_lo + 2u * k, desc_hi, idesc,
+                                 ((kb - wk.kb0) | k) != 0 ? 1u : 0u);
           }
-          umma_commit_pair(&empty_bar[stage]);
+          if (elect_one()) umma_commit_pair(&empty_bar[stage]);
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
           }
         }
-        umma_commit_pair(&tfull_bar[acc]);
+        if (elect_one()) umma_commit_pair(&tfull_bar[acc]);
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }

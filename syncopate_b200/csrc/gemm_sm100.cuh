@@ -317,38 +317,47 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // The whole warp walks the tiles and waits on the barriers; one elected lane issues each
+    // tcgen05 instruction (and makes the queue hand-back).
+    {
       int stage = 0;
       uint32_t phase = 0;
       int acc = 0;
       uint32_t acc_phase = 0;
+      const uint32_t desc_hi = static_cast<uint32_t>(make_smem_desc_sw128(0, 16, 1024) >> 32);
+      const uint32_t a_lo0 = static_cast<uint32_t>(make_smem_desc_sw128(smem_u32(sA), 16, 1024));
+      const uint32_t b_lo0 = static_cast<uint32_t>(make_smem_desc_sw128(smem_u32(sB), 16, 1024));
+      const uint32_t idesc = p.idesc;
+      const int k_blocks = p.k_blocks;
+      const uint64_t timeout_ns = p.timeout_ns;
       for (uint32_t n = 0;; ++n) {
         const int slot = n % TILE_Q;
-        mbar_wait(&tq_full[slot], (n / TILE_Q) & 1u, abort_word, p.timeout_ns);
+        mbar_wait(&tq_full[slot], (n / TILE_Q) & 1u, abort_word, timeout_ns);
         const int tile = tile_q[slot];
-        mbar_arrive(&tq_empty[slot]);
+        __syncwarp();  // every lane has read the slot before it is handed back
+        if (elect_one()) mbar_arrive(&tq_empty[slot]);
         if (tile < 0 || *abort_word != 0) break;
-        mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, abort_word, p.timeout_ns);
+        mbar_wait(&tempty_bar[acc], acc_phase ^ 1u, abort_word, timeout_ns);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * ACC_STRIDE);
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
-          mbar_wait(&full_bar[stage], phase, abort_word, p.timeout_ns);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          mbar_wait(&full_bar[stage], phase, abort_word, timeout_ns);
           tc_fence_after();
-          const uint64_t a_desc = make_smem_desc_sw128(smem_u32(sA + stage * L::A_BYTES), 16, 1024);
-          const uint64_t b_desc = make_smem_desc_sw128(smem_u32(sB + stage * L::B_BYTES), 16, 1024);
+          const uint32_t a_lo = a_lo0 + static_cast<uint32_t>(stage) * (L::A_BYTES >> 4);
+          const uint32_t b_lo = b_lo0 + static_cast<uint32_t>(stage) * (L::B_BYTES >> 4);
 #pragma unroll
           for (int k = 0; k < GEMM_BK / GEMM_UMMA_K; ++k) {
             // advancing 16 elements along K inside the 128-byte swizzle row = +32 bytes = +2 (16-byte units)
-            umma_f16_ss(d_tmem, a_desc + static_cast<uint64_t>(2 * k), b_desc + static_cast<uint64_t>(2 * k),
-                        p.idesc, (kb | k) != 0 ? 1u : 0u);
+            if (elect_one())
+              umma_ss_words(d_tmem, a_lo + 2u * k, desc_hi, b_lo + 2u * k, desc_hi, idesc, (kb | k) != 0 ? 1u : 0u);
           }
-          umma_commit(&empty_bar[stage]);
+          if (elect_one()) umma_commit(&empty_bar[stage]);
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
           }
         }
-        umma_commit(&tfull_bar[acc]);
+        if (elect_one()) umma_commit(&tfull_bar[acc]);
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }
