@@ -603,10 +603,9 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
              trace_buf[0][b][4] - t0, trace_buf[1][b][0] - t0, trace_buf[1][b][1] - t0, trace_buf[1][b][2] - t0,
              trace_buf[1][b][3] - t0, trace_buf[1][b][4] - t0);
       for (int x = 0; x < 2; ++x)
-        printf("   MMA %c: top %u p0 %u fence %u pv0 %u p1 %u fence %u pv1 %u vcommit %u kwait %u qk %u kcommit %u\n", 'A' + x,
+        printf("   MMA %c: top %u p0 %u fence %u pv0 %u p1 %u pv1 %u qk %u end %u\n", 'A' + x,
                trace_buf[2 + x][b][0] - t0, trace_buf[2 + x][b][1] - t0, trace_buf[2 + x][b][2] - t0,
-               trace_buf[2 + x][b][3] - t0, trace_buf[2 + x][b][4] - t0, trace_buf[2 + x][b][5] - t0,
-               trace_buf[2 + x][b][6] - t0, trace_buf[2 + x][b][7] - t0, trace_buf[2 + x][b][8] - t0,
+               trace_buf[2 + x][b][3] - t0, trace_buf[2 + x][b][4] - t0, trace_buf[2 + x][b][6] - t0,
                trace_buf[2 + x][b][9] - t0, trace_buf[2 + x][b][10] - t0);
     }
   }

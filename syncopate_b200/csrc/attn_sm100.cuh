@@ -272,60 +272,76 @@ __global__ void __launch_bounds__(256, 1) attn_kernel(const __grid_constant__ At
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // The whole warp walks the units and waits on the barriers; one elected lane issues each
+    // tcgen05 instruction, with descriptor words computed as warp-uniform values.
+    {
       UnitCursor cur;
       int z, h, qt;
       uint32_t u = 0, g = 0;
+      constexpr uint32_t TILE_UNITS = ATTN_TILE_BYTES >> 4;
+      const uint32_t desc_hi = static_cast<uint32_t>(make_smem_desc_sw128(0, 16, 1024) >> 32);
+      const uint32_t q_lo = static_cast<uint32_t>(make_smem_desc_sw128(smem_u32(sQ), 16, 1024));
+      const uint32_t k_lo = static_cast<uint32_t>(make_smem_desc_sw128(smem_u32(sK), 16, 1024));
+      const uint32_t v_lo = static_cast<uint32_t>(make_smem_desc_sw128(smem_u32(sV), ATTN_TILE_BYTES / 2, 1024));
+      const uint32_t idesc_qk = p.idesc_qk, idesc_pv = p.idesc_pv;
+      const uint64_t timeout_ns = p.timeout_ns;
       auto issue_qk = [&](uint32_t gi, int qb) {
         const int st = gi % ATTN_KV_STAGES;
-        mbar_wait(&k_full[st], (gi / ATTN_KV_STAGES) & 1u, abort_word, p.timeout_ns);
+        mbar_wait(&k_full[st], (gi / ATTN_KV_STAGES) & 1u, abort_word, timeout_ns);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (gi & 1u) * 128u;
+        const uint32_t a0 = q_lo + static_cast<uint32_t>(qb) * TILE_UNITS;
+        const uint32_t b0 = k_lo + static_cast<uint32_t>(st) * TILE_UNITS;
 #pragma unroll
         for (int kk = 0; kk < ATTN_D / 16; ++kk) {
-          const uint32_t half = (kk >> 2) * (ATTN_TILE_BYTES / 2);
-          const uint64_t a = make_smem_desc_sw128(smem_u32(sQ + qb * ATTN_TILE_BYTES + half), 16, 1024) + 2 * (kk & 3);
-          const uint64_t b = make_smem_desc_sw128(smem_u32(sK + st * ATTN_TILE_BYTES + half), 16, 1024) + 2 * (kk & 3);
-          umma_f16_ss(d_tmem, a, b, p.idesc_qk, kk != 0 ? 1u : 0u);
+          // 16 elements along d are 32 bytes inside the 128-byte swizzle row; d 64..127 is the second box
+          const uint32_t off = static_cast<uint32_t>((kk >> 2) * (TILE_UNITS / 2) + 2 * (kk & 3));
+          if (elect_one()) umma_ss_words(d_tmem, a0 + off, desc_hi, b0 + off, desc_hi, idesc_qk, kk != 0 ? 1u : 0u);
         }
-        umma_commit(&k_empty[st]);
-        umma_commit(&s_full[gi & 1u]);
+        if (elect_one()) {
+          umma_commit(&k_empty[st]);
+          umma_commit(&s_full[gi & 1u]);
+        }
       };
       while (cur.next(p, z, h, qt)) {
+        if (*abort_word != 0) break;
         const AttnWave& w = p.waves[cur.wave];
         const int qpos0 = p.q_pos ? __ldg(p.q_pos + qt) : qt * ATTN_BM;
         int active = 0;
         for (int kb = w.kb0; kb < w.kb1; ++kb) active += block_mode(p, qpos0, kb) != 0;
         if (active == 0) continue;
         const int qb = u & 1;
-        mbar_wait(&q_full[qb], (u >> 1) & 1u, abort_word, p.timeout_ns);
+        mbar_wait(&q_full[qb], (u >> 1) & 1u, abort_word, timeout_ns);
         issue_qk(g, qb);
         for (int j = 0; j < active; ++j) {
           const uint32_t gi = g + j;
           if (j + 1 < active) issue_qk(gi + 1, qb);
           // P_j is in tensor memory (and O has been rescaled if the row maximum jumped)
-          mbar_wait(&p_full[gi & 1u], (gi >> 1) & 1u, abort_word, p.timeout_ns);
+          mbar_wait(&p_full[gi & 1u], (gi >> 1) & 1u, abort_word, timeout_ns);
           if (j == 0) {
             // the first product of a unit overwrites O: the previous unit's result must have been read
-            mbar_wait(&o_empty[0], (u & 1u) ^ 1u, abort_word, p.timeout_ns);
+            mbar_wait(&o_empty[0], (u & 1u) ^ 1u, abort_word, timeout_ns);
           }
           const int st = gi % ATTN_KV_STAGES;
-          mbar_wait(&v_full[st], (gi / ATTN_KV_STAGES) & 1u, abort_word, p.timeout_ns);
+          mbar_wait(&v_full[st], (gi / ATTN_KV_STAGES) & 1u, abort_word, timeout_ns);
           tc_fence_after();
           const uint32_t p_tmem = tmem_base + (gi & 1u) * 128u;  // bf16 pairs over the first 64 columns of S
           const uint32_t o_tmem = tmem_base + 256u;
+          const uint32_t b0 = v_lo + static_cast<uint32_t>(st) * TILE_UNITS;
 #pragma unroll
           for (int kk = 0; kk < ATTN_BN / 16; ++kk) {
             // V block in shared memory: [128 keys][64 d] per box, keys are the K axis (128 B apart),
             // d is the contiguous (MN) axis; the second box (d 64..127) lies 16 KB further
-            const uint64_t b = make_smem_desc_sw128(smem_u32(sV + st * ATTN_TILE_BYTES + kk * 16 * 128),
-                                                    ATTN_TILE_BYTES / 2, 1024);
-            umma_f16_ts(o_tmem, p_tmem + kk * 8, b, p.idesc_pv, (j | kk) != 0 ? 1u : 0u);
+            if (elect_one())
+              umma_ts_words(o_tmem, p_tmem + kk * 8, b0 + static_cast<uint32_t>(kk * 128), desc_hi, idesc_pv,
+                            (j | kk) != 0 ? 1u : 0u);
           }
-          umma_commit(&v_empty[st]);
-          umma_commit(&o_full[gi & 1u]);
+          if (elect_one()) {
+            umma_commit(&v_empty[st]);
+            umma_commit(&o_full[gi & 1u]);
+          }
         }
-        umma_commit(&q_empty[qb]);
+        if (elect_one()) umma_commit(&q_empty[qb]);
         g += active;
         ++u;
       }
