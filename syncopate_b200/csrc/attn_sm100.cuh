@@ -68,7 +68,9 @@ struct AttnParams {
 // Ownership is fixed for the whole launch.  Non-causal: query tile qt of head (z, h) belongs to CTA
 // ((z * Hq + h) * T + qt) mod grid.  Causal: tiles are owned in pairs {j, T-1-j} (tile t has about
 // t + 1 visible key blocks, so every pair carries the same work) and pair j of head (z, h)
-// belongs to CTA ((z * Hq + h) * ceil(T / 2) + j) mod grid (only when there are at least two pairs per CTA).
+// belongs to CTA ((z * Hq + h) * ceil(T / 2) + j) mod grid (when the host sets `own_pairs`: enough pairs
+// for every CTA).  With `use_lists` the host has planned the ownership instead (syn_attention_plan)
+// and the CTA walks its own list of units once per wave.
 //
 // `shift` = 1 makes the unit a run of two adjacent query tiles (2 * unit, 2 * unit + 1), for the
 // kernel that works on two tiles at a time; a wave then touches every such run it overlaps.

@@ -77,3 +77,40 @@ def test_attention_plan_balances_causal_units_without_a_gpu():
     assert max(loads) <= 1.08 * sum(loads) / 148
     a.Hq = a.Hkv = 64  # 8192 units: more than a plan holds
     assert L.lib().syn_attention_plan(ctypes.byref(a), ctypes.byref(sched), None, None, ctypes.byref(plan)) == L.SYN_ERR_TOO_LARGE
+
+
+def test_attention_plan_with_zigzag_positions_and_waves():
+    """Context-parallel shape (rank 3 of 8, 8192 local queries, eight KV waves of 8192 keys, zigzag
+    positions): the planner weighs a unit by the key blocks its tiles really see in every wave, so the
+    late half of the local queries (which sees nearly everything) is spread over all CTAs."""
+    from syncopate_b200 import _lib as L
+    from syncopate_b200.computation.attn.plan import zigzag_tables
+
+    world, rank, S, H = 8, 3, 65536, 8
+    local = S // world
+    q_pos, kv_pos = zigzag_tables(world, rank, S)
+    a = L.AttnArgs()
+    a.Z, a.Hq, a.Hkv, a.Sq, a.Skv, a.D = 1, H, 1, local, S, 128
+    a.causal, a.dtype, a.num_sms = 1, L.SYN_DTYPE_BF16, 148
+    a.q_pos, a.kv_pos = 1, 1  # device pointers are not touched by the planner; non-NULL marks "tables given"
+    offs = [[0, 0, 0, ((rank + i) % world) * local] for i in range(world)]
+    sizes = [[1, H, local, local]] * world
+    sched, keep = L.make_schedule(offs, sizes, None, ndim=4)
+    qh = (ctypes.c_int32 * len(q_pos))(*q_pos)
+    kh = (ctypes.c_int32 * len(kv_pos))(*kv_pos)
+    plan = L.AttnPlan()
+    assert L.lib().syn_attention_plan(ctypes.byref(a), ctypes.byref(sched), qh, kh, ctypes.byref(plan)) == 0
+    per_head = local // 256
+    assert plan.num_units == H * per_head and sorted(plan.units[i] for i in range(plan.start[148])) == list(range(H * per_head))
+
+    def weight(u):  # key blocks (of any wave) that the two tiles of unit u see
+        seen = 0
+        for kb, kp in enumerate(kv_pos):
+            seen += any(kp <= q_pos[2 * u + x] + 127 for x in range(2))
+        return seen
+
+    w = [weight(u) for u in range(per_head)]
+    loads = [sum(w[plan.units[i] % per_head] for i in range(plan.start[c], plan.start[c + 1])) for c in range(148)]
+    assert max(loads) <= 1.25 * sum(loads) / 148   # 256 units of very different length on 148 CTAs
+    # tables must be given on both sides or on neither
+    assert L.lib().syn_attention_plan(ctypes.byref(a), ctypes.byref(sched), None, kh, ctypes.byref(plan)) == -1
