@@ -184,6 +184,11 @@ int syn_flag_set(uint64_t* flag, uint64_t value, void* stream);
 int syn_memcpy_async(void* dst, const void* src, size_t bytes, void* stream);
 int syn_flag_wait(const uint64_t* flag, uint64_t value, uint64_t timeout_ns, int32_t* status, int tag,
                   void* stream);
+/* Stream-ordered wait until *flag >= value as a stream memory operation: needs no SM, so it is not
+ * starved by a persistent kernel that fills the GPU (which syn_flag_wait's one-thread kernel can
+ * be).  Unbounded by itself: use it only for flags that a bounded kernel raises on every path.
+ * SYN_ERR_UNSUPPORTED when the driver offers no such operation. */
+int syn_flag_wait_stream(const uint64_t* flag, uint64_t value, void* stream);
 
 /* ------------------------------------------------------------------ fused operators
  * The flag value of one fused call is `gemm.signal_value` (an epoch that the caller increases by
@@ -225,6 +230,16 @@ typedef struct syn_gemm_rs_args {
   void* out;                    /* [M / world, N] */
   int32_t ldo;                  /* 0 = N */
   uint32_t* counters;
+  /* Optional transport by somebody else (copy engines): with `send_buf` set, the tiles of a wave
+   * for another rank are stored into the LOCAL buffer send_buf[target][M / world][N] (16 bit) and
+   * the LOCAL flag send_flags[target] is raised to the epoch when the wave is complete; the kernel
+   * then writes nothing to a peer.  The caller moves each slab to stage.ptrs[target] +
+   * ((epoch & 1) * world + rank) * slab and raises recv_flags.ptrs[target][remote_signals[w]]
+   * (e.g. syn_flag_wait_stream + syn_memcpy_async + syn_flag_set on side streams).  A kernel that
+   * gives up on a timed-out wait still raises every send flag, so such a stream cannot be left
+   * waiting; the error is in the status block. */
+  void* send_buf;
+  uint64_t* send_flags;         /* device uint64[world] */
 } syn_gemm_rs_args;
 int syn_gemm_rs(const syn_gemm_rs_args* args, const syn_schedule* src_sched, const syn_schedule* dst_sched,
                 void* stream);

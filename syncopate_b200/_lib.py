@@ -122,6 +122,8 @@ class GemmRsArgs(C.Structure):
         ("out", C.c_void_p),
         ("ldo", C.c_int32),
         ("counters", C.c_void_p),
+        ("send_buf", C.c_void_p),
+        ("send_flags", C.c_void_p),
     ]
 
 
@@ -256,6 +258,8 @@ def _declare(l: C.CDLL) -> None:
     l.syn_flag_set.argtypes = [C.c_void_p, C.c_uint64, C.c_void_p]
     l.syn_flag_wait.restype = C.c_int
     l.syn_flag_wait.argtypes = [C.c_void_p, C.c_uint64, C.c_uint64, C.c_void_p, C.c_int, C.c_void_p]
+    l.syn_flag_wait_stream.restype = C.c_int
+    l.syn_flag_wait_stream.argtypes = [C.c_void_p, C.c_uint64, C.c_void_p]
     l.syn_ag_gemm.restype = C.c_int
     l.syn_ag_gemm.argtypes = [C.POINTER(AgGemmArgs), C.POINTER(Schedule), C.c_void_p]
     l.syn_copy.restype = C.c_int

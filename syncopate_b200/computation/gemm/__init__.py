@@ -204,9 +204,13 @@ def gemm_rs(
     timeout_ns: int = 0,
     status=None,
     stream=None,
+    send_buf: Optional[torch.Tensor] = None,
+    send_flags: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """GEMM + reduce-scatter.  ``a`` ``[M, K_local]``, ``b`` ``[N, K_local]``; ``out``
-    ``[M / world, N]`` receives the fp32 sum over ranks of this rank's row slab."""
+    ``[M / world, N]`` receives the fp32 sum over ranks of this rank's row slab.  With ``send_buf``
+    ``[world, M / world, N]`` and ``send_flags`` (int64 ``[world]``) the kernel stores the slabs
+    for other ranks locally and raises the local flag of each; moving them is the caller's job."""
     g = _gemm_args(a, b, None, num_sms, block_n, group_size_m, epoch, timeout_ns, status)
     _check_mat("out", out)
     args = L.GemmRsArgs()
@@ -218,6 +222,9 @@ def gemm_rs(
     args.out = out.data_ptr()
     args.ldo = out.stride(0)
     args.counters = _ptr(counters)
+    if send_buf is not None:
+        args.send_buf = send_buf.data_ptr()
+        args.send_flags = send_flags.data_ptr()
     s, keep1 = _schedule_struct(src_schedule)
     d, keep2 = _schedule_struct(dst_schedule)
     rc = L.lib().syn_gemm_rs(C.byref(args), C.byref(s), C.byref(d), _stream_ptr(stream))

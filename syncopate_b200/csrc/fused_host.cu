@@ -135,6 +135,8 @@ int syn_gemm_rs(const syn_gemm_rs_args* args, const syn_schedule* src_sched, con
   const int world = args->stage.world, rank = args->stage.rank;
   if (args->recv_flags.world != world || args->recv_flags.rank != rank) return SYN_ERR_INVALID;
   if (args->out == nullptr || args->counters == nullptr) return SYN_ERR_INVALID;
+  if (args->send_buf != nullptr && (args->send_flags == nullptr || (reinterpret_cast<uintptr_t>(args->send_buf) & 15)))
+    return SYN_ERR_INVALID;
   if (src_sched->ndim != 2 || src_sched->target_ranks == nullptr) return SYN_ERR_INVALID;
   if (g.M % world != 0) return SYN_ERR_SHAPE;
   const int slab_rows = g.M / world;
@@ -179,6 +181,12 @@ int syn_gemm_rs(const syn_gemm_rs_args* args, const syn_schedule* src_sched, con
       slab_ld = ldo;
       rt.flag = nullptr;
       rt.reduce = 1;
+    } else if (args->send_buf != nullptr) {
+      // transport by the caller: local send slab, local flag
+      slab0 = static_cast<char*>(args->send_buf) + static_cast<size_t>(tgt) * slab_elems * 2;
+      slab_ld = g.N;
+      rt.flag = args->send_flags + tgt;
+      rt.reduce = 0;
     } else {
       slab0 = static_cast<char*>(args->stage.ptrs[tgt]) + (half + rank) * slab_elems * 2;
       slab_ld = g.N;
@@ -221,6 +229,7 @@ int syn_gemm_rs(const syn_gemm_rs_args* args, const syn_schedule* src_sched, con
   if (dynamic_sched()) p.sched = args->counters + SYN_MAX_WAVES + SYN_MAX_COMM_OPS;
   p.c = args->out;
   p.ldc = ldo;
+  p.raise_flags_on_abort = args->send_buf != nullptr ? 1 : 0;
   grid = std::min(grid, p.total_tiles);
   if (grid <= 0) return SYN_ERR_INVALID;
   return gemm_launch(p, bn, /*fused=*/true, grid, static_cast<cudaStream_t>(stream));

@@ -78,6 +78,7 @@ struct GemmParams {
   int32_t num_waves;
   int32_t num_comm_ops;
   int32_t wide_store;     // 1: TMA-store routes send 64-row x 128-column boxes (256-byte row segments)
+  int32_t raise_flags_on_abort;  // 1: a CTA that gave up on a wait raises every route flag before it leaves
   int32_t num_red;        // staged partial slabs to add in `reduce` routes
   int32_t red_ld;
   int32_t red_row0;       // global C row of the staged slabs' row 0
@@ -594,6 +595,16 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
       p.status[1] = abort_info[0];
       p.status[2] = abort_info[1];
       p.status[3] = static_cast<int>(blockIdx.x);
+    }
+  }
+  if constexpr (FUSED) {
+    // Somebody outside the kernel may be waiting for the wave flags without a bound of its own (a
+    // stream memory operation): after a failed wait the data are lost anyway, so let everybody go on.
+    if (threadIdx.x == 0 && *abort_word != 0 && p.raise_flags_on_abort) {
+      for (int w = 0; w < p.num_waves; ++w) {
+        const int r = p.waves[w].route;
+        if (r >= 0 && p.routes[r].flag != nullptr) st_release_sys_u64(p.routes[r].flag, p.signal_value);
+      }
     }
   }
 }

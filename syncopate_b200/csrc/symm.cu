@@ -145,6 +145,32 @@ int syn_flag_wait(const uint64_t* flag, uint64_t value, uint64_t timeout_ns, int
   return SYN_OK;
 }
 
+int syn_flag_wait_stream(const uint64_t* flag, uint64_t value, void* stream) {
+  using namespace syn;
+  if (flag == nullptr) return SYN_ERR_INVALID;
+  typedef CUresult (*wait_value_fn)(CUstream, CUdeviceptr, cuuint64_t, unsigned int);
+  static wait_value_fn wait_value = nullptr;
+  static bool looked_up = false;
+  if (!looked_up) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuStreamWaitValue64", &fn, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      wait_value = reinterpret_cast<wait_value_fn>(fn);
+    looked_up = true;
+  }
+  if (wait_value == nullptr) return SYN_ERR_UNSUPPORTED;
+  CUresult r = wait_value(static_cast<CUstream>(stream), reinterpret_cast<CUdeviceptr>(flag), value,
+                          CU_STREAM_WAIT_VALUE_GEQ);
+  if (r != CUDA_SUCCESS) {
+    char buf[64];
+    snprintf(buf, sizeof(buf), "CUresult %d", static_cast<int>(r));
+    set_cuda_error("cuStreamWaitValue64", buf);
+    return SYN_ERR_CUDA;
+  }
+  return SYN_OK;
+}
+
 int syn_ctx_create(int rank, int world, int device, const char* rendezvous_dir, syn_ctx** out) {
   using namespace syn;
   if (out == nullptr || world <= 0 || world > SYN_MAX_WORLD || rank < 0 || rank >= world) return SYN_ERR_INVALID;

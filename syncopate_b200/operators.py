@@ -184,8 +184,16 @@ class GemmReduceScatter:
     """``out[M / world, N] = sum over ranks of (A_r[M, K_r] @ B_r[N, K_r]^T)[own rows]``."""
 
     def __init__(self, ctx: SymmetricContext, M: int, N: int, dtype=torch.bfloat16, plan: str = "direct",
-                 num_sms: int = 0, block_n: int = 0, timeout_ns: int = 0, lockstep: bool = True):
+                 num_sms: int = 0, block_n: int = 0, timeout_ns: int = 0, lockstep: bool = True, comm: str = "sm",
+                 copy_streams: int = 2):
+        """``comm="sm"``: the GEMM's epilogue stores each tile straight into the target rank's staging
+        slab.  ``comm="ce"`` (experimental): the epilogue stores locally and raises a local flag per
+        slab; side streams wait for the flag (a stream memory operation), move the slab with a copy
+        engine and raise the target's flag."""
+        if comm not in ("sm", "ce"):
+            raise ValueError("comm must be 'sm' or 'ce'")
         self.ctx = ctx
+        self.comm = comm
         self.lockstep = lockstep  # see AllGatherGemm: keeps the ranks' push targets disjoint in time
         self.world, self.rank = ctx.world, ctx.rank
         self.M, self.N, self.dtype = M, N, dtype
@@ -201,6 +209,31 @@ class GemmReduceScatter:
         self.stage = ctx.alloc((2, self.world, self.slab, N), dtype)
         self.flags = ctx.alloc((max(self.info.recv_signal_num, 1),), torch.int64)
         self.counters = torch.zeros(NUM_COUNTERS, dtype=torch.int32, device=ctx.device)
+        self.send = self.send_flags = None
+        if comm == "ce":
+            self.send = torch.empty(self.world, self.slab, N, dtype=dtype, device=ctx.device)
+            self.send_flags = torch.zeros(self.world, dtype=torch.int64, device=ctx.device)
+            self._copy_streams = [torch.cuda.Stream(device=ctx.device) for _ in range(max(1, copy_streams))]
+
+    def transport_program(self, epoch: int):
+        """``[(local flag ptr, src ptr, dst ptr, nbytes, remote flag ptr)]`` in wave order: what the
+        side streams do for the slabs of other ranks in the call with this epoch (the staging half
+        alternates with the epoch's parity)."""
+        elem = torch.empty((), dtype=self.dtype).element_size()
+        slab_bytes = self.slab * self.N * elem
+        half = (epoch & 1) * self.world
+        targets = self.src_schedule.gen_target_rank_list()
+        prog = []
+        for w, tgt in enumerate(targets):
+            tgt = self.rank if tgt is None or tgt < 0 else int(tgt)
+            if tgt == self.rank or self.remote_signals[w] < 0:
+                continue
+            prog.append((self.send_flags.data_ptr() + 8 * tgt,
+                         self.send.data_ptr() + tgt * slab_bytes,
+                         self.stage.symm.ptrs[tgt] + (half + self.rank) * slab_bytes,
+                         slab_bytes,
+                         self.flags.symm.ptrs[tgt] + 8 * int(self.remote_signals[w])))
+        return prog
 
     def __call__(self, a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, stream=None):
         if out is None:
@@ -211,6 +244,23 @@ class GemmReduceScatter:
                         timeout_ns=self.timeout_ns, stream=stream)
         if self.lockstep:
             self.ctx.barrier(stream)
+        if self.comm == "ce":
+            cur = stream or torch.cuda.current_stream()
+            # the kernel first (a launch that fails must not leave stream waits behind), then the
+            # transport: wait for the slab's local flag, copy, raise the target's flag
+            gemm_rs(a, b, out, self.src_schedule, self.dst_schedule, self.remote_signals, self.stage.symm,
+                    self.flags.symm, self.counters, epoch=self.epoch, num_sms=self.num_sms, block_n=self.block_n,
+                    timeout_ns=self.timeout_ns, status=self.ctx.status, stream=cur, send_buf=self.send,
+                    send_flags=self.send_flags)
+            lib = _raw_lib()
+            for i, (lflag, src, dst, nbytes, rflag) in enumerate(self.transport_program(self.epoch)):
+                sp = self._copy_streams[i % len(self._copy_streams)].cuda_stream
+                _L.check(lib.syn_flag_wait_stream(lflag, self.epoch, sp), "syn_flag_wait_stream")
+                _L.check(lib.syn_memcpy_async(dst, src, nbytes, sp), "syn_memcpy_async")
+                _L.check(lib.syn_flag_set(rflag, self.epoch, sp), "syn_flag_set")
+            for s in self._copy_streams:
+                cur.wait_stream(s)  # the next call's kernel may overwrite the send slabs
+            return out
         return gemm_rs(a, b, out, self.src_schedule, self.dst_schedule, self.remote_signals, self.stage.symm,
                        self.flags.symm, self.counters, epoch=self.epoch, num_sms=self.num_sms,
                        block_n=self.block_n, timeout_ns=self.timeout_ns, status=self.ctx.status, stream=stream)

@@ -60,8 +60,11 @@ def main():
             ctx.barrier()  # nobody may overwrite its shard while a peer still pulls it
             torch.cuda.synchronize()
 
-    for kind, M, N, Kl in (("direct", 256 * world, 512, 256), ("a2a", 128 * world, 1024, 512), ("direct", 8192, 8192, 28672 // world)):
-        op = GemmReduceScatter(ctx, M, N, dt, plan=kind, timeout_ns=2_000_000_000)
+    # comm "sm": the epilogue pushes tiles to the peers; "ce": local slabs moved by copy engines
+    for kind, M, N, Kl, comm in (("direct", 256 * world, 512, 256, "sm"), ("a2a", 128 * world, 1024, 512, "sm"),
+                                 ("direct", 8192, 8192, 28672 // world, "sm"), ("direct", 256 * world, 512, 256, "ce"),
+                                 ("a2a", 128 * world, 1024, 512, "ce")):
+        op = GemmReduceScatter(ctx, M, N, dt, plan=kind, timeout_ns=2_000_000_000, comm=comm)
         a = seeded(2000 + rank, (M, Kl), 1.0, dt, dev)
         b = seeded(3000 + rank, (N, Kl), 0.02, dt, dev)
         part = a.float() @ b.float().t()
@@ -72,7 +75,7 @@ def main():
             ctx.check()
             e = rel(out, ref)
             if not e < TOL:
-                failures.append(f"gemm_rs {kind} M={M} it={it} rank={rank}: relerr={e:.3e}")
+                failures.append(f"gemm_rs {kind}/{comm} M={M} it={it} rank={rank}: relerr={e:.3e}")
 
     # ---- attention operators (reference: gather with torch.distributed, dense fp32 attention per head)
     def dense(q, k, v, causal, q_pos=None, k_pos=None):
