@@ -471,12 +471,13 @@ def run_own_arm(args):
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_ms,
                     "path": e2e_path},
-            "gpu_launches": args.steps,
+            # one GEMM kernel per step; with more than one rank also the operator's lockstep barrier kernel
+            "gpu_launches": args.steps * (2 if world > 1 else 1),
             "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peak, "unit": "TFLOP/s",
                          "frac": per_gpu / peak,
                          # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this
                          # workload (ncu capture summarised in profiles/gemm2_kernel_bn256_cfg1_tp8_local.md)
-                         "traffic": 605.4e6 if world == 1 else None,
+                         "traffic": 610.7e6 if world == 1 else None,
                          "algorithmic_bytes": (M * K_DIM + n_local * K_DIM + M * n_local) * 2,
                          "peak_source": f"{peaks['source']} cuBLAS bf16 burst (MEASURED_PEAKS.json)",
                          "frac_of_sustained": per_gpu / peaks["bf16_tflops_sustained"] if peaks["bf16_tflops_sustained"] else None,
