@@ -21,7 +21,7 @@ from .communication.common_descriptors import (
     build_ring_all_gather_plan,
 )
 from .computation.gemm import ag_gemm, gemm, gemm_rs
-from .computation.gemm.plan import rs_remote_signals
+from .computation.gemm.plan import rs_remote_signals, rs_transport_program
 from .interface import lower_comm_plan_to_raw_schedules
 from .runtime import SymmetricContext
 
@@ -216,24 +216,11 @@ class GemmReduceScatter:
             self._copy_streams = [torch.cuda.Stream(device=ctx.device) for _ in range(max(1, copy_streams))]
 
     def transport_program(self, epoch: int):
-        """``[(local flag ptr, src ptr, dst ptr, nbytes, remote flag ptr)]`` in wave order: what the
-        side streams do for the slabs of other ranks in the call with this epoch (the staging half
-        alternates with the epoch's parity)."""
+        """The side streams' work for the call with this epoch (see ``rs_transport_program``)."""
         elem = torch.empty((), dtype=self.dtype).element_size()
-        slab_bytes = self.slab * self.N * elem
-        half = (epoch & 1) * self.world
-        targets = self.src_schedule.gen_target_rank_list()
-        prog = []
-        for w, tgt in enumerate(targets):
-            tgt = self.rank if tgt is None or tgt < 0 else int(tgt)
-            if tgt == self.rank or self.remote_signals[w] < 0:
-                continue
-            prog.append((self.send_flags.data_ptr() + 8 * tgt,
-                         self.send.data_ptr() + tgt * slab_bytes,
-                         self.stage.symm.ptrs[tgt] + (half + self.rank) * slab_bytes,
-                         slab_bytes,
-                         self.flags.symm.ptrs[tgt] + 8 * int(self.remote_signals[w])))
-        return prog
+        return rs_transport_program(self.rank, self.world, self.slab * self.N * elem, epoch, self.src_schedule,
+                                    self.remote_signals, self.send.data_ptr(), self.send_flags.data_ptr(),
+                                    self.stage.symm.ptrs, self.flags.symm.ptrs)
 
     def __call__(self, a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, stream=None):
         if out is None:

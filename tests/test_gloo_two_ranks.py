@@ -62,6 +62,50 @@ def _worker(rank, world, port, results):
             wave = src_sched.gen_target_rank_list().index(rank)
             assert table[src_rank][wave] == sig
 
+        # ---- GEMM + reduce-scatter with the slabs moved by somebody else than the kernel: every rank
+        # runs its transport program against a byte image of all ranks' staging buffers (addresses are
+        # offsets into per-rank arrays here), then the owner sums the staged slabs with its own
+        from syncopate_b200.computation.gemm.plan import rs_transport_program
+
+        M, Nn, slab = 256, 64, 256 // world
+        slab_bytes = slab * Nn * 2
+        g2 = torch.Generator().manual_seed(300 + rank)
+        partial = torch.randn(M, Nn, generator=g2).to(dt)             # this rank's partial product
+        BASE = 1 << 20                                                 # "address" of a rank's staging / flag arrays
+        for epoch in (1, 2):
+            prog = rs_transport_program(rank, world, slab_bytes, epoch, rs_low[rank]["src"], sent,
+                                        send_ptr=0, send_flags_ptr=0, stage_ptrs=[BASE * (t + 1) for t in range(world)],
+                                        flag_ptrs=[BASE * (t + 1) for t in range(world)])
+            assert len(prog) == world - 1
+            moves = []
+            for lflag, src_addr, dst_addr, nbytes, rflag in prog:
+                tgt = dst_addr // BASE - 1
+                assert lflag == 8 * tgt and src_addr == tgt * slab_bytes and nbytes == slab_bytes
+                slot = (dst_addr - BASE * (tgt + 1)) // slab_bytes
+                assert slot == (epoch & 1) * world + rank
+                moves.append((tgt, slot, (rflag - BASE * (tgt + 1)) // 8, partial[tgt * slab:(tgt + 1) * slab].clone()))
+            everyone = [None] * world
+            dist.all_gather_object(everyone, moves)
+            staged = {}
+            raised = set()
+            for src_rank, mv in enumerate(everyone):
+                for tgt, slot, flag, data in mv:
+                    if tgt == rank:
+                        assert slot not in staged      # no two senders share a slot
+                        staged[slot] = data
+                        raised.add(flag)
+            # the flags that were raised here are exactly the ones this rank's owner wave waits for
+            waits = {sig for src_rank, sig in zip(dst.gen_target_rank_list(), dst.gen_signal_lists())
+                     if src_rank >= 0 and src_rank != rank}
+            assert raised == waits
+            total = partial[rank * slab:(rank + 1) * slab].float()
+            for data in staged.values():
+                total = total + data.float()
+            parts = [None] * world
+            dist.all_gather_object(parts, partial)
+            want = sum(p_[rank * slab:(rank + 1) * slab].float() for p_ in parts)
+            assert torch.allclose(total, want, atol=1e-6)
+
         # ---- Ulysses reshard: the comm warps' copy list moves exactly the bytes the plan describes
         shape = (3, 1, 2 * world, 16, 8)
         _g, a2a_info, a2a_low = _plan({
