@@ -524,67 +524,7 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
       mbar_wait(&o_full[x], ux & 1u, abort_word, p.timeout_ns);
       tc_fence_after();
 
-      // ---- finalise this visit and merge with what earlier waves left for the row.  Every lane runs
-      // the loop (the tensor-memory loads are warp-wide); rows past the end only skip memory accesses.
-      {
-        const int srow = qt * ATTN_BM + row;
-        const bool valid = srow < p.Sq;
-        const size_t stat_idx = (static_cast<size_t>(z) * p.Hq + h) * p.Sq + (valid ? srow : 0);
-        uint4* o_ptr = reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.o) +
-                                                (z * p.o_sz + h * p.o_sh + static_cast<int64_t>(valid ? srow : 0) * p.o_ss) * 2);
-        const bool seen = valid && p.visit[stat_idx] == p.epoch;
-        float lse_new = (l > 0.f) ? m + log2f(l) : -INFINITY;
-        const float inv_l = (l > 0.f) ? 1.f / l : 0.f;
-        float w_new = inv_l, w_old = 0.f;
-        if (seen) {
-          const float lse_old = p.lse[stat_idx];
-          const float mm = fmaxf(lse_old, lse_new);
-          if (mm == -INFINITY) {
-            w_new = 0.f;
-            w_old = 1.f;
-          } else {
-            const float e_old = exp2f(lse_old - mm), e_new = exp2f(lse_new - mm);
-            const float tot = e_old + e_new;
-            w_old = e_old / tot;
-            w_new = e_new / tot * inv_l;
-            lse_new = mm + log2f(tot);
-          }
-        }
-#pragma unroll 1
-        for (int v = 0; v < ATTN_D / 32; ++v) {
-          uint32_t r[32];
-          tmem_ld_32x32(o_tmem + v * 32, r);
-          tmem_ld_wait();
-          if (valid) {
-#pragma unroll
-            for (int c4 = 0; c4 < 4; ++c4) {
-              float f[8];
-#pragma unroll
-              for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(r[c4 * 8 + i]) * w_new;
-              if (seen) {
-                const uint4 old = o_ptr[v * 4 + c4];
-                const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  const float2 tt = unpack2(ow[i], p.dtype);
-                  f[2 * i] += tt.x * w_old;
-                  f[2 * i + 1] += tt.y * w_old;
-                }
-              }
-              uint4 out;
-              out.x = BF16 ? pack2_bf16(f[0], f[1]) : pack2_f16(f[0], f[1]);
-              out.y = BF16 ? pack2_bf16(f[2], f[3]) : pack2_f16(f[2], f[3]);
-              out.z = BF16 ? pack2_bf16(f[4], f[5]) : pack2_f16(f[4], f[5]);
-              out.w = BF16 ? pack2_bf16(f[6], f[7]) : pack2_f16(f[6], f[7]);
-              o_ptr[v * 4 + c4] = out;
-            }
-          }
-        }
-        if (valid) {
-          p.lse[stat_idx] = lse_new;
-          p.visit[stat_idx] = p.epoch;
-        }
-      }
+      attn_finish_row<BF16>(p, z, h, qt, row, m, l, o_tmem);
       // O_x has been read: the next unit's first product may overwrite it
       tc_fence_before();
       mbar_arrive(&o_empty[x]);

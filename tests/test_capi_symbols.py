@@ -46,6 +46,9 @@ def test_argument_errors_are_reported_without_a_gpu():
     assert lib.syn_gemm_pick_block_n(0, 8, 148) == -1
     out = ctypes.c_void_p()
     assert lib.syn_ctx_create(3, 2, 0, b"/tmp/x", ctypes.byref(out)) == -1  # rank >= world
+    assert lib.syn_flag_wait_stream(None, 1, None) == -1
+    assert lib.syn_attention_plan(None, None, None, None, None) == -1
+    assert lib.syn_gemm_rs(None, None, None, None) == -1
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
