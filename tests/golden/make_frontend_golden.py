@@ -1,6 +1,6 @@
 """Generates ``frontend_golden.json`` by running the REFERENCE front end over the case grid.
 
-    PYTHONPATH=/root/reference python tests/golden/make_frontend_golden.py
+    PYTHONPATH=<reference checkout> python tests/golden/make_frontend_golden.py
 
 Needs the reference checkout on PYTHONPATH (it is pure Python: torch + triton.cdiv).  The JSON is
 committed; the tests only read it.
