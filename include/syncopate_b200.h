@@ -218,10 +218,14 @@ int syn_ag_gemm(const syn_ag_gemm_args* args, const syn_schedule* a_sched, void*
  * of wave w (rows of `src_sched`, the RawSchedule of the partial-C buffer) go, as 16-bit values,
  * straight from the epilogue into the target rank's staging slab stage.ptrs[target] +
  * ((epoch & 1) * world + rank) * slab, and once the wave's last tile has landed
- * recv_flags.ptrs[target][remote_signals[w]] is raised.  The wave whose target is this rank (last
- * in the plan) waits for the flags listed in `dst_sched` (RawSchedule of the receive buffer:
- * target = sending rank, signal = local flag), adds the staged partial sums to its own
- * accumulators in fp32 and writes `out` [M / world, N].  gemm.c is unused and may be NULL. */
+ * recv_flags.ptrs[target][remote_signals[w]] is raised.  A target may get its slab in several waves
+ * (row pieces).  `dst_sched` is the RawSchedule of the receive buffer (target = sending rank,
+ * signal = local flag; rows and columns are its last two axes): the rows kept here are cut into
+ * the row pieces that the senders' waves arrive in, and each piece becomes one wave that waits for
+ * the flags of exactly its rows from every other rank, adds the staged partial sums to its own
+ * accumulators in fp32 (fixed order: ascending sender rank as first met in `dst_sched`) and writes
+ * `out` [M / world, N].  Every other rank must send every piece exactly once.  gemm.c is unused
+ * and may be NULL. */
 typedef struct syn_gemm_rs_args {
   syn_gemm_args gemm;
   syn_symm stage;               /* 16-bit [2, world, M / world, N] on every rank */
@@ -231,18 +235,38 @@ typedef struct syn_gemm_rs_args {
   int32_t ldo;                  /* 0 = N */
   uint32_t* counters;
   /* Optional transport by somebody else (copy engines): with `send_buf` set, the tiles of a wave
-   * for another rank are stored into the LOCAL buffer send_buf[target][M / world][N] (16 bit) and
-   * the LOCAL flag send_flags[target] is raised to the epoch when the wave is complete; the kernel
-   * then writes nothing to a peer.  The caller moves each slab to stage.ptrs[target] +
-   * ((epoch & 1) * world + rank) * slab and raises recv_flags.ptrs[target][remote_signals[w]]
-   * (e.g. syn_flag_wait_stream + syn_memcpy_async + syn_flag_set on side streams).  A kernel that
-   * gives up on a timed-out wait still raises every send flag, so such a stream cannot be left
-   * waiting; the error is in the status block. */
+   * for another rank are stored into the LOCAL buffer send_buf[target][M / world][N] (16 bit, at the
+   * wave's rows inside the slab) and the LOCAL flag send_flags[w] (w = the wave's index in
+   * `src_sched`) is raised to the epoch when the wave is complete; the kernel then writes nothing
+   * to a peer.  The caller moves each wave's rows to stage.ptrs[target] + ((epoch & 1) * world +
+   * rank) * slab and raises recv_flags.ptrs[target][remote_signals[w]] (syn_ce_run below does this
+   * on side streams).  A kernel that gives up on a timed-out wait still raises every send flag, so
+   * such a stream cannot be left waiting; the error is in the status block. */
   void* send_buf;
-  uint64_t* send_flags;         /* device uint64[world] */
+  uint64_t* send_flags;         /* device uint64[num_waves of src_sched] */
 } syn_gemm_rs_args;
 int syn_gemm_rs(const syn_gemm_rs_args* args, const syn_schedule* src_sched, const syn_schedule* dst_sched,
                 void* stream);
+
+/* A copy-engine program: the host-side form of a rank's CopyEngineOp / IntraNodeSignal /
+ * WaitIntraNodeSignal records (syncopate/communication/comm_runtime/operations.py:9-69, interpreted
+ * by communication_context.py:129-160) with every address resolved.  Step i runs on stream
+ * streams[step.stream % num_streams], in array order per stream:
+ *   wait_flag != NULL : stream waits until *wait_flag >= value (syn_flag_wait_stream: needs no SM)
+ *   bytes > 0         : cudaMemcpyAsync(dst, src, bytes) (peer-mapped pointers allowed)
+ *   set_flag != NULL  : *set_flag = value, ordered after the copy (syn_flag_set)
+ * One call issues the whole program from C, so a program of a few dozen steps costs a few dozen
+ * driver calls and nothing else. */
+typedef struct syn_ce_step {
+  const uint64_t* wait_flag;
+  void* dst;
+  const void* src;
+  size_t bytes;
+  uint64_t* set_flag;
+  int32_t stream;
+  int32_t reserved;
+} syn_ce_step;
+int syn_ce_run(const syn_ce_step* steps, int num_steps, void* const* streams, int num_streams, uint64_t value);
 
 /* ------------------------------------------------------------------ attention
  * Flash-attention forward over a wave schedule (replaces the TLX kernel
@@ -329,6 +353,13 @@ typedef struct syn_copy_op {
   uint64_t src_pitch, dst_pitch;
   uint32_t rows, row_bytes;
   int32_t flag_rank, flag;
+  /* SMCopyOp.reduce_op (operations.py:31, executed by tma_persistent_copy.py:129-169 in the
+   * reference): 0 = plain copy; 1 = dst += src for 16-bit elements of type `dtype` (SYN_DTYPE_*),
+   * performed as vector reductions at the memory that owns dst, so reducing copies from several
+   * ranks into the same bytes may overlap in time; every addition rounds to the element type.
+   * Only syn_copy executes reducing copies (the kernels' comm warps move bytes and do not add). */
+  int32_t reduce;
+  int32_t dtype;
 } syn_copy_op;
 
 typedef struct syn_attn_comm {

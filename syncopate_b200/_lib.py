@@ -127,6 +127,40 @@ class GemmRsArgs(C.Structure):
     ]
 
 
+class CeStep(C.Structure):
+    """``syn_ce_step``: wait for a flag, copy, raise a flag - on one of the caller's streams."""
+
+    _fields_ = [
+        ("wait_flag", C.c_void_p),
+        ("dst", C.c_void_p),
+        ("src", C.c_void_p),
+        ("bytes", C.c_size_t),
+        ("set_flag", C.c_void_p),
+        ("stream", C.c_int32),
+        ("reserved", C.c_int32),
+    ]
+
+
+def make_ce_program(steps):
+    """ctypes array of ``syn_ce_step`` from ``(wait_flag, dst, src, nbytes, set_flag, stream)`` tuples
+    (addresses as integers, 0 / None = absent)."""
+    arr = (CeStep * max(len(steps), 1))()
+    for i, (wait, dst, src, nbytes, flag, stream) in enumerate(steps):
+        arr[i].wait_flag = wait or None
+        arr[i].dst = dst or None
+        arr[i].src = src or None
+        arr[i].bytes = int(nbytes)
+        arr[i].set_flag = flag or None
+        arr[i].stream = int(stream)
+    return arr
+
+
+def ce_run(program, num_steps: int, streams, value: int) -> None:
+    """Issues a copy-engine program (``make_ce_program``) on ``streams`` (torch streams)."""
+    ptrs = (C.c_void_p * len(streams))(*[s.cuda_stream or None for s in streams])
+    check(lib().syn_ce_run(program, num_steps, ptrs, len(streams), value), "syn_ce_run")
+
+
 class AttnArgs(C.Structure):
     """``syn_attn_args``."""
 
@@ -194,6 +228,8 @@ class CopyOp(C.Structure):
         ("row_bytes", C.c_uint32),
         ("flag_rank", C.c_int32),
         ("flag", C.c_int32),
+        ("reduce", C.c_int32),
+        ("dtype", C.c_int32),
     ]
 
 
@@ -260,6 +296,8 @@ def _declare(l: C.CDLL) -> None:
     l.syn_flag_wait.argtypes = [C.c_void_p, C.c_uint64, C.c_uint64, C.c_void_p, C.c_int, C.c_void_p]
     l.syn_flag_wait_stream.restype = C.c_int
     l.syn_flag_wait_stream.argtypes = [C.c_void_p, C.c_uint64, C.c_void_p]
+    l.syn_ce_run.restype = C.c_int
+    l.syn_ce_run.argtypes = [C.POINTER(CeStep), C.c_int, C.POINTER(C.c_void_p), C.c_int, C.c_uint64]
     l.syn_ag_gemm.restype = C.c_int
     l.syn_ag_gemm.argtypes = [C.POINTER(AgGemmArgs), C.POINTER(Schedule), C.c_void_p]
     l.syn_copy.restype = C.c_int

@@ -3,17 +3,23 @@
 Same constructor, attributes and methods as the reference's
 syncopate/communication/comm_runtime/communication_context.py (:15-305), on a different substrate:
 buffers and flag arrays are CUDA-IPC symmetric allocations (``syncopate_b200.runtime``) instead of
-NVSHMEM tensors; copy-engine ops are peer ``cudaMemcpyAsync`` calls; flag sets / waits are
-one-thread kernels with bounded waits instead of stream memory operations.  Flags carry
+NVSHMEM tensors; copy-engine ops are peer ``cudaMemcpyAsync`` calls; SM copies (plain and reducing)
+run on the ``syn_copy`` kernel; flag sets are stream memory operations and flag waits bounded
+one-thread kernels (or stream memory operations with ``stream_waits=True``).  Flags carry
 ``signal_value`` (1 after ``reset_signals``; ``next_epoch()`` raises it so that a loop needs neither
 a reset nor a barrier per iteration).
 
+``CommContext(rank, info)`` allocates from the process's symmetric context
+(``syncopate_b200.runtime.current_context()``, opened by ``init_from_env``), as the reference
+allocates from the process-wide NVSHMEM heap; ``symmetric=`` names another one (tests that emulate
+several ranks in one process).
+
 The fused kernels (``syncopate_b200.computation``) move data themselves; ``execute()`` is the
-un-fused path (``CodeGenOptions(copy_engine=True)`` programs, or SM box copies done as strided
-device copies).
+un-fused path: ``CodeGenOptions(copy_engine=True)`` programs, or SM box copies run by ``syn_copy``.
 """
 from __future__ import annotations
 
+import ctypes as C
 from typing import Dict, List, Optional
 
 import torch
@@ -28,18 +34,25 @@ from syncopate_b200.communication.comm_runtime.operations import (
     WaitIntraNodeSignal,
 )
 from syncopate_b200.communication.descriptor import CollectiveOp, SignalType
-from syncopate_b200.runtime import SymmetricContext, SymmetricTensor
+from syncopate_b200.computation.attn.plan import box_copy_ops
+from syncopate_b200.runtime import SymmetricTensor, current_context
 
 SIGNAL_DTYPE = torch.int64  # 64-bit flag words (NVSHMEM_SIGNAL_DTYPE in the reference is uint64)
+_SYN_DTYPES = {torch.float16: L.SYN_DTYPE_F16, torch.bfloat16: L.SYN_DTYPE_BF16}
+_COPY_MAX_OPS = 64  # pieces one syn_copy launch takes
 
 
 class CommContext:
     """Runtime state of one rank for one ``CommInfo``."""
 
-    def __init__(self, rank: int, info: CommInfo, multi_info: bool = False, *,
-                 symmetric: Optional[SymmetricContext] = None, timeout_ns: int = 0):
+    def __init__(self, rank: int, info: CommInfo, multi_info: bool = False, *, symmetric=None, timeout_ns: int = 0,
+                 stream_waits: bool = False):
+        """``stream_waits``: run ``WaitIntraNodeSignal`` as a stream memory operation (needs no SM, so a
+        persistent kernel that fills the GPU cannot starve it; it has no time bound of its own, so
+        use it only for flags that a bounded kernel raises on every path).  Default: a one-thread
+        kernel whose wait is bounded by ``timeout_ns``."""
         if symmetric is None:
-            raise ValueError("pass the rank's SymmetricContext (syncopate_b200.runtime.init_from_env)")
+            symmetric = current_context()
         if info.local_world_size == 0:
             info.local_world_size = info.world_size
         self.rank = rank
@@ -48,6 +61,7 @@ class CommContext:
         self.info = info
         self.symmetric = symmetric
         self.timeout_ns = timeout_ns
+        self.stream_waits = stream_waits
         self.signal_value = 1
         extra = 100 if multi_info else 0  # head-room for later infos, as the reference leaves
 
@@ -71,7 +85,7 @@ class CommContext:
         self._make_streams()
 
     def _make_streams(self) -> None:
-        self.streams = [torch.cuda.Stream() for _ in range(len(self.info.operations[self.rank]))]
+        self.streams = [torch.cuda.Stream(device=self.symmetric.device) for _ in range(len(self.info.operations[self.rank]))]
         self.compute_stream = None
 
     # ---- symmetric tables for the fused kernels
@@ -118,6 +132,45 @@ class CommContext:
             return self.recv_signal_bufs[rank % self.info.local_world_size]
         raise NotImplementedError(f"Signal type {kind} not implemented yet.")
 
+    def _sm_copy(self, op: SMCopyOp, sp) -> None:
+        """One ``SMCopyOp`` (an N-D box, optionally reducing) on the SM copy kernel: the box is cut
+        into 2-D strided pieces and handed to ``syn_copy``, at most 64 pieces per launch."""
+        src_t, dst_t = self._buffers[op.src], self._buffers[op.dst]
+        elem = src_t.dtype.itemsize
+        src_off = [a.start for a in op.src_slice]
+        dst_off = [a.start for a in op.dst_slice]
+        extent_s = [a.end - a.start for a in op.src_slice]
+        extent_d = [a.end - a.start for a in op.dst_slice]
+        if extent_s != extent_d:
+            # same bytes, different box shapes (a reshaping copy): fall back on the flat view of both
+            if _numel(extent_s) != _numel(extent_d):
+                raise ValueError("source and destination boxes of an SM copy differ in size")
+            raise NotImplementedError("SM copies between boxes of different shape are not supported")
+        reduce = 0
+        if op.reduce_op is not None:
+            if src_t.dtype not in _SYN_DTYPES or dst_t.dtype != src_t.dtype:
+                raise NotImplementedError("reducing SM copies take fp16 / bf16 buffers of one type")
+            reduce = 1
+        pieces = box_copy_ops(src_t.shape, src_off, dst_t.shape, dst_off, extent_s, elem)
+        lib = L.lib()
+        status = self.symmetric.status.data_ptr()
+        n_sms = self.info.num_copy_sms if getattr(self.info, "num_copy_sms", 0) else 0
+        for first in range(0, len(pieces), _COPY_MAX_OPS):
+            ops = []
+            for so, do, rows, row_bytes, spitch, dpitch in pieces[first:first + _COPY_MAX_OPS]:
+                c = L.CopyOp()
+                c.src_rank, c.dst_rank = op.src_rank % self.info.local_world_size, op.dst_rank % self.info.local_world_size
+                c.src_buf, c.dst_buf = 0, 1
+                c.src_offset, c.dst_offset = so, do
+                c.src_pitch, c.dst_pitch = spitch, dpitch
+                c.rows, c.row_bytes = rows, row_bytes
+                c.flag_rank, c.flag = 0, -1
+                c.reduce = reduce
+                c.dtype = _SYN_DTYPES.get(src_t.dtype, 0)
+                ops.append(c)
+            comm, keep = L.make_attn_comm(ops, [src_t.symm, dst_t.symm], src_t.symm, None)
+            L.check(lib.syn_copy(C.byref(comm), n_sms, self.signal_value, self.timeout_ns, status, sp), "syn_copy")
+
     def execute(self, neglect_local: bool = False):
         """Issues this rank's op program on the communication streams."""
         lib = L.lib()
@@ -144,20 +197,17 @@ class CommContext:
                     elif isinstance(op, WaitIntraNodeSignal):
                         assert op.rank // lws == self.node_id
                         flag = self._flag_array(op.signal_type, op.rank)
-                        L.check(lib.syn_flag_wait(flag.data_ptr() + 8 * op.offset, self.signal_value, self.timeout_ns,
-                                                  status, op.offset, sp), "syn_flag_wait")
+                        if self.stream_waits:
+                            L.check(lib.syn_flag_wait_stream(flag.data_ptr() + 8 * op.offset, self.signal_value, sp),
+                                    "syn_flag_wait_stream")
+                        else:
+                            L.check(lib.syn_flag_wait(flag.data_ptr() + 8 * op.offset, self.signal_value,
+                                                      self.timeout_ns, status, op.offset, sp), "syn_flag_wait")
                     elif isinstance(op, SMCopyOp):
                         assert op.src_rank == self.rank or op.dst_rank == self.rank
                         if neglect_local and op.src_rank == op.dst_rank:
                             continue
-                        if op.reduce_op is not None:
-                            raise NotImplementedError(
-                                "reducing box copies run inside the fused GEMM epilogue (syn_gemm_rs), not here")
-                        src = self.comm_buffers[op.src][op.src_rank % lws]
-                        dst = self.comm_buffers[op.dst][op.dst_rank % lws]
-                        src_box = src[tuple(slice(a.start, a.end) for a in op.src_slice)]
-                        dst_box = dst[tuple(slice(a.start, a.end) for a in op.dst_slice)]
-                        dst_box.copy_(src_box.reshape(dst_box.shape), non_blocking=True)
+                        self._sm_copy(op, sp)
                     elif isinstance(op, CollectiveComm):
                         self._collective(op)
                     else:  # pragma: no cover
@@ -187,7 +237,10 @@ class CommContext:
         return self.info.num_copy_sms
 
     def get_graph(self) -> torch.cuda.CUDAGraph:
-        """Captures start_after / execute / end_before into a CUDA graph for replay."""
+        """Captures start_after / execute / end_before into a CUDA graph for replay.  The flag value
+        is captured with the graph: replay it with the same ``signal_value`` (``reset_signals``
+        between replays, as the reference's drivers do)."""
+        L.lib()  # resolve the library (and its driver entry points) outside the capture
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             self.start_after(torch.cuda.current_stream())
@@ -201,3 +254,10 @@ class CommContext:
             info.local_world_size = info.world_size
         self.info = info
         self._make_streams()
+
+
+def _numel(extent) -> int:
+    n = 1
+    for e in extent:
+        n *= int(e)
+    return n

@@ -12,6 +12,7 @@ from .all_to_all import (
     build_all_to_all_plan_dim,
     build_all_to_all_plan_dim_waves,
 )
+from .chunk_split import split_transfers_along_axis
 from .reduce_scatter import build_reduce_scatter_collective_plan, build_reduce_scatter_direct_reduce_plan
 
 __all__ = [
@@ -24,4 +25,5 @@ __all__ = [
     "build_all_to_all_plan_axis",
     "build_reduce_scatter_collective_plan",
     "build_reduce_scatter_direct_reduce_plan",
+    "split_transfers_along_axis",
 ]

@@ -54,18 +54,21 @@ def _check_mat(name: str, t: torch.Tensor) -> None:
 _WORKSPACES = {}
 
 
-def tail_workspace(device) -> torch.Tensor:
-    """Zeroed scratch (one per device, kept zero by the kernel) that lets the CTA-pair GEMM split the
-    tiles left over after the last full persistent round along K."""
-    key = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
+def tail_workspace(device, stream_ptr=None) -> torch.Tensor:
+    """Zeroed scratch (one per device and stream, kept zero by the kernel) that lets the CTA-pair
+    GEMM split the tiles left over after the last full persistent round along K.  Launches that
+    share a scratch must not overlap on the GPU (its counters and partial tiles belong to one
+    launch at a time), which stream order guarantees for one stream; every stream gets its own."""
+    index = torch.device(device).index if torch.device(device).index is not None else torch.cuda.current_device()
+    key = (index, stream_ptr or 0)
     ws = _WORKSPACES.get(key)
     if ws is None:
-        ws = torch.zeros(256 + 74 * 256 * 256 * 4, dtype=torch.uint8, device=torch.device("cuda", key))
+        ws = torch.zeros(256 + 74 * 256 * 256 * 4, dtype=torch.uint8, device=torch.device("cuda", index))
         _WORKSPACES[key] = ws
     return ws
 
 
-def _gemm_args(a, b, c, num_sms, block_n, group_m, signal_value, timeout_ns, status) -> L.GemmArgs:
+def _gemm_args(a, b, c, num_sms, block_n, group_m, signal_value, timeout_ns, status, stream=None) -> L.GemmArgs:
     _check_mat("a", a)
     _check_mat("b", b)
     if a.dtype != b.dtype or a.shape[1] != b.shape[1]:
@@ -86,7 +89,7 @@ def _gemm_args(a, b, c, num_sms, block_n, group_m, signal_value, timeout_ns, sta
     g.signal_value = int(signal_value or 1)
     g.timeout_ns = int(timeout_ns or 0)
     g.status = _ptr(status)
-    ws = tail_workspace(a.device)
+    ws = tail_workspace(a.device, _stream_ptr(stream))
     g.workspace, g.workspace_bytes = ws.data_ptr(), ws.numel()
     return g
 
@@ -129,7 +132,7 @@ def gemm(
     """
     if BLOCK_SIZE_M not in (0, 128) or BLOCK_SIZE_K not in (0, 64):
         raise ValueError("this backend uses 128 x N x 64 tiles")
-    g = _gemm_args(a, b, c, num_gemm_sms, BLOCK_SIZE_N, GROUP_SIZE_M, signal_value, timeout_ns, status)
+    g = _gemm_args(a, b, c, num_gemm_sms, BLOCK_SIZE_N, GROUP_SIZE_M, signal_value, timeout_ns, status, stream)
     g.sched_counter = _ptr(sched_counter)  # uint32[2], zero: dynamic tile scheduling
     g.trace = _ptr(trace)                  # uint64[2 + 3 * waves] timer stamps (see the header)
     keep = []
@@ -169,13 +172,15 @@ def ag_gemm(
     group_size_m: int = 8,
     timeout_ns: int = 0,
     status=None,
+    trace=None,
     stream=None,
 ) -> torch.Tensor:
     """All-gather + GEMM.  ``a_local`` ``[M, K]`` is this rank's copy of the gathered buffer (own
     shard in place) and ``a_symm`` its symmetric table; ``schedule`` is the lowered ``RawSchedule``
     of that buffer (or a tuple ``(offsets, shapes, signals, target_ranks, dst_offsets)``)."""
-    g = _gemm_args(a_local, b, c, num_sms, block_n, group_size_m, epoch, timeout_ns, status)
+    g = _gemm_args(a_local, b, c, num_sms, block_n, group_size_m, epoch, timeout_ns, status, stream)
     g.consumer_signal_ptr = _ptr(recv_flags)
+    g.trace = _ptr(trace)
     args = L.AgGemmArgs()
     args.gemm = g
     args.a = a_symm
@@ -206,13 +211,16 @@ def gemm_rs(
     stream=None,
     send_buf: Optional[torch.Tensor] = None,
     send_flags: Optional[torch.Tensor] = None,
+    trace=None,
 ) -> torch.Tensor:
     """GEMM + reduce-scatter.  ``a`` ``[M, K_local]``, ``b`` ``[N, K_local]``; ``out``
     ``[M / world, N]`` receives the fp32 sum over ranks of this rank's row slab.  With ``send_buf``
-    ``[world, M / world, N]`` and ``send_flags`` (int64 ``[world]``) the kernel stores the slabs
-    for other ranks locally and raises the local flag of each; moving them is the caller's job."""
-    g = _gemm_args(a, b, None, num_sms, block_n, group_size_m, epoch, timeout_ns, status)
+    ``[world, M / world, N]`` and ``send_flags`` (int64, one word per wave of ``src_schedule``) the
+    kernel stores the rows for other ranks locally and raises the local flag of each wave; moving
+    them is the caller's job."""
+    g = _gemm_args(a, b, None, num_sms, block_n, group_size_m, epoch, timeout_ns, status, stream)
     _check_mat("out", out)
+    g.trace = _ptr(trace)
     args = L.GemmRsArgs()
     args.gemm = g
     args.stage = stage

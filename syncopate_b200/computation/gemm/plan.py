@@ -44,28 +44,34 @@ def rs_remote_signals(comm_info, rank: int, src_schedule) -> List[int]:
     return out
 
 
-def rs_transport_program(rank: int, world: int, slab_bytes: int, epoch: int, src_schedule, remote_signals,
-                         send_ptr: int, send_flags_ptr: int, stage_ptrs, flag_ptrs):
+def rs_transport_program(rank: int, world: int, slab_rows: int, row_bytes: int, epoch: int, src_schedule,
+                         remote_signals, send_ptr: int, send_flags_ptr: int, stage_ptrs, flag_ptrs):
     """What moves the slabs of a GEMM + reduce-scatter call when the kernel stores them locally
     (``syn_gemm_rs_args.send_buf``): one entry per wave of the partial-C schedule whose target is
     another rank, in wave order,
 
         ``(local flag address, source address, destination address, bytes, remote flag address)``
 
-    The source is slab ``target`` of the local send buffer and its local flag word ``target``; the
-    destination is slot ``(epoch & 1) * world + rank`` of the target's staging buffer (the half
+    A wave is a run of rows of its target's slab (the whole slab, or one piece of it when the plan
+    was cut into smaller chunks).  The source is those rows of slab ``target`` of the local send
+    buffer and the local flag word is the wave's own (index = wave index); the destination is the
+    same rows of slot ``(epoch & 1) * world + rank`` of the target's staging buffer (the half
     alternates with the epoch so that a rank one call ahead does not overwrite what a slower rank
-    still reads) and the remote flag the one the target's owner wave waits for."""
+    still reads) and the remote flag the one the target's reduce wave for these rows waits for."""
     half = (epoch & 1) * world
+    slab_bytes = slab_rows * row_bytes
     prog = []
+    offsets, shapes = src_schedule.gen_block_offset_lists(), src_schedule.gen_block_shape_lists()
     for w, tgt in enumerate(src_schedule.gen_target_rank_list()):
         tgt = rank if tgt is None or tgt < 0 else int(tgt)
         if tgt == rank or remote_signals[w] < 0:
             continue
-        prog.append((send_flags_ptr + 8 * tgt,
-                     send_ptr + tgt * slab_bytes,
-                     stage_ptrs[tgt] + (half + rank) * slab_bytes,
-                     slab_bytes,
+        row_in_slab = offsets[w][0] - tgt * slab_rows
+        inner = row_in_slab * row_bytes
+        prog.append((send_flags_ptr + 8 * w,
+                     send_ptr + tgt * slab_bytes + inner,
+                     stage_ptrs[tgt] + (half + rank) * slab_bytes + inner,
+                     shapes[w][0] * row_bytes,
                      flag_ptrs[tgt] + 8 * int(remote_signals[w])))
     return prog
 

@@ -22,9 +22,6 @@
 // gives registers up (setmaxnreg) so that a softmax thread can hold a whole row of S.
 #pragma once
 #include "attn_sm100.cuh"
-#ifdef SYN_ATTN2_TRACE
-#include <cstdio>
-#endif
 
 namespace syn {
 
@@ -93,24 +90,8 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
   return d;
 }
 
-// Build with -DSYN_ATTN2_TRACE to make CTA 0 print SM-clock stamps of its first hand-overs (a
-// tuning aid; never defined in the shipped library).
-#ifdef SYN_ATTN2_TRACE
-#define ATTN2_STAMP(role, blk, ev)                                                     \
-  do {                                                                                 \
-    if (blockIdx.x == 0 && (blk) < 24u) trace_buf[role][blk][ev] = static_cast<uint32_t>(clock64()); \
-  } while (0)
-#else
-#define ATTN2_STAMP(role, blk, ev) \
-  do {                             \
-  } while (0)
-#endif
-
 template <bool FUSED, bool BF16>
 __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_constant__ AttnParams p) {
-#ifdef SYN_ATTN2_TRACE
-  __shared__ uint32_t trace_buf[4][24][12];
-#endif
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;                                        // tile A, tile B
@@ -182,7 +163,9 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
       uint32_t uq[2] = {0, 0};  // units each tile has taken part in (parity of its Q barriers)
       uint32_t g = 0;           // shared key blocks loaded so far (ring position)
       int flag_wave = -1;
-      while (cur.next(p, z, h, un)) {
+      uint32_t kfills = 0, vfills = 0;  // K / V loads issued (a give-up may fall between the two)
+      bool ok = true;
+      while (ok && cur.next(p, z, h, un)) {
         if (*abort_word != 0) break;
         const AttnWave& w = p.waves[cur.wave];
         const TileRole ta = tile_role(p, w, 2 * un), tb = tile_role(p, w, 2 * un + 1);
@@ -199,14 +182,18 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
               abort_info[0] = cur.wave;
               abort_info[1] = w.sig;
             }
+            break;  // the wave's data never arrived: issue no load for it
           }
           fence_proxy_async();
         }
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
-          if (act[x] == 0) continue;
+          if (act[x] == 0 || !ok) continue;
           const int qt = 2 * un + x;
-          mbar_wait(&q_empty[x], (uq[x] & 1u) ^ 1u, abort_word, p.timeout_ns);
+          if (!mbar_wait(&q_empty[x], (uq[x] & 1u) ^ 1u, abort_word, p.timeout_ns)) {
+            ok = false;
+            continue;
+          }
           mbar_expect_tx(&q_full[x], ATTN_TILE_BYTES);
           tma_load_4d(sQ + x * ATTN_TILE_BYTES, &p.tmap_q, &q_full[x], 0, qt * ATTN_BM, h, z);
           tma_load_4d(sQ + x * ATTN_TILE_BYTES + ATTN_TILE_BYTES / 2, &p.tmap_q, &q_full[x], 64, qt * ATTN_BM, h, z);
@@ -214,19 +201,37 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
         }
         const int hk = h / group;
         int ma, mb;
-        for (int kb = next_shared_block(p, w, ta, tb, w.kb0, ma, mb); kb >= 0;
+        for (int kb = next_shared_block(p, w, ta, tb, w.kb0, ma, mb); ok && kb >= 0;
              kb = next_shared_block(p, w, ta, tb, kb + 1, ma, mb)) {
           const int st = g % ATTN_KV_STAGES;
           const uint32_t par = ((g / ATTN_KV_STAGES) & 1u) ^ 1u;
-          mbar_wait(&k_empty[st], par, abort_word, p.timeout_ns);
+          if (!mbar_wait(&k_empty[st], par, abort_word, p.timeout_ns)) {
+            ok = false;
+            break;
+          }
           mbar_expect_tx(&k_full[st], ATTN_TILE_BYTES);
           tma_load_4d(sK + st * ATTN_TILE_BYTES, &p.tmap_k, &k_full[st], 0, kb * ATTN_BN, hk, z);
           tma_load_4d(sK + st * ATTN_TILE_BYTES + ATTN_TILE_BYTES / 2, &p.tmap_k, &k_full[st], 64, kb * ATTN_BN, hk, z);
-          mbar_wait(&v_empty[st], par, abort_word, p.timeout_ns);
+          ++kfills;
+          if (!mbar_wait(&v_empty[st], par, abort_word, p.timeout_ns)) {
+            ok = false;
+            break;
+          }
           mbar_expect_tx(&v_full[st], ATTN_TILE_BYTES);
           tma_load_4d(sV + st * ATTN_TILE_BYTES, &p.tmap_v, &v_full[st], 0, kb * ATTN_BN, hk, z);
           tma_load_4d(sV + st * ATTN_TILE_BYTES + ATTN_TILE_BYTES / 2, &p.tmap_v, &v_full[st], 64, kb * ATTN_BN, hk, z);
+          ++vfills;
           ++g;
+        }
+      }
+      if (*abort_word != 0) {
+        // loads already issued keep writing this CTA's shared memory: wait for them before leaving
+        for (int x = 0; x < 2; ++x) drain_stage(&q_full[x], uq[x], p.timeout_ns);
+        for (int st = 0; st < ATTN_KV_STAGES; ++st) {
+          drain_stage(&k_full[st], kfills / ATTN_KV_STAGES + (static_cast<uint32_t>(st) < kfills % ATTN_KV_STAGES ? 1u : 0u),
+                      p.timeout_ns);
+          drain_stage(&v_full[st], vfills / ATTN_KV_STAGES + (static_cast<uint32_t>(st) < vfills % ATTN_KV_STAGES ? 1u : 0u),
+                      p.timeout_ns);
         }
       }
     }
@@ -324,31 +329,24 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
           const int st = g % ATTN_KV_STAGES, st_n = (g + 1) % ATTN_KV_STAGES;
           const uint32_t par = (g / ATTN_KV_STAGES) & 1u, par_n = ((g + 1) / ATTN_KV_STAGES) & 1u;
           if (m[x]) {
-            if (lane == 0) ATTN2_STAMP(2 + x, cbx, 0);
             mbar_wait(&p_full[2 * x], cbx & 1u, abort_word, timeout_ns);
-            if (lane == 0) ATTN2_STAMP(2 + x, cbx, 1);
             if (!started) {
               // the first product of a unit overwrites O_x: the previous unit's result must have been read
               mbar_wait(&o_empty[x], (uqx & 1u) ^ 1u, abort_word, timeout_ns);
             }
             mbar_wait(&v_full[st], par, abort_word, timeout_ns);
             tc_fence_after();
-            if (lane == 0) ATTN2_STAMP(2 + x, cbx, 2);
             issue_pv(st, 0, started);
-            if (lane == 0) ATTN2_STAMP(2 + x, cbx, 3);
             // the next K block has long landed; looking now keeps this wait off the path from the
             // second half of P to the next S
             if (kn >= 0) mbar_wait(&k_full[st_n], par_n, abort_word, timeout_ns);
             mbar_wait(&p_full[2 * x + 1], cbx & 1u, abort_word, timeout_ns);
-            if (lane == 0) ATTN2_STAMP(2 + x, cbx, 4);
             tc_fence_after();
             issue_pv(st, 1, true);
-            if (lane == 0) ATTN2_STAMP(2 + x, cbx, 6);
             ++cbx;
             started = true;
             if (kn >= 0 && n[x]) {
               issue_qk(st_n);
-              if (lane == 0) ATTN2_STAMP(2 + x, cbx - 1, 9);
             }
             // both stages are released by one commit each, after everything issued so far
             release(&v_empty[st], true);
@@ -365,7 +363,6 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
               release(&k_empty[st_n], n[x] != 0);
             }
           }
-          if (lane == 0) ATTN2_STAMP(2 + x, cbx - 1, 10);
           kb = kn;
           m[0] = n[0];
           m[1] = n[1];
@@ -423,14 +420,12 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
           lim = min(ATTN_BN - 1, qpos0 + row - kpos0);
         }
         mbar_wait(&s_full[x], cbx & 1u, abort_word, p.timeout_ns);
-        if (threadIdx.x % 128 == 0) ATTN2_STAMP(x, cbx, 0);
         ++cbx;
         tc_fence_after();
         uint32_t sr[ATTN_BN / 32][32];
 #pragma unroll
         for (int c = 0; c < ATTN_BN / 32; ++c) tmem_ld_32x32(s_tmem + c * 32, sr[c]);
         tmem_ld_wait();
-        if (threadIdx.x % 128 == 0) ATTN2_STAMP(x, cbx - 1, 1);
         if (mode == 2) {
 #pragma unroll
           for (int c = 0; c < ATTN_BN / 32; ++c) {
@@ -468,7 +463,6 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
           m = mx;
         }
         const float neg_m = (m == -INFINITY) ? 0.f : -m;
-        if (threadIdx.x % 128 == 0) ATTN2_STAMP(x, cbx - 1, 2);
         // P = 2^(S * scale - m), two elements per instruction where the hardware allows; the two
         // halves of P (keys 0..63, 64..127) are handed over separately, so that the product with
         // the first half of V runs while the second half is still being exponentiated
@@ -505,7 +499,6 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
             tmem_st_wait();
             tc_fence_before();
             mbar_arrive(&p_full[2 * x + (c >> 1)]);
-            if (threadIdx.x % 128 == 0) ATTN2_STAMP(x, cbx - 1, 3 + (c >> 1));
           }
         }
         if (both) {
@@ -534,22 +527,6 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
 
   tc_fence_before();
   __syncthreads();
-#ifdef SYN_ATTN2_TRACE
-  if (blockIdx.x == 0 && threadIdx.x == 0) {
-    const uint32_t t0 = trace_buf[0][8][0];
-    for (int b = 8; b < 16; ++b) {
-      printf("blk %2d A: s_full %u ld %u max %u p0 %u p1 %u | B: s_full %u ld %u max %u p0 %u p1 %u\n", b,
-             trace_buf[0][b][0] - t0, trace_buf[0][b][1] - t0, trace_buf[0][b][2] - t0, trace_buf[0][b][3] - t0,
-             trace_buf[0][b][4] - t0, trace_buf[1][b][0] - t0, trace_buf[1][b][1] - t0, trace_buf[1][b][2] - t0,
-             trace_buf[1][b][3] - t0, trace_buf[1][b][4] - t0);
-      for (int x = 0; x < 2; ++x)
-        printf("   MMA %c: top %u p0 %u fence %u pv0 %u p1 %u pv1 %u qk %u end %u\n", 'A' + x,
-               trace_buf[2 + x][b][0] - t0, trace_buf[2 + x][b][1] - t0, trace_buf[2 + x][b][2] - t0,
-               trace_buf[2 + x][b][3] - t0, trace_buf[2 + x][b][4] - t0, trace_buf[2 + x][b][6] - t0,
-               trace_buf[2 + x][b][9] - t0, trace_buf[2 + x][b][10] - t0);
-    }
-  }
-#endif
   if (warp == 2) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);

@@ -263,6 +263,7 @@ extern "C" int syn_attention(const syn_attn_args* a, const syn_schedule* sched, 
       if (o.src_rank < 0 || o.src_rank >= world || o.dst_rank < 0 || o.dst_rank >= world) return SYN_ERR_INVALID;
       if (o.src_rank != rank && o.dst_rank != rank) return SYN_ERR_INVALID;
       if ((o.src_offset | o.dst_offset | o.src_pitch | o.dst_pitch | o.row_bytes) & 15) return SYN_ERR_INVALID;
+      if (o.reduce != 0) return SYN_ERR_UNSUPPORTED;  // comm warps move bytes; reducing copies belong to syn_copy
       CommOp& c = p.comm[i];
       c.src = static_cast<const char*>(comm->bufs[o.src_buf].ptrs[o.src_rank]) + o.src_offset;
       c.dst = static_cast<char*>(comm->bufs[o.dst_buf].ptrs[o.dst_rank]) + o.dst_offset;

@@ -300,7 +300,10 @@ __global__ void __launch_bounds__(256, 1) attn_kernel(const __grid_constant__ At
       int z, h, qt;
       uint32_t u = 0, g = 0;  // running unit / key-block counters (ring positions)
       int flag_wave = -1;     // last wave whose flag this CTA has waited for
-      while (cur.next(p, z, h, qt)) {
+      uint32_t kfills = 0, vfills = 0;
+      bool ok = true;
+      while (ok && cur.next(p, z, h, qt)) {
+        if (*abort_word != 0) break;
         const AttnWave& w = p.waves[cur.wave];
         const int qpos0 = p.q_pos ? __ldg(p.q_pos + qt) : qt * ATTN_BM;
         int active = 0;
@@ -313,11 +316,12 @@ __global__ void __launch_bounds__(256, 1) attn_kernel(const __grid_constant__ At
               abort_info[0] = cur.wave;
               abort_info[1] = w.sig;
             }
+            break;  // the wave's data never arrived: issue no load for it
           }
           fence_proxy_async();
         }
         const int qb = u & 1;
-        mbar_wait(&q_empty[qb], ((u >> 1) & 1u) ^ 1u, abort_word, p.timeout_ns);
+        if (!mbar_wait(&q_empty[qb], ((u >> 1) & 1u) ^ 1u, abort_word, p.timeout_ns)) break;
         mbar_expect_tx(&q_full[qb], ATTN_TILE_BYTES);
         tma_load_4d(sQ + qb * ATTN_TILE_BYTES, &p.tmap_q, &q_full[qb], 0, qt * ATTN_BM, h, z);
         tma_load_4d(sQ + qb * ATTN_TILE_BYTES + ATTN_TILE_BYTES / 2, &p.tmap_q, &q_full[qb], 64, qt * ATTN_BM, h, z);
@@ -327,15 +331,33 @@ __global__ void __launch_bounds__(256, 1) attn_kernel(const __grid_constant__ At
           if (block_mode(p, qpos0, kb) == 0) continue;
           const int st = g % ATTN_KV_STAGES;
           const uint32_t par = ((g / ATTN_KV_STAGES) & 1u) ^ 1u;
-          mbar_wait(&k_empty[st], par, abort_word, p.timeout_ns);
+          if (!mbar_wait(&k_empty[st], par, abort_word, p.timeout_ns)) {
+            ok = false;
+            break;
+          }
           mbar_expect_tx(&k_full[st], ATTN_TILE_BYTES);
           tma_load_4d(sK + st * ATTN_TILE_BYTES, &p.tmap_k, &k_full[st], 0, kb * ATTN_BN, hk, z);
           tma_load_4d(sK + st * ATTN_TILE_BYTES + ATTN_TILE_BYTES / 2, &p.tmap_k, &k_full[st], 64, kb * ATTN_BN, hk, z);
-          mbar_wait(&v_empty[st], par, abort_word, p.timeout_ns);
+          ++kfills;
+          if (!mbar_wait(&v_empty[st], par, abort_word, p.timeout_ns)) {
+            ok = false;
+            break;
+          }
           mbar_expect_tx(&v_full[st], ATTN_TILE_BYTES);
           tma_load_4d(sV + st * ATTN_TILE_BYTES, &p.tmap_v, &v_full[st], 0, kb * ATTN_BN, hk, z);
           tma_load_4d(sV + st * ATTN_TILE_BYTES + ATTN_TILE_BYTES / 2, &p.tmap_v, &v_full[st], 64, kb * ATTN_BN, hk, z);
+          ++vfills;
           ++g;
+        }
+      }
+      if (*abort_word != 0) {
+        // loads already issued keep writing this CTA's shared memory: wait for them before leaving
+        for (int qb = 0; qb < 2; ++qb) drain_stage(&q_full[qb], u / 2 + (static_cast<uint32_t>(qb) < u % 2 ? 1u : 0u), p.timeout_ns);
+        for (int st = 0; st < ATTN_KV_STAGES; ++st) {
+          drain_stage(&k_full[st], kfills / ATTN_KV_STAGES + (static_cast<uint32_t>(st) < kfills % ATTN_KV_STAGES ? 1u : 0u),
+                      p.timeout_ns);
+          drain_stage(&v_full[st], vfills / ATTN_KV_STAGES + (static_cast<uint32_t>(st) < vfills % ATTN_KV_STAGES ? 1u : 0u),
+                      p.timeout_ns);
         }
       }
     }

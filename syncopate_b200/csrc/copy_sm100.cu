@@ -18,7 +18,24 @@ struct CopyParams {
   uint64_t timeout_ns;
   int32_t* status;
   CommOp ops[COPY_MAX_OPS];
+  int8_t reduce[COPY_MAX_OPS];  // 0 = copy, 1 = dst += src as fp16, 2 = as bf16
 };
+
+// dst += v for eight 16-bit elements, as one vector reduction performed at the memory that owns
+// `dst` (this GPU's or a peer's): concurrent reducing copies from several ranks into the same bytes
+// do not lose updates.  Each addition rounds to the element type, as the reference's TMA reduce-add
+// does (syncopate/communication/comm_runtime/tma_persistent_copy.py:129-169).
+__device__ __forceinline__ void red_add16(void* dst, uint4 v, int kind) {
+  if (kind == 2) {
+    asm volatile("red.relaxed.sys.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};"
+                 ::"l"(dst), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+  } else {
+    asm volatile("red.relaxed.sys.global.add.noftz.v4.f16x2 [%0], {%1, %2, %3, %4};"
+                 ::"l"(dst), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+  }
+}
 
 __global__ void __launch_bounds__(COPY_THREADS) copy_kernel(const __grid_constant__ CopyParams p) {
   __shared__ int abort_word;
@@ -50,7 +67,11 @@ __global__ void __launch_bounds__(COPY_THREADS) copy_kernel(const __grid_constan
         const size_t j = i + u * nthreads;
         if (j < total) {
           const size_t r = j / cpr, c = j - r * cpr;
-          *reinterpret_cast<uint4*>(op.dst + r * op.dst_pitch + c * 16) = v[u];
+          if (p.reduce[o] != 0) {
+            red_add16(op.dst + r * op.dst_pitch + c * 16, v[u], p.reduce[o]);
+          } else {
+            *reinterpret_cast<uint4*>(op.dst + r * op.dst_pitch + c * 16) = v[u];
+          }
         }
       }
     }
@@ -105,6 +126,10 @@ extern "C" int syn_copy(const syn_attn_comm* comm, int num_sms, uint64_t signal_
     c.dst_pitch = o.dst_pitch;
     c.rows = o.rows;
     c.row_bytes = o.row_bytes;
+    if (o.reduce != 0) {
+      if (o.reduce != 1 || (o.dtype != SYN_DTYPE_F16 && o.dtype != SYN_DTYPE_BF16)) return SYN_ERR_UNSUPPORTED;
+      p.reduce[i] = static_cast<int8_t>(o.dtype == SYN_DTYPE_BF16 ? 2 : 1);
+    }
     if (o.flag >= 0) {
       if (o.flag_rank < 0 || o.flag_rank >= world || comm->flags.ptrs[o.flag_rank] == nullptr) return SYN_ERR_INVALID;
       c.set_flag = static_cast<uint64_t*>(comm->flags.ptrs[o.flag_rank]) + o.flag;

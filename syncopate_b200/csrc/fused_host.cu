@@ -19,17 +19,6 @@ static bool dynamic_sched() {
   return cached == 1;
 }
 
-// SYNCOPATE_B200_RS_WIDE=1 sends 128-column (256-byte segment) store boxes in GEMM + reduce-scatter
-// instead of the 64-column swizzled ones; measured no faster at 8 GPUs, so it is off by default.
-static bool rs_wide_store() {
-  static int cached = -1;
-  if (cached < 0) {
-    const char* e = getenv("SYNCOPATE_B200_RS_WIDE");
-    cached = (e != nullptr && e[0] == '1') ? 1 : 0;
-  }
-  return cached == 1;
-}
-
 static int check_symm(const syn_symm& s) {
   if (s.world <= 0 || s.world > SYN_MAX_WORLD || s.rank < 0 || s.rank >= s.world) return SYN_ERR_INVALID;
   for (int r = 0; r < s.world; ++r)
@@ -72,7 +61,8 @@ int syn_ag_gemm(const syn_ag_gemm_args* args, const syn_schedule* a_sched, void*
   c_sched.shapes = c_shape.data();
 
   int grid = 0, bn = 0;
-  rc = gemm_resolve_grid_and_bn(&g, &c_sched, &grid, &bn);
+  bool want_pair = false;
+  rc = gemm_resolve_grid_and_bn(&g, &c_sched, &grid, &bn, 32, &want_pair);
   if (rc != SYN_OK) return rc;
   GemmParams p;
   rc = gemm_fill_common(&p, &g, &c_sched, bn);
@@ -117,6 +107,9 @@ int syn_ag_gemm(const syn_ag_gemm_args* args, const syn_schedule* a_sched, void*
   }
   p.num_comm_ops = n_ops;
   p.counters = args->counters;
+  // the CTA-pair kernel where the waves allow it (256-row boundaries); it hands tiles out round-robin
+  if (want_pair && pair_eligible(p, bn, grid))
+    return gemm_launch_pair(p, &g, bn, grid, /*fused=*/n_ops > 0, static_cast<cudaStream_t>(stream));
   if (args->counters != nullptr && dynamic_sched()) p.sched = args->counters + SYN_MAX_WAVES + SYN_MAX_COMM_OPS;
   grid = std::min(grid, p.total_tiles);
   if (grid <= 0) return SYN_ERR_INVALID;
@@ -137,7 +130,13 @@ int syn_gemm_rs(const syn_gemm_rs_args* args, const syn_schedule* src_sched, con
   if (args->out == nullptr || args->counters == nullptr) return SYN_ERR_INVALID;
   if (args->send_buf != nullptr && (args->send_flags == nullptr || (reinterpret_cast<uintptr_t>(args->send_buf) & 15)))
     return SYN_ERR_INVALID;
-  if (src_sched->ndim != 2 || src_sched->target_ranks == nullptr) return SYN_ERR_INVALID;
+  if (src_sched->ndim != 2 || src_sched->target_ranks == nullptr || src_sched->num_waves <= 0) return SYN_ERR_INVALID;
+  if (src_sched->offsets == nullptr || src_sched->shapes == nullptr) return SYN_ERR_INVALID;
+  // the receive buffer is [M / world, N] (direct reduce) or [world, M / world, N] (one slab per sender):
+  // rows and columns are its last two axes
+  const int dnd = dst_sched->ndim;
+  if ((dnd != 2 && dnd != 3) || dst_sched->num_waves <= 0 || dst_sched->offsets == nullptr || dst_sched->shapes == nullptr)
+    return SYN_ERR_INVALID;
   if (g.M % world != 0) return SYN_ERR_SHAPE;
   const int slab_rows = g.M / world;
   const int ldo = args->ldo ? args->ldo : g.N;
@@ -146,90 +145,171 @@ int syn_gemm_rs(const syn_gemm_rs_args* args, const syn_schedule* src_sched, con
   if (g.c == nullptr) g.c = args->out;
   g.consumer_signal_ptr = nullptr;
 
+  // ---- what arrives here: pieces of this rank's slab staged by the other ranks, one flag each.
+  // Pieces are grouped by the rows they cover; a group that every other rank contributes to
+  // becomes one reduce wave that waits for exactly its own flags.
+  struct Group {
+    int off, rows;
+    int sig[SYN_MAX_WORLD];
+  };
+  std::vector<Group> groups;
+  int src_index[SYN_MAX_WORLD];  // source rank -> position among the staged slabs
+  int n_red = 0;
+  for (int r = 0; r < SYN_MAX_WORLD; ++r) src_index[r] = -1;
+  for (int w = 0; w < dst_sched->num_waves; ++w) {
+    const int src_rank = dst_sched->target_ranks ? dst_sched->target_ranks[w] : -1;
+    const int sig = dst_sched->signals ? dst_sched->signals[w] : -1;
+    if (src_rank < 0 || src_rank == rank) continue;
+    if (src_rank >= world || sig < 0 || sig > 32767) return SYN_ERR_SHAPE;
+    if (dst_sched->offsets[w * dnd + dnd - 1] != 0 || dst_sched->shapes[w * dnd + dnd - 1] != g.N) return SYN_ERR_SHAPE;
+    if (src_index[src_rank] < 0) {
+      if (n_red >= GEMM_MAX_RED) return SYN_ERR_SHAPE;
+      src_index[src_rank] = n_red++;
+    }
+    const int off = dst_sched->offsets[w * dnd + dnd - 2], rows = dst_sched->shapes[w * dnd + dnd - 2];
+    Group* grp = nullptr;
+    for (auto& x : groups)
+      if (x.off == off && x.rows == rows) grp = &x;
+    if (grp == nullptr) {
+      Group fresh;
+      fresh.off = off;
+      fresh.rows = rows;
+      for (int r = 0; r < SYN_MAX_WORLD; ++r) fresh.sig[r] = -1;
+      groups.push_back(fresh);
+      grp = &groups.back();
+    }
+    if (grp->sig[src_index[src_rank]] >= 0) return SYN_ERR_SHAPE;  // the same rows twice from one rank
+    grp->sig[src_index[src_rank]] = sig;
+  }
+  if (n_red != world - 1) return SYN_ERR_SHAPE;
+  std::sort(groups.begin(), groups.end(), [](const Group& x, const Group& y) { return x.off < y.off; });
+  int covered = 0;
+  for (const auto& x : groups) {
+    if (x.off != covered || x.rows <= 0 || (x.off % GEMM_BM) != 0) return SYN_ERR_SHAPE;
+    for (int i = 0; i < n_red; ++i)
+      if (x.sig[i] < 0) return SYN_ERR_SHAPE;  // every other rank contributes to every group
+    covered += x.rows;
+  }
+  if (covered != slab_rows) return SYN_ERR_SHAPE;
+
+  // ---- the waves the kernel walks: those of `src_sched`, with the wave kept here cut into the groups
+  struct Piece {
+    int r0, rows, orig, group;  // group >= 0: reduce wave
+  };
+  std::vector<Piece> pieces;
+  for (int w = 0; w < src_sched->num_waves; ++w) {
+    const int r0 = src_sched->offsets[w * 2], rows = src_sched->shapes[w * 2];
+    if (src_sched->offsets[w * 2 + 1] != 0 || src_sched->shapes[w * 2 + 1] != g.N) return SYN_ERR_SHAPE;
+    if (r0 < 0 || rows <= 0 || r0 + rows > g.M) return SYN_ERR_SHAPE;
+    const int owner = r0 / slab_rows;  // rank whose output the rows belong to
+    if ((r0 + rows - 1) / slab_rows != owner) return SYN_ERR_SHAPE;
+    int tgt = src_sched->target_ranks[w];
+    if (tgt < 0) tgt = rank;
+    if (tgt != owner) return SYN_ERR_SHAPE;
+    if (tgt != rank) {
+      pieces.push_back({r0, rows, w, -1});
+      continue;
+    }
+    const int lo = r0 - rank * slab_rows, hi = lo + rows;
+    for (size_t gi = 0; gi < groups.size(); ++gi) {
+      const int a = std::max(lo, groups[gi].off), b = std::min(hi, groups[gi].off + groups[gi].rows);
+      if (a >= b) continue;
+      if (a != groups[gi].off || b != groups[gi].off + groups[gi].rows) return SYN_ERR_SHAPE;  // partial overlap
+      pieces.push_back({rank * slab_rows + a, b - a, w, static_cast<int>(gi)});
+    }
+  }
+  const int nw = static_cast<int>(pieces.size());
+  if (nw > GEMM_MAX_WAVES) return SYN_ERR_TOO_LARGE;
+  std::vector<int32_t> k_off(nw * 2), k_shape(nw * 2), k_sig(nw, -1);
+  for (int w = 0; w < nw; ++w) {
+    k_off[w * 2] = pieces[w].r0;
+    k_off[w * 2 + 1] = 0;
+    k_shape[w * 2] = pieces[w].rows;
+    k_shape[w * 2 + 1] = g.N;
+  }
+  syn_schedule k_sched;
+  memset(&k_sched, 0, sizeof(k_sched));
+  k_sched.num_waves = nw;
+  k_sched.ndim = 2;
+  k_sched.offsets = k_off.data();
+  k_sched.shapes = k_shape.data();
+  k_sched.signals = k_sig.data();
+
   int grid = 0, bn = 0;
-  rc = gemm_resolve_grid_and_bn(&g, src_sched, &grid, &bn, /*multiple=*/64);
+  bool want_pair = false;
+  rc = gemm_resolve_grid_and_bn(&g, &k_sched, &grid, &bn, /*multiple=*/64, &want_pair);
   if (rc != SYN_OK) return rc;
   GemmParams p;
-  rc = gemm_fill_common(&p, &g, src_sched, bn);
+  rc = gemm_fill_common(&p, &g, &k_sched, bn);
   if (rc != SYN_OK) return rc;
   const uint64_t epoch = p.signal_value;
-  const bool wide = rs_wide_store() && bn % 128 == 0;
-  p.wide_store = wide ? 1 : 0;
   int tmap_of_rank[SYN_MAX_WORLD];
   for (int r = 0; r < SYN_MAX_WORLD; ++r) tmap_of_rank[r] = -1;
   int n_maps = 0;
   const size_t slab_elems = static_cast<size_t>(slab_rows) * g.N;
   const size_t half = static_cast<size_t>(epoch & 1) * world;
 
-  for (int w = 0; w < src_sched->num_waves; ++w) {
-    const int r0 = src_sched->offsets[w * 2], rows = src_sched->shapes[w * 2];
-    if (src_sched->offsets[w * 2 + 1] != 0 || src_sched->shapes[w * 2 + 1] != g.N) return SYN_ERR_SHAPE;
-    const int owner = r0 / slab_rows;  // rank whose output the rows belong to
-    if ((r0 + rows - 1) / slab_rows != owner) return SYN_ERR_SHAPE;
-    int tgt = src_sched->target_ranks[w];
-    if (tgt < 0) tgt = rank;
-    if (tgt != owner) return SYN_ERR_SHAPE;
+  for (int w = 0; w < nw; ++w) {
+    const Piece& pc = pieces[w];
+    const int tgt = pc.r0 / slab_rows;
     GemmRoute& rt = p.routes[w];
     p.waves[w].route = static_cast<int16_t>(w);
     rt.gate = nullptr;
     rt.gate_value = 0;
-    const int row_in_slab = r0 - owner * slab_rows;
+    const int row_in_slab = pc.r0 - tgt * slab_rows;
     char* slab0;  // row 0 of the destination slab
     int slab_ld;
+    bool local = true;
     if (tgt == rank) {
       slab0 = static_cast<char*>(args->out);
       slab_ld = ldo;
       rt.flag = nullptr;
       rt.reduce = 1;
+      for (int i = 0; i < n_red; ++i) rt.red_sig[i] = static_cast<int16_t>(groups[pc.group].sig[i]);
     } else if (args->send_buf != nullptr) {
-      // transport by the caller: local send slab, local flag
+      // transport by the caller: local send slab, local flag per wave
       slab0 = static_cast<char*>(args->send_buf) + static_cast<size_t>(tgt) * slab_elems * 2;
       slab_ld = g.N;
-      rt.flag = args->send_flags + tgt;
+      rt.flag = args->send_flags + pc.orig;
       rt.reduce = 0;
     } else {
       slab0 = static_cast<char*>(args->stage.ptrs[tgt]) + (half + rank) * slab_elems * 2;
       slab_ld = g.N;
-      const int rsig = args->remote_signals ? args->remote_signals[w] : -1;
+      const int rsig = args->remote_signals ? args->remote_signals[pc.orig] : -1;
       rt.flag = rsig >= 0 ? static_cast<uint64_t*>(args->recv_flags.ptrs[tgt]) + rsig : nullptr;
       rt.reduce = 0;
+      local = false;
     }
     rt.base = slab0 + static_cast<size_t>(row_in_slab) * slab_ld * 2;
     rt.ld = slab_ld;
-    // tiles leave through shared memory and TMA stores: one output map per destination slab
-    if (tmap_of_rank[tgt] < 0) {
-      rc = wide ? encode_tmap_2d_plain(&p.tmap_out[n_maps], slab0, slab_rows, g.N, slab_ld, 64, 128)
-                : encode_tmap_2d_sw128(&p.tmap_out[n_maps], slab0, slab_rows, g.N, slab_ld, GEMM_BM, 64);
-      if (rc != SYN_OK) return rc;
-      tmap_of_rank[tgt] = n_maps++;
-    }
-    rt.tmap = static_cast<int16_t>(tmap_of_rank[tgt]);
+    rt.tmap = -1;
     rt.tmap_row0 = row_in_slab;
+    if (!local) {
+      // tiles for a peer leave through shared memory and TMA stores (full 128-byte lines): one
+      // output map per destination slab, boxes of one epilogue warp's 32 rows x 64 columns
+      if (tmap_of_rank[tgt] < 0) {
+        rc = encode_tmap_2d_sw128(&p.tmap_out[n_maps], slab0, slab_rows, g.N, slab_ld, 32, 64);
+        if (rc != SYN_OK) return rc;
+        tmap_of_rank[tgt] = n_maps++;
+      }
+      rt.tmap = static_cast<int16_t>(tmap_of_rank[tgt]);
+    }
   }
-  // staged partial sums to add in the owner wave, with the local flags that publish them
-  int n_red = 0;
-  for (int w = 0; w < dst_sched->num_waves; ++w) {
-    const int src_rank = dst_sched->target_ranks ? dst_sched->target_ranks[w] : -1;
-    const int sig = dst_sched->signals ? dst_sched->signals[w] : -1;
-    if (src_rank < 0 || src_rank == rank) continue;
-    if (src_rank >= world || sig < 0 || n_red >= 7) return SYN_ERR_SHAPE;
-    bool seen = false;
-    for (int i = 0; i < n_red; ++i)
-      if (p.red_flag[i] == static_cast<const uint64_t*>(args->recv_flags.ptrs[rank]) + sig) seen = true;
-    if (seen) continue;
-    p.red_src[n_red] = static_cast<const char*>(args->stage.ptrs[rank]) + (half + src_rank) * slab_elems * 2;
-    p.red_flag[n_red] = static_cast<const uint64_t*>(args->recv_flags.ptrs[rank]) + sig;
-    ++n_red;
-  }
-  if (n_red != world - 1) return SYN_ERR_SHAPE;
+  // staged partial sums, in the order of `src_index`, and the flag array the reduce waves index
+  for (int r = 0; r < world; ++r)
+    if (src_index[r] >= 0)
+      p.red_src[src_index[r]] = static_cast<const char*>(args->stage.ptrs[rank]) + (half + r) * slab_elems * 2;
+  p.red_flags = static_cast<const uint64_t*>(args->recv_flags.ptrs[rank]);
   p.num_red = n_red;
   p.red_ld = g.N;
   p.red_row0 = rank * slab_rows;
   p.counters = args->counters;
-  if (dynamic_sched()) p.sched = args->counters + SYN_MAX_WAVES + SYN_MAX_COMM_OPS;
   p.c = args->out;
   p.ldc = ldo;
   p.raise_flags_on_abort = args->send_buf != nullptr ? 1 : 0;
+  if (want_pair && pair_eligible(p, bn, grid))
+    return gemm_launch_pair(p, &g, bn, grid, /*fused=*/true, static_cast<cudaStream_t>(stream));
+  if (dynamic_sched()) p.sched = args->counters + SYN_MAX_WAVES + SYN_MAX_COMM_OPS;
   grid = std::min(grid, p.total_tiles);
   if (grid <= 0) return SYN_ERR_INVALID;
   return gemm_launch(p, bn, /*fused=*/true, grid, static_cast<cudaStream_t>(stream));

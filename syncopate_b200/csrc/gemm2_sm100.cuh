@@ -4,9 +4,10 @@
 // operand reads of the tensor cores no longer compete with a full B tile per CTA.
 //
 // Same schedule semantics as gemm_kernel (waves in order, consumer flags, grouped raster inside a
-// wave, here over 256-row tiles).  Plain local stores only: the routed epilogue and the comm warp
-// stay with the one-CTA kernel.  No TMA load carries a multicast qualifier; only tcgen05.commit
-// signals both CTAs' barriers.
+// wave, here over 256-row tiles).  With FUSED the kernel also has the comm warp (one per CTA) and
+// the routed epilogue of gemm_kernel: each CTA of a pair routes, counts and reduces its own 128
+// rows of the tile.  No TMA load carries a multicast qualifier; only tcgen05.commit signals both
+// CTAs' barriers.
 #pragma once
 #include "gemm_sm100.cuh"
 
@@ -142,7 +143,7 @@ struct PairCursor {
   }
 };
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool FUSED>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm2_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUtensorMap tmap_b_half,
              const int total_pair_tiles, const PairTail tail) {
@@ -153,12 +154,14 @@ gemm2_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUten
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sA = smem;
   uint8_t* sB = smem + STAGES * A_BYTES;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint8_t* ring = smem + STAGES * STAGE_BYTES;  // FUSED only: comm ring / epilogue staging
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ring + (FUSED ? COMM_NBUF * COMM_PIECE : 0));
   uint64_t* full_bar = bars;                    // leader's copy counts both CTAs' bytes
   uint64_t* empty_bar = bars + STAGES;          // signalled in both CTAs by the leader's commits
   uint64_t* tfull_bar = bars + 2 * STAGES;      // [2], signalled in both CTAs
   uint64_t* tempty_bar = bars + 2 * STAGES + 2; // [2], leader's copy collects both CTAs' epilogue warps
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+  uint64_t* comm_bar = bars + 2 * STAGES + 4;   // [COMM_NBUF]
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(comm_bar + COMM_NBUF);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_holder + 1);
   int* abort_info = const_cast<int*>(abort_word) + 1;
 
@@ -178,6 +181,7 @@ gemm2_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUten
       mbar_init(&tfull_bar[i], 1);
       mbar_init(&tempty_bar[i], 8);  // four epilogue warps of each CTA
     }
+    for (int i = 0; i < COMM_NBUF; ++i) mbar_init(&comm_bar[i], 1);
     *abort_word = 0;
     abort_info[0] = -1;
     abort_info[1] = -1;
@@ -196,6 +200,7 @@ gemm2_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUten
   cluster_sync_all();  // the peer's barriers exist before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  if (p.trace != nullptr && threadIdx.x == 0) atomicMin(&p.trace[0], globaltimer_ns());
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer (both CTAs)
@@ -203,37 +208,57 @@ gemm2_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUten
       PairCursor cur;
       int stage = 0;
       uint32_t phase = 0;
+      uint32_t issued = 0;
       bool first = true;
+      bool gave_up = false;
       PairWork wk;
-      for (int n = 0; pair_work(p, tail, total_pair_tiles, pair_id, num_pairs, n, wk); ++n) {
+      for (int n = 0; !gave_up && pair_work(p, tail, total_pair_tiles, pair_id, num_pairs, n, wk); ++n) {
         int m2_blk, n_blk;
         const bool moved = cur.seek(p, wk.tile, m2_blk, n_blk);
         if (moved || first) {
           const int sig = p.waves[cur.wave].csig;
           if (sig >= 0 && p.csig != nullptr) {
+            const unsigned long long t_wait0 = p.trace != nullptr ? globaltimer_ns() : 0ull;
             if (!flag_wait_ge(p.csig + sig, p.signal_value, abort_word, p.timeout_ns)) {
               if (abort_info[0] < 0) {
                 abort_info[0] = cur.wave;
                 abort_info[1] = sig;
               }
+              gave_up = true;  // the wave's data never arrived: issue no load for it
             }
             fence_proxy_async();
+            if (p.trace != nullptr) {
+              const unsigned long long t_wait1 = globaltimer_ns();
+              atomicMin(&p.trace[2 + 3 * cur.wave], t_wait0);
+              atomicMax(&p.trace[3 + 3 * cur.wave], t_wait1);
+              atomicAdd(&p.trace[4 + 3 * cur.wave], t_wait1 - t_wait0);
+            }
           }
           first = false;
         }
         const int row0 = m2_blk * GEMM2_BM + static_cast<int>(cta_rank) * GEMM_BM;
         const int col0 = n_blk * BN + static_cast<int>(cta_rank) * (BN / 2);
-        for (int kb = wk.kb0; kb < wk.kb1; ++kb) {
-          mbar_wait(&empty_bar[stage], phase ^ 1u, abort_word, p.timeout_ns);
+        for (int kb = wk.kb0; kb < wk.kb1 && !gave_up; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_word, p.timeout_ns)) {
+            gave_up = true;
+            break;
+          }
           if (leader) mbar_expect_tx(&full_bar[stage], 2 * STAGE_BYTES);
           const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
           tma_load_2d_pair(sA + stage * A_BYTES, &p.tmap_a, bar, kb * GEMM_BK, row0);
           tma_load_2d_pair(sB + stage * B_BYTES, &tmap_b_half, bar, kb * GEMM_BK, col0);
+          ++issued;
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
           }
         }
+      }
+      if (*abort_word != 0 && leader) {
+        // Loads already issued keep writing shared memory.  The leader's full barriers count both
+        // CTAs' bytes, and the cluster barrier at the end keeps the other CTA alive meanwhile.
+        for (int s = 0; s < STAGES; ++s)
+          drain_stage(&full_bar[s], issued / STAGES + (static_cast<uint32_t>(s) < issued % STAGES ? 1u : 0u), p.timeout_ns);
       }
     }
   } else if (warp == 1) {
@@ -278,19 +303,95 @@ gemm2_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUten
         if (acc == 0) acc_phase ^= 1u;
       }
     }
+  } else if (warp == 3) {
+    // ------------------------------------------------------------ comm warp (both CTAs)
+    if constexpr (FUSED) {
+      comm_warp_run(p.comm, p.num_comm_ops, p.counters + p.num_waves, p.signal_value,
+                    reinterpret_cast<char*>(ring), comm_bar, abort_word, p.timeout_ns, lane);
+    }
   } else if (warp >= 4) {
     // ------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
+    // The four warps walk the same static list of work items to its end (no early exit), so the
+    // named barriers they meet at always see all of them.
     const int q = warp & 3;
     PairCursor cur;
     int acc = 0;
     uint32_t acc_phase = 0;
+    bool first = true;
+    int done_wave = -1;
+    uint32_t done_tiles = 0;  // 128-row pieces of this CTA finished in `done_wave`
+    uint8_t* wstage = ring + q * (2 * EPI_STAGE_BYTES);
+    uint32_t nstore = 0;  // TMA stores this warp has issued
+    auto flush_wave = [&]() {
+      if constexpr (FUSED) {
+        if (done_wave >= 0 && done_tiles > 0) {
+          const GemmWave& dw = p.waves[done_wave];
+          if (lane == 0) {
+            bulk_wait<0>();
+            fence_proxy_async();
+          }
+          __threadfence_system();
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (warp == 4 && lane == 0) {
+            // the wave's total in 128-row pieces: every CTA of every pair counts its own
+            const uint32_t tiles_w = static_cast<uint32_t>(dw.tiles_m) * static_cast<uint32_t>(dw.tiles_n);
+            __threadfence_system();
+            const uint32_t old = atomicAdd(&p.counters[done_wave], done_tiles);
+            if (old + done_tiles == tiles_w) {
+              p.counters[done_wave] = 0;
+              __threadfence_system();
+              st_release_sys_u64(p.routes[dw.route].flag, p.signal_value);
+            }
+          }
+        }
+      }
+      done_wave = -1;
+      done_tiles = 0;
+    };
     PairWork wk;
     for (int n = 0; pair_work(p, tail, total_pair_tiles, pair_id, num_pairs, n, wk); ++n) {
       int m2_blk, n_blk;
-      cur.seek(p, wk.tile, m2_blk, n_blk);
+      const bool moved = cur.seek(p, wk.tile, m2_blk, n_blk);
+      const GemmWave& wv = p.waves[cur.wave];
+      if (done_wave >= 0 && done_wave != cur.wave) flush_wave();
+      const int row_base = m2_blk * GEMM2_BM + static_cast<int>(cta_rank) * GEMM_BM + q * 32;
+      const int grow = row_base + lane;
+      char* out_base = reinterpret_cast<char*>(p.c);
+      int out_ld = p.ldc;
+      int out_row = grow;
+      bool reduce = false;
+      int tmap_idx = -1, tmap_y = 0;
+      if constexpr (FUSED) {
+        if (wv.route >= 0) {
+          const GemmRoute& rt = p.routes[wv.route];
+          out_base = reinterpret_cast<char*>(rt.base);
+          out_ld = rt.ld;
+          out_row -= wv.off_m * GEMM_BM;
+          reduce = rt.reduce != 0;
+          if (rt.tmap >= 0) {
+            tmap_idx = rt.tmap;
+            tmap_y = rt.tmap_row0 + row_base - wv.off_m * GEMM_BM;
+          }
+          if (moved || first) {
+            if (rt.gate != nullptr) {
+              if (lane == 0) flag_wait_ge(rt.gate, rt.gate_value, abort_word, p.timeout_ns);
+              __syncwarp();
+            }
+            if (reduce) {
+              if (lane < p.num_red) {
+                if (!flag_wait_ge(p.red_flags + rt.red_sig[lane], p.signal_value, abort_word, p.timeout_ns)) {
+                  abort_info[0] = cur.wave;
+                  abort_info[1] = -2 - lane;
+                }
+              }
+              __syncwarp();
+            }
+          }
+        }
+      }
+      first = false;
       mbar_wait(&tfull_bar[acc], acc_phase, abort_word, p.timeout_ns);
       tc_fence_after();
-      const int grow = m2_blk * GEMM2_BM + static_cast<int>(cta_rank) * GEMM_BM + q * 32 + lane;
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * ACC_STRIDE);
       const int col0 = n_blk * BN;
       const bool row_ok = grow < p.M;
@@ -310,18 +411,25 @@ gemm2_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUten
           for (int v = 0; v < 8; ++v)
             __stcg(w + v, make_float4(__uint_as_float(r[v * 4 + 0]), __uint_as_float(r[v * 4 + 1]),
                                       __uint_as_float(r[v * 4 + 2]), __uint_as_float(r[v * 4 + 3])));
-        } else if (row_ok) {
-          uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.c) + (static_cast<size_t>(grow) * p.ldc + col) * 2);
+          continue;
+        }
+        if constexpr (FUSED) {
+          if (reduce && row_ok) epi_add_staged(p, r, grow, col);
+        }
+        uint4 packed[4];
+        epi_pack(r, packed, p.dtype);
+        bool staged = false;
+        if constexpr (FUSED) {
+          if (tmap_idx >= 0) {
+            staged = true;
+            epi_stage_chunk(wstage, c, lane, packed, &p.tmap_out[tmap_idx], col0, tmap_y, nstore);
+          }
+        }
+        if (!staged && row_ok) {
+          uint4* dst = reinterpret_cast<uint4*>(out_base + (static_cast<size_t>(out_row) * out_ld + col) * 2);
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
-            if (col + v * 8 < p.N) {
-              uint4 u;
-              u.x = pack2(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]), p.dtype);
-              u.y = pack2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]), p.dtype);
-              u.z = pack2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]), p.dtype);
-              u.w = pack2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]), p.dtype);
-              dst[v] = u;
-            }
+            if (col + v * 8 < p.N) dst[v] = packed[v];
           }
         }
       }
@@ -330,6 +438,12 @@ gemm2_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUten
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[acc]), 0));
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
+      if constexpr (FUSED) {
+        if (wv.route >= 0 && p.routes[wv.route].flag != nullptr) {
+          done_wave = cur.wave;
+          ++done_tiles;
+        }
+      }
       if (wk.is_slice) {
         // arrive; wait (bounded) for the tile's other slices; reduce this CTA's share of the rows
         const int tl = wk.tile - tail.first_tile;
@@ -364,17 +478,18 @@ gemm2_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUten
             acc8[0] += x.x; acc8[1] += x.y; acc8[2] += x.z; acc8[3] += x.w;
             acc8[4] += y.x; acc8[5] += y.y; acc8[6] += y.z; acc8[7] += y.w;
           }
-          const int out_row = m2_blk * GEMM2_BM + rr, col = col0 + cc * 8;
-          if (out_row < p.M && col < p.N) {
+          const int out_r = m2_blk * GEMM2_BM + rr, col = col0 + cc * 8;
+          if (out_r < p.M && col < p.N) {
             uint4 u;
             u.x = pack2(acc8[0], acc8[1], p.dtype);
             u.y = pack2(acc8[2], acc8[3], p.dtype);
             u.z = pack2(acc8[4], acc8[5], p.dtype);
             u.w = pack2(acc8[6], acc8[7], p.dtype);
-            *reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.c) + (static_cast<size_t>(out_row) * p.ldc + col) * 2) = u;
+            *reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.c) + (static_cast<size_t>(out_r) * p.ldc + col) * 2) = u;
           }
         }
-        // the last CTA to finish reading rewinds the tile's counters for the next launch
+        // the last CTA to finish reading rewinds the tile's counters for the next launch (every
+        // CTA of a slice arrives and departs exactly once on every path, so they always rewind)
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (warp == 4 && lane == 0) {
           const unsigned int old = atomicAdd(&tail.count[2 * tl + 1], 1u);
@@ -385,6 +500,10 @@ gemm2_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUten
         }
       }
     }
+    flush_wave();
+    if constexpr (FUSED) {
+      if (lane == 0) bulk_wait<0>();
+    }
   }
 
   tc_fence_before();
@@ -394,11 +513,20 @@ gemm2_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUten
     tc_fence_after();
     tmem_dealloc_pair(tmem_base, TMEM_COLS);
   }
+  if (p.trace != nullptr && threadIdx.x == 0) atomicMax(&p.trace[1], globaltimer_ns());
   if (threadIdx.x == 0 && *abort_word != 0 && p.status != nullptr) {
     if (atomicCAS(p.status, 0, *abort_word) == 0) {
       p.status[1] = abort_info[0];
       p.status[2] = abort_info[1];
       p.status[3] = static_cast<int>(blockIdx.x);
+    }
+  }
+  if constexpr (FUSED) {
+    if (threadIdx.x == 0 && *abort_word != 0 && p.raise_flags_on_abort) {
+      for (int w = 0; w < p.num_waves; ++w) {
+        const int r = p.waves[w].route;
+        if (r >= 0 && p.routes[r].flag != nullptr) st_release_sys_u64(p.routes[r].flag, p.signal_value);
+      }
     }
   }
 }

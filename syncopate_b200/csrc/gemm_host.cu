@@ -176,7 +176,7 @@ template <int BN, bool FUSED>
 static int launch_bn(const GemmParams& p, int grid, cudaStream_t stream) {
   using L = GemmSmem<BN>;
   constexpr int kMaxSmem = 232448;
-  constexpr int kFixed = 1024 /*alignment slack*/ + (FUSED ? COMM_NBUF * COMM_PIECE : 0) + 256 /*barriers*/;
+  constexpr int kFixed = 1024 /*alignment slack*/ + (FUSED ? COMM_NBUF * COMM_PIECE : 0) + 512 /*barriers, queues*/;
   constexpr int kStagesRaw = (kMaxSmem - kFixed) / L::STAGE_BYTES;
   constexpr int STAGES = kStagesRaw > 6 ? 6 : kStagesRaw;
   static_assert(STAGES >= 3, "shared-memory ring too shallow");
@@ -196,14 +196,16 @@ static int launch_bn(const GemmParams& p, int grid, cudaStream_t stream) {
   return SYN_OK;
 }
 
-template <int BN>
+template <int BN, bool FUSED>
 static int launch_pair_bn(const GemmParams& p, const CUtensorMap& tmap_b_half, int pair_tiles, int grid,
                           const PairTail& tail, cudaStream_t stream) {
   constexpr int kStage = GEMM_BM * GEMM_BK * 2 + (BN / 2) * GEMM_BK * 2;
-  constexpr int kStagesRaw = (232448 - 1024 - 512) / kStage;
+  constexpr int kFixed = 1024 + 512 + (FUSED ? COMM_NBUF * COMM_PIECE : 0);
+  constexpr int kStagesRaw = (232448 - kFixed) / kStage;
   constexpr int STAGES = kStagesRaw > 8 ? 8 : kStagesRaw;
-  constexpr int smem = STAGES * kStage + 1024 + 512;
-  auto kern = gemm2_kernel<BN, STAGES>;
+  static_assert(STAGES >= 3, "shared-memory ring too shallow");
+  constexpr int smem = STAGES * kStage + kFixed;
+  auto kern = gemm2_kernel<BN, STAGES, FUSED>;
   static int configured_dev = -1;
   int dev = 0;
   SYN_CUDA_TRY(cudaGetDevice(&dev));
@@ -216,9 +218,10 @@ static int launch_pair_bn(const GemmParams& p, const CUtensorMap& tmap_b_half, i
   return SYN_OK;
 }
 
-// CTA-pair kernel: 256-row tiles, plain local stores.  Usable when every wave starts and ends on a
-// 256-row boundary.  SYNCOPATE_B200_NO_PAIR=1 keeps the one-CTA kernel (tuning aid).
-static bool pair_eligible(const GemmParams& p, int bn, int grid) {
+// CTA-pair kernel: 256-row tiles.  Usable when every wave starts and ends on a 256-row boundary and
+// tiles are handed out round-robin (no grid-wide tile counter).  SYNCOPATE_B200_NO_PAIR=1 keeps the
+// one-CTA kernel (tuning aid).
+bool pair_eligible(const GemmParams& p, int bn, int grid) {
   static int disabled = -1;
   if (disabled < 0) {
     const char* e = getenv("SYNCOPATE_B200_NO_PAIR");
@@ -227,13 +230,14 @@ static bool pair_eligible(const GemmParams& p, int bn, int grid) {
   if (disabled || grid < 2 || p.sched != nullptr) return false;
   if (bn % 32 != 0 || bn < 64) return false;
   for (int w = 0; w < p.num_waves; ++w) {
-    if (p.waves[w].route >= 0) return false;
     if ((p.waves[w].tiles_m & 1) || (p.waves[w].off_m & 1)) return false;
+    if (p.waves[w].route >= 0 && p.routes[p.waves[w].route].tmap >= 0 && bn % 64 != 0) return false;
   }
   return true;
 }
 
-static int gemm_launch_pair(const GemmParams& p_in, const syn_gemm_args* a, int bn, int grid, cudaStream_t stream) {
+int gemm_launch_pair(const GemmParams& p_in, const syn_gemm_args* a, int bn, int grid, bool fused,
+                     cudaStream_t stream) {
   GemmParams p = p_in;
   p.idesc = make_idesc_f16(GEMM2_BM, bn, a->dtype == SYN_DTYPE_BF16 ? 1u : 0u, 0, 0);
   CUtensorMap tmap_b_half;
@@ -241,16 +245,21 @@ static int gemm_launch_pair(const GemmParams& p_in, const syn_gemm_args* a, int 
   int rc = encode_tmap_2d_sw128(&tmap_b_half, a->b, a->N, a->K, ldb, bn / 2, GEMM_BK);
   if (rc != SYN_OK) return rc;
   int pair_tiles = 0;
-  for (int w = 0; w < p.num_waves; ++w) pair_tiles += (p.waves[w].tiles_m >> 1) * p.waves[w].tiles_n;
+  bool routed = false;
+  for (int w = 0; w < p.num_waves; ++w) {
+    pair_tiles += (p.waves[w].tiles_m >> 1) * p.waves[w].tiles_n;
+    routed = routed || p.waves[w].route >= 0;
+  }
   int g = std::min(grid & ~1, 2 * pair_tiles);
   if (g < 2) return SYN_ERR_INVALID;
   // Tail splitting: a small remainder after the last full round is cut along K over all pairs
-  // instead of occupying a round of its own.  Needs the caller's zeroed workspace.
+  // instead of occupying a round of its own.  Needs the caller's zeroed workspace, and plain local
+  // stores (a routed tile is counted, staged or reduced where it is finished).
   PairTail tail;
   memset(&tail, 0, sizeof(tail));
   const int pairs = g / 2;
   const int rem = pair_tiles % pairs, rounds = pair_tiles / pairs;
-  if (a->workspace != nullptr && rounds >= 1 && rem > 0 && rem * 4 <= pairs) {
+  if (!routed && a->workspace != nullptr && rounds >= 1 && rem > 0 && rem * 4 <= pairs) {
     const int slices = std::min(std::min(pairs / rem, p.k_blocks), 32);
     const size_t need = 256 + static_cast<size_t>(rem) * slices * GEMM2_BM * bn * sizeof(float);
     if (slices >= 2 && a->workspace_bytes >= need && (reinterpret_cast<uintptr_t>(a->workspace) & 255) == 0) {
@@ -261,16 +270,22 @@ static int gemm_launch_pair(const GemmParams& p_in, const syn_gemm_args* a, int 
       tail.ws = reinterpret_cast<float*>(static_cast<char*>(a->workspace) + 256);
     }
   }
+#define SYN_PAIR_CASE(BN_)                                                                         \
+  case BN_:                                                                                        \
+    return fused ? launch_pair_bn<BN_, true>(p, tmap_b_half, pair_tiles, g, tail, stream)           \
+                 : launch_pair_bn<BN_, false>(p, tmap_b_half, pair_tiles, g, tail, stream);
   switch (bn) {
-    case 256: return launch_pair_bn<256>(p, tmap_b_half, pair_tiles, g, tail, stream);
-    case 224: return launch_pair_bn<224>(p, tmap_b_half, pair_tiles, g, tail, stream);
-    case 192: return launch_pair_bn<192>(p, tmap_b_half, pair_tiles, g, tail, stream);
-    case 160: return launch_pair_bn<160>(p, tmap_b_half, pair_tiles, g, tail, stream);
-    case 128: return launch_pair_bn<128>(p, tmap_b_half, pair_tiles, g, tail, stream);
-    case 96: return launch_pair_bn<96>(p, tmap_b_half, pair_tiles, g, tail, stream);
-    case 64: return launch_pair_bn<64>(p, tmap_b_half, pair_tiles, g, tail, stream);
-    default: return SYN_ERR_UNSUPPORTED;
+    SYN_PAIR_CASE(256)
+    SYN_PAIR_CASE(224)
+    SYN_PAIR_CASE(192)
+    SYN_PAIR_CASE(160)
+    SYN_PAIR_CASE(128)
+    SYN_PAIR_CASE(96)
+    SYN_PAIR_CASE(64)
+    default:
+      return SYN_ERR_UNSUPPORTED;
   }
+#undef SYN_PAIR_CASE
 }
 
 int gemm_launch(const GemmParams& p, int bn, bool fused, int grid, cudaStream_t stream) {
@@ -321,8 +336,8 @@ int syn_gemm(const syn_gemm_args* args, const syn_schedule* sched, const syn_sch
   if (args == nullptr) return SYN_ERR_INVALID;
   int grid = 0, bn = 0;
   bool want_pair = false;
-  const bool plain = !(producer_sched != nullptr && args->producer_signal_ptr != nullptr) && args->sched_counter == nullptr;
-  int rc = gemm_resolve_grid_and_bn(args, sched ? sched : producer_sched, &grid, &bn, 32, plain ? &want_pair : nullptr);
+  int rc = gemm_resolve_grid_and_bn(args, sched ? sched : producer_sched, &grid, &bn, 32,
+                                    args->sched_counter == nullptr ? &want_pair : nullptr);
   if (rc != SYN_OK) return rc;
   const syn_schedule* order = sched ? sched : producer_sched;
   GemmParams p;
@@ -354,7 +369,8 @@ int syn_gemm(const syn_gemm_args* args, const syn_schedule* sched, const syn_sch
       fused = true;
     }
   }
-  if (!fused && want_pair && pair_eligible(p, bn, grid)) return gemm_launch_pair(p, args, bn, grid, static_cast<cudaStream_t>(stream));
+  if (want_pair && pair_eligible(p, bn, grid))
+    return gemm_launch_pair(p, args, bn, grid, fused, static_cast<cudaStream_t>(stream));
   grid = std::min(grid, p.total_tiles);
   if (grid <= 0) return SYN_ERR_INVALID;
   return gemm_launch(p, bn, fused, grid, static_cast<cudaStream_t>(stream));

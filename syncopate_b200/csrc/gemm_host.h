@@ -13,5 +13,8 @@ int gemm_fill_common(GemmParams* p, const syn_gemm_args* a, const syn_schedule* 
 int gemm_resolve_grid_and_bn(const syn_gemm_args* a, const syn_schedule* sched, int* grid, int* bn, int multiple = 32,
                              bool* pair_out = nullptr);
 int gemm_launch(const GemmParams& p, int bn, bool fused, int grid, cudaStream_t stream);
+// CTA-pair form (gemm2_kernel): usable when pair_eligible() says so for the filled parameters.
+bool pair_eligible(const GemmParams& p, int bn, int grid);
+int gemm_launch_pair(const GemmParams& p, const syn_gemm_args* a, int bn, int grid, bool fused, cudaStream_t stream);
 
 }  // namespace syn

@@ -30,7 +30,10 @@ constexpr int GEMM_THREADS = 256;    // warp0 TMA, warp1 MMA, warp2 TMEM alloc, 
 #endif
 constexpr int COMM_PIECE = SYN_COMM_PIECE;  // bytes per bulk copy of the comm warp
 constexpr int COMM_NBUF = SYN_COMM_NBUF;    // ring slots (NBUF - 1 loads in flight at most)
-static_assert(COMM_PIECE * COMM_NBUF >= 2 * 128 * 128, "the routed epilogue stages two 128 x 64 16-bit half tiles there");
+constexpr int EPI_STAGE_BYTES = 32 * 128;     // one epilogue warp's 32 rows x 64 columns of 16 bit
+static_assert(COMM_PIECE * COMM_NBUF >= 4 * 2 * EPI_STAGE_BYTES,
+              "the routed epilogue stages two 32 x 64 16-bit pieces per epilogue warp there");
+constexpr int GEMM_MAX_RED = 7;               // staged partial slabs an owner wave can add (world - 1)
 
 struct GemmWave {
   int16_t tiles_m, tiles_n;  // tile grid of the wave
@@ -51,6 +54,9 @@ struct GemmRoute {
   int16_t tmap;           // index into GemmParams::tmap_out: tiles leave through shared memory and TMA
                           // stores (full 128-byte lines, the form NVLink carries well); -1 = direct stores
   int32_t tmap_row0;      // row of the wave's first tile row in that map's coordinates
+  int16_t red_sig[GEMM_MAX_RED];  // reduce waves: flag index (in GemmParams::red_flags) guarding the rows of this
+                                  // wave in staged slab s
+  int16_t pad_;
 };
 
 // One 2-D strided copy between mapped buffers, executed cooperatively by all comm warps.
@@ -77,7 +83,6 @@ struct GemmParams {
   int32_t total_tiles;
   int32_t num_waves;
   int32_t num_comm_ops;
-  int32_t wide_store;     // 1: TMA-store routes send 64-row x 128-column boxes (256-byte row segments)
   int32_t raise_flags_on_abort;  // 1: a CTA that gave up on a wait raises every route flag before it leaves
   int32_t num_red;        // staged partial slabs to add in `reduce` routes
   int32_t red_ld;
@@ -90,8 +95,8 @@ struct GemmParams {
   uint64_t signal_value;
   uint64_t timeout_ns;
   int32_t* status;
-  const void* red_src[7];       // staged slabs (address of the slab's row 0)
-  const uint64_t* red_flag[7];  // flag guarding each slab
+  const void* red_src[GEMM_MAX_RED];  // staged slabs (address of the slab's row 0)
+  const uint64_t* red_flags;          // local flag array the reduce waves' red_sig index
   GemmWave waves[GEMM_MAX_WAVES];
   GemmRoute routes[GEMM_MAX_WAVES];
   CommOp comm[GEMM_MAX_COMM_OPS];
@@ -145,62 +150,167 @@ __device__ __forceinline__ float2 unpack2(uint32_t u, int dtype) {
   }
 }
 
+// Bounded wait (regardless of the abort word) until the phase `parity` of a barrier that counts
+// bulk-load bytes has completed: used by a role that gives up while its loads are still in flight,
+// because a CTA must not exit while the async proxy may still write its shared memory.
+__device__ __forceinline__ void drain_wait(uint64_t* bar, uint32_t parity, uint64_t timeout_ns) {
+  const uint64_t t0 = globaltimer_ns();
+  while (!mbar_try_wait(bar, parity)) {
+    if (globaltimer_ns() - t0 > timeout_ns) break;
+  }
+}
+
 // The comm warp of each CTA: walks the op list in order; for each op copies pieces
-// blockIdx.x, blockIdx.x + gridDim.x, ... through a small shared-memory ring.
+// blockIdx.x, blockIdx.x + gridDim.x, ... through a small shared-memory ring.  A wait that fails
+// (its own flag wait, or the CTA's abort word seen inside a ring wait) ends the walk: the loads in
+// flight are waited for, nothing more is copied and no flag is raised for the unfinished op.
 __device__ __forceinline__ void comm_warp_run(const CommOp* ops, int num_ops, uint32_t* counters,
                                               uint64_t signal_value, char* ring, uint64_t* bars,
                                               volatile int* abort_word, uint64_t timeout_ns, int lane) {
+  if (lane != 0) return;
   uint32_t issued = 0;    // loads issued so far, over all ops (ring slot = n % NBUF, parity = (n / NBUF) & 1)
   uint32_t consumed = 0;  // stores issued so far, over all ops (same order as the loads)
-  for (int o = 0; o < num_ops; ++o) {
+  bool ok = true;
+  for (int o = 0; o < num_ops && ok; ++o) {
     const CommOp& op = ops[o];
-    if (lane == 0) {
-      if (op.wait_flag != nullptr) flag_wait_ge(op.wait_flag, signal_value, abort_word, timeout_ns);
-      const uint32_t ppr = (op.row_bytes + COMM_PIECE - 1) / COMM_PIECE;
-      const uint32_t total = op.rows * ppr;
-      constexpr uint32_t LOOKAHEAD = COMM_NBUF - 2;
-      uint32_t next_load = blockIdx.x;  // piece index of the next load to issue
-      uint32_t cur = blockIdx.x;        // piece index of the next store to issue
-      auto issue_load = [&](uint32_t piece) {
-        const uint32_t row = piece / ppr, col = (piece - row * ppr) * COMM_PIECE;
-        const uint32_t bytes = min(static_cast<uint32_t>(COMM_PIECE), op.row_bytes - col);
-        const uint32_t slot = issued % COMM_NBUF;
-        mbar_expect_tx(&bars[slot], bytes);
-        bulk_g2s(ring + slot * COMM_PIECE, op.src + row * op.src_pitch + col, bytes, &bars[slot]);
-        ++issued;
-      };
-      while (issued - consumed < LOOKAHEAD && next_load < total) {
+    if (op.wait_flag != nullptr && !flag_wait_ge(op.wait_flag, signal_value, abort_word, timeout_ns)) {
+      ok = false;
+      break;
+    }
+    const uint32_t ppr = (op.row_bytes + COMM_PIECE - 1) / COMM_PIECE;
+    const uint32_t total = op.rows * ppr;
+    constexpr uint32_t LOOKAHEAD = COMM_NBUF - 2;
+    uint32_t next_load = blockIdx.x;  // piece index of the next load to issue
+    uint32_t cur = blockIdx.x;        // piece index of the next store to issue
+    auto issue_load = [&](uint32_t piece) {
+      const uint32_t row = piece / ppr, col = (piece - row * ppr) * COMM_PIECE;
+      const uint32_t bytes = min(static_cast<uint32_t>(COMM_PIECE), op.row_bytes - col);
+      const uint32_t slot = issued % COMM_NBUF;
+      mbar_expect_tx(&bars[slot], bytes);
+      bulk_g2s(ring + slot * COMM_PIECE, op.src + row * op.src_pitch + col, bytes, &bars[slot]);
+      ++issued;
+    };
+    while (issued - consumed < LOOKAHEAD && next_load < total) {
+      issue_load(next_load);
+      next_load += gridDim.x;
+    }
+    while (cur < total) {
+      if (next_load < total) {
+        // the slot about to be refilled was last read by a store at least two groups back
+        bulk_wait_read<1>();
         issue_load(next_load);
         next_load += gridDim.x;
       }
-      while (cur < total) {
-        if (next_load < total) {
-          // the slot about to be refilled was last read by a store at least two groups back
-          bulk_wait_read<1>();
-          issue_load(next_load);
-          next_load += gridDim.x;
-        }
-        const uint32_t slot = consumed % COMM_NBUF;
-        mbar_wait(&bars[slot], (consumed / COMM_NBUF) & 1u, abort_word, timeout_ns);
-        const uint32_t row = cur / ppr, col = (cur - row * ppr) * COMM_PIECE;
-        const uint32_t bytes = min(static_cast<uint32_t>(COMM_PIECE), op.row_bytes - col);
-        bulk_s2g(op.dst + row * op.dst_pitch + col, ring + slot * COMM_PIECE, bytes);
-        bulk_commit();
-        ++consumed;
-        cur += gridDim.x;
+      const uint32_t slot = consumed % COMM_NBUF;
+      if (!mbar_wait(&bars[slot], (consumed / COMM_NBUF) & 1u, abort_word, timeout_ns)) {
+        ok = false;
+        break;
       }
-      bulk_wait<0>();
-      fence_proxy_async();
-      if (op.set_flag != nullptr) {
+      const uint32_t row = cur / ppr, col = (cur - row * ppr) * COMM_PIECE;
+      const uint32_t bytes = min(static_cast<uint32_t>(COMM_PIECE), op.row_bytes - col);
+      bulk_s2g(op.dst + row * op.dst_pitch + col, ring + slot * COMM_PIECE, bytes);
+      bulk_commit();
+      ++consumed;
+      cur += gridDim.x;
+    }
+    if (!ok) break;
+    bulk_wait<0>();
+    fence_proxy_async();
+    if (op.set_flag != nullptr) {
+      __threadfence_system();
+      const uint32_t old = atomicAdd(&counters[o], 1u);
+      if (old == gridDim.x - 1) {
+        counters[o] = 0;
         __threadfence_system();
-        const uint32_t old = atomicAdd(&counters[o], 1u);
-        if (old == gridDim.x - 1) {
-          counters[o] = 0;
-          __threadfence_system();
-          st_release_sys_u64(op.set_flag, signal_value);
+        st_release_sys_u64(op.set_flag, signal_value);
+      }
+    }
+  }
+  if (!ok) {
+    for (uint32_t n = consumed; n < issued; ++n) drain_wait(&bars[n % COMM_NBUF], (n / COMM_NBUF) & 1u, timeout_ns);
+    bulk_wait<0>();
+  }
+}
+
+// Bounded wait for the bulk loads still in flight into one stage of this CTA's shared memory, for a
+// producer that gives up: a CTA must not exit while the async proxy may still write its shared
+// memory.  `fills` = how many times the stage's full barrier has been armed with a load.
+__device__ __forceinline__ void drain_stage(uint64_t* full_bar, uint32_t fills, uint64_t timeout_ns) {
+  if (fills != 0) drain_wait(full_bar, (fills - 1u) & 1u, timeout_ns);
+}
+
+// Adds the 16-bit partial sums staged by the peers (slab order = rank order, fixed) to 32 fp32
+// accumulator values of one output row; four slabs' loads are in flight at a time.
+__device__ __forceinline__ void epi_add_staged(const GemmParams& p, uint32_t (&r)[32], int grow, int col) {
+  const size_t elem = static_cast<size_t>(grow - p.red_row0) * p.red_ld + col;
+#pragma unroll
+  for (int g = 0; g < 2; ++g) {
+    uint4 u[4][4];
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+      if (g * 4 + s < p.num_red) {
+        const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(p.red_src[(g * 4 + s) % GEMM_MAX_RED]) + elem * 2);
+#pragma unroll
+        for (int v = 0; v < 4; ++v)
+          if (col + v * 8 < p.N) u[s][v] = __ldcg(src + v);
+      }
+    }
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+      if (g * 4 + s < p.num_red) {
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          if (col + v * 8 < p.N) {
+            const uint32_t w4[4] = {u[s][v].x, u[s][v].y, u[s][v].z, u[s][v].w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 f = unpack2(w4[j], p.dtype);
+              r[v * 8 + 2 * j] = __float_as_uint(__uint_as_float(r[v * 8 + 2 * j]) + f.x);
+              r[v * 8 + 2 * j + 1] = __float_as_uint(__uint_as_float(r[v * 8 + 2 * j + 1]) + f.y);
+            }
+          }
         }
       }
     }
+  }
+}
+
+__device__ __forceinline__ void epi_pack(const uint32_t (&r)[32], uint4 (&packed)[4], int dtype) {
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {
+    packed[v].x = pack2(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]), dtype);
+    packed[v].y = pack2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]), dtype);
+    packed[v].z = pack2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]), dtype);
+    packed[v].w = pack2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]), dtype);
+  }
+}
+
+// TMA-store route, one epilogue warp: the warp's 32 rows of a 64-column half tile go through one of
+// the warp's own two 4 KB staging pieces (128-byte swizzle of the output tensor map) and leave as
+// one 32 x 64 box issued by the warp's lane 0.  No other warp is involved, so nothing but the warp
+// itself synchronises.  `c` is the index of the 32-column chunk inside the tile.
+__device__ __forceinline__ void epi_stage_chunk(uint8_t* wstage, int c, int lane, const uint4 (&packed)[4],
+                                                const CUtensorMap* map, int x0, int y, uint32_t& nstore) {
+  // the two pieces alternate with the stores this warp has issued (over tiles as well), so the
+  // piece being refilled was read by the store before the previous one
+  uint8_t* sbuf = wstage + (nstore & 1u) * EPI_STAGE_BYTES;
+  if ((c & 1) == 0) {
+    if (lane == 0) bulk_wait_read<1>();  // the store that last read this piece is done with it
+    __syncwarp();
+  }
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {
+    const int chunk16 = (c & 1) * 4 + v;
+    *reinterpret_cast<uint4*>(sbuf + lane * 128 + ((chunk16 ^ (lane & 7)) << 4)) = packed[v];
+  }
+  if (c & 1) {
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_2d(map, sbuf, x0 + (c >> 1) * 64, y);
+      bulk_commit();
+    }
+    ++nstore;
   }
 }
 
@@ -225,6 +335,7 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_holder + 1);
   int* abort_info = const_cast<int*>(abort_word) + 1;  // {wave, flag}
   volatile int* tile_q = reinterpret_cast<volatile int*>(abort_info + 2);  // [TILE_Q] tile ids, -1 = no more
+  volatile int* epi_sync = tile_q + TILE_Q;  // [2][2] {tile, abort} agreed on by the four epilogue warps
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -270,8 +381,10 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
       TileCursor cur;
       int stage = 0;
       uint32_t phase = 0;
+      uint32_t issued = 0;  // k-block loads issued so far
       bool first = true;
-      for (uint32_t n = 0;; ++n) {
+      bool gave_up = false;
+      for (uint32_t n = 0; !gave_up; ++n) {
         // next tile: taken from the grid-wide counter (dynamic) or round-robin (static), then
         // handed to the other roles through the tile queue
         const int slot = n % TILE_Q;
@@ -293,6 +406,7 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
                 abort_info[0] = cur.wave;
                 abort_info[1] = sig;
               }
+              gave_up = true;  // the wave's data never arrived: issue no load for it
             }
             fence_proxy_async();  // order the flag read before async-proxy (TMA) reads of the chunk
             if (p.trace != nullptr) {
@@ -304,16 +418,25 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
           }
           first = false;
         }
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
-          mbar_wait(&empty_bar[stage], phase ^ 1u, abort_word, p.timeout_ns);
+        for (int kb = 0; kb < p.k_blocks && !gave_up; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_word, p.timeout_ns)) {
+            gave_up = true;  // somebody in the CTA gave up: the stage may never be released
+            break;
+          }
           mbar_expect_tx(&full_bar[stage], L::STAGE_BYTES);
           tma_load_2d(sA + stage * L::A_BYTES, &p.tmap_a, &full_bar[stage], kb * GEMM_BK, m_blk * GEMM_BM);
           tma_load_2d(sB + stage * L::B_BYTES, &p.tmap_b, &full_bar[stage], kb * GEMM_BK, n_blk * BN);
+          ++issued;
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
           }
         }
+      }
+      if (*abort_word != 0) {
+        // loads already issued keep writing this CTA's shared memory: wait for them before leaving
+        for (int s = 0; s < STAGES; ++s)
+          drain_stage(&full_bar[s], issued / STAGES + (static_cast<uint32_t>(s) < issued % STAGES ? 1u : 0u), p.timeout_ns);
       }
     }
   } else if (warp == 1) {
@@ -376,17 +499,18 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
     int acc = 0;
     uint32_t acc_phase = 0;
     bool first = true;
-    bool red_ready = false;
     int done_wave = -1;        // wave whose tiles this CTA has stored but not yet counted
     uint32_t done_tiles = 0;
-    // counts this CTA's finished tiles of a wave once, when it leaves the wave: its TMA stores have
-    // been performed and its plain stores fenced before the count; the CTA that completes the
-    // wave's total raises the wave's flag
+    uint8_t* wstage = ring + q * (2 * EPI_STAGE_BYTES);  // this warp's staging pieces (TMA-store routes)
+    uint32_t nstore = 0;                                  // TMA stores this warp has issued
+    // counts this CTA's finished tiles of a wave once, when it leaves the wave: every warp's TMA
+    // stores have been performed and its plain stores fenced before the count; the CTA that
+    // completes the wave's total raises the wave's flag
     auto flush_wave = [&]() {
       if constexpr (FUSED) {
         if (done_wave >= 0 && done_tiles > 0) {
           const GemmWave& dw = p.waves[done_wave];
-          if (warp == 4 && lane == 0) {
+          if (lane == 0) {
             bulk_wait<0>();
             fence_proxy_async();
           }
@@ -410,10 +534,23 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
     for (uint32_t n = 0;; ++n) {
       const int slot = n % TILE_Q;
       mbar_wait(&tq_full[slot], (n / TILE_Q) & 1u, abort_word, p.timeout_ns);
-      const int tile = tile_q[slot];
+      int tile = tile_q[slot];
+      int ab = *abort_word;
       __syncwarp();
       if (lane == 0) mbar_arrive(&tq_empty[slot]);
-      if (tile < 0 || tile >= p.total_tiles || *abort_word != 0) break;
+      if constexpr (FUSED) {
+        // The four warps meet at named barriers inside a wave (flush_wave): they must take the
+        // same tiles and leave at the same tile, so warp 4's view of the queue slot and of the
+        // abort word is the one all of them use.
+        if (warp == 4 && lane == 0) {
+          epi_sync[2 * (n & 1u)] = tile;
+          epi_sync[2 * (n & 1u) + 1] = ab;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        tile = epi_sync[2 * (n & 1u)];
+        ab = epi_sync[2 * (n & 1u) + 1];
+      }
+      if (tile < 0 || tile >= p.total_tiles || ab != 0) break;
       int m_blk, n_blk;
       const bool moved = cur.seek(p, tile, m_blk, n_blk);
       const GemmWave& wv = p.waves[cur.wave];
@@ -424,6 +561,7 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
       int out_row = m_blk * GEMM_BM + q * 32 + lane;  // row inside the destination
       const int grow = out_row;                       // global row of C
       bool reduce = false;
+      int tmap_idx = -1, tmap_y = 0;
       if constexpr (FUSED) {
         if (wv.route >= 0) {
           const GemmRoute& rt = p.routes[wv.route];
@@ -431,19 +569,25 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
           out_ld = rt.ld;
           out_row -= wv.off_m * GEMM_BM;
           reduce = rt.reduce != 0;
-          if ((moved || first) && rt.gate != nullptr) {
-            if (lane == 0) flag_wait_ge(rt.gate, rt.gate_value, abort_word, p.timeout_ns);
-            __syncwarp();
+          if (rt.tmap >= 0) {
+            tmap_idx = rt.tmap;
+            tmap_y = rt.tmap_row0 + (m_blk - wv.off_m) * GEMM_BM + q * 32;
           }
-          if (reduce && !red_ready) {
-            if (lane < p.num_red) {
-              if (!flag_wait_ge(p.red_flag[lane], p.signal_value, abort_word, p.timeout_ns)) {
-                abort_info[0] = cur.wave;
-                abort_info[1] = -2 - lane;
-              }
+          if (moved || first) {
+            if (rt.gate != nullptr) {
+              if (lane == 0) flag_wait_ge(rt.gate, rt.gate_value, abort_word, p.timeout_ns);
+              __syncwarp();
             }
-            __syncwarp();
-            red_ready = true;
+            if (reduce) {
+              // the staged partial sums of this wave's rows: one flag per contributing rank
+              if (lane < p.num_red) {
+                if (!flag_wait_ge(p.red_flags + rt.red_sig[lane], p.signal_value, abort_word, p.timeout_ns)) {
+                  abort_info[0] = cur.wave;
+                  abort_info[1] = -2 - lane;
+                }
+              }
+              __syncwarp();
+            }
           }
         }
       }
@@ -453,15 +597,6 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
       const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc * ACC_STRIDE);
       const int col0 = n_blk * BN;
       const bool row_ok = grow < p.M;
-      int tmap_idx = -1, tmap_y = 0;
-      if constexpr (FUSED) {
-        if (wv.route >= 0 && p.routes[wv.route].tmap >= 0) {
-          tmap_idx = p.routes[wv.route].tmap;
-          tmap_y = p.routes[wv.route].tmap_row0 + (m_blk - wv.off_m) * GEMM_BM;
-        }
-      }
-      const bool leader = (warp == 4 && lane == 0);
-      const int srow = q * 32 + lane;  // row of this thread inside the 128-row staging tile
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -469,83 +604,15 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
         tmem_ld_wait();
         const int col = col0 + c * 32;
         if constexpr (FUSED) {
-          if (reduce && row_ok) {
-            // add the partial sums staged by the peers (16-bit on the wire, fp32 here)
-            for (int s = 0; s < p.num_red; ++s) {
-              const uint4* src = reinterpret_cast<const uint4*>(
-                  reinterpret_cast<const char*>(p.red_src[s]) +
-                  (static_cast<size_t>(grow - p.red_row0) * p.red_ld + col) * 2);
-#pragma unroll
-              for (int v = 0; v < 4; ++v) {
-                if (col + v * 8 < p.N) {
-                  const uint4 u = __ldcg(src + v);
-                  const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-                  for (int j = 0; j < 4; ++j) {
-                    const float2 f = unpack2(w4[j], p.dtype);
-                    r[v * 8 + 2 * j] = __float_as_uint(__uint_as_float(r[v * 8 + 2 * j]) + f.x);
-                    r[v * 8 + 2 * j + 1] = __float_as_uint(__uint_as_float(r[v * 8 + 2 * j + 1]) + f.y);
-                  }
-                }
-              }
-            }
-          }
+          if (reduce && row_ok) epi_add_staged(p, r, grow, col);
         }
         uint4 packed[4];
-#pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          packed[v].x = pack2(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]), p.dtype);
-          packed[v].y = pack2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]), p.dtype);
-          packed[v].z = pack2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]), p.dtype);
-          packed[v].w = pack2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]), p.dtype);
-        }
+        epi_pack(r, packed, p.dtype);
         bool staged = false;
         if constexpr (FUSED) {
-          if (tmap_idx >= 0 && p.wide_store) {
+          if (tmap_idx >= 0) {
             staged = true;
-            // 128-column groups leave as two 64-row boxes with 256-byte row segments (longer
-            // segments travel better over NVLink); rows 0-63 use the first 16 KB of the staging
-            // space, rows 64-127 the second, no swizzle
-            uint8_t* sbuf = ring + (srow >> 6) * (64 * 256);
-            if ((c & 3) == 0) {
-              if (leader) bulk_wait_read<0>();
-              asm volatile("bar.sync 1, 128;" ::: "memory");
-            }
-#pragma unroll
-            for (int v = 0; v < 4; ++v)
-              *reinterpret_cast<uint4*>(sbuf + (srow & 63) * 256 + (c & 3) * 64 + v * 16) = packed[v];
-            if ((c & 3) == 3) {
-              fence_proxy_async_smem();
-              asm volatile("bar.sync 1, 128;" ::: "memory");
-              if (leader) {
-                tma_store_2d(&p.tmap_out[tmap_idx], ring, col0 + (c >> 2) * 128, tmap_y);
-                tma_store_2d(&p.tmap_out[tmap_idx], ring + 64 * 256, col0 + (c >> 2) * 128, tmap_y + 64);
-                bulk_commit();
-              }
-            }
-          } else if (tmap_idx >= 0) {
-            staged = true;
-            // 64-column halves of the tile go through two 16 KB staging buffers (the comm ring's
-            // space, which a routed epilogue does not otherwise use), laid out with the 128-byte
-            // swizzle of the output tensor map
-            uint8_t* sbuf = ring + ((c >> 1) & 1) * (GEMM_BM * 128);
-            if ((c & 1) == 0) {
-              if (leader) bulk_wait_read<1>();  // the store that last read this buffer is done with it
-              asm volatile("bar.sync 1, 128;" ::: "memory");
-            }
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-              const int chunk16 = (c & 1) * 4 + v;
-              *reinterpret_cast<uint4*>(sbuf + srow * 128 + ((chunk16 ^ (srow & 7)) << 4)) = packed[v];
-            }
-            if ((c & 1) == 1) {
-              fence_proxy_async_smem();
-              asm volatile("bar.sync 1, 128;" ::: "memory");
-              if (leader) {
-                tma_store_2d(&p.tmap_out[tmap_idx], sbuf, col0 + (c >> 1) * 64, tmap_y);
-                bulk_commit();
-              }
-            }
+            epi_stage_chunk(wstage, c, lane, packed, &p.tmap_out[tmap_idx], col0, tmap_y, nstore);
           }
         }
         if (!staged && row_ok) {
@@ -570,11 +637,11 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
       }
     }
     flush_wave();
+    if constexpr (FUSED) {
+      if (lane == 0) bulk_wait<0>();  // staged pieces still being read by this warp's TMA stores
+    }
   }
 
-  if constexpr (FUSED) {
-    if (warp == 4 && lane == 0) bulk_wait<0>();  // staged tiles still being read by TMA stores
-  }
   tc_fence_before();
   __syncthreads();
   if (warp == 2) {

@@ -126,7 +126,14 @@ int syn_flag_set(uint64_t* flag, uint64_t value, void* stream) {
       write_value = reinterpret_cast<write_value_fn>(fn);
     looked_up = true;
   }
-  if (write_value != nullptr) {
+  // (while the stream is being captured into a graph the kernel form is used: a kernel node is
+  // always capturable)
+  cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(static_cast<cudaStream_t>(stream), &capturing) != cudaSuccess) {
+    cudaGetLastError();
+    capturing = cudaStreamCaptureStatusNone;
+  }
+  if (write_value != nullptr && capturing == cudaStreamCaptureStatusNone) {
     CUresult r = write_value(static_cast<CUstream>(stream), reinterpret_cast<CUdeviceptr>(flag), value, 0);
     if (r == CUDA_SUCCESS) return SYN_OK;
   }
@@ -167,6 +174,21 @@ int syn_flag_wait_stream(const uint64_t* flag, uint64_t value, void* stream) {
     snprintf(buf, sizeof(buf), "CUresult %d", static_cast<int>(r));
     set_cuda_error("cuStreamWaitValue64", buf);
     return SYN_ERR_CUDA;
+  }
+  return SYN_OK;
+}
+
+int syn_ce_run(const syn_ce_step* steps, int num_steps, void* const* streams, int num_streams, uint64_t value) {
+  if (steps == nullptr || num_steps < 0 || streams == nullptr || num_streams <= 0) return SYN_ERR_INVALID;
+  for (int i = 0; i < num_steps; ++i) {
+    const syn_ce_step& st = steps[i];
+    if (st.stream < 0) return SYN_ERR_INVALID;
+    void* sp = streams[st.stream % num_streams];
+    int rc = SYN_OK;
+    if (st.wait_flag != nullptr) rc = syn_flag_wait_stream(st.wait_flag, value, sp);
+    if (rc == SYN_OK && st.bytes > 0) rc = syn_memcpy_async(st.dst, st.src, st.bytes, sp);
+    if (rc == SYN_OK && st.set_flag != nullptr) rc = syn_flag_set(st.set_flag, value, sp);
+    if (rc != SYN_OK) return rc;
   }
   return SYN_OK;
 }

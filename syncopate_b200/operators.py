@@ -4,8 +4,8 @@ times.  Each object does, for one rank, what the reference's test drivers do by 
 rank's plan, plan signals, generate the op program, lower to schedules, allocate the symmetric
 buffers and flags, then launch the fused kernel with this rank's schedule.
 
-Flags carry an epoch that grows by one per call, so nothing is reset between calls and no barrier
-is needed inside the timed path.
+Flags carry an epoch that grows by one per call, so nothing is reset between calls; the one
+synchronisation per call is the device-side barrier described in the operators' docstrings.
 """
 from __future__ import annotations
 
@@ -14,11 +14,13 @@ from typing import Optional
 import torch
 
 from .communication.code_gen import CodeGenOptions, CommGenerator
+from . import _lib as _L
 from .communication.common_descriptors import (
     build_all_gather_plan_1d_swizzle,
     build_all_to_all_plan,
     build_reduce_scatter_direct_reduce_plan,
     build_ring_all_gather_plan,
+    split_transfers_along_axis,
 )
 from .computation.gemm import ag_gemm, gemm, gemm_rs
 from .computation.gemm.plan import rs_remote_signals, rs_transport_program
@@ -35,8 +37,10 @@ NUM_COUNTERS = 130  # SYN_NUM_COUNTERS: wave counters, copy counters, tile sched
 
 
 def plan_all_gather(world: int, rows_per_rank: int, K: int, dtype: torch.dtype, kind: str = "swizzle",
-                    copy_engine: bool = False):
-    """(generator, comm_info, lowered) for gathering ``[rows_per_rank, K]`` shards along dim 0."""
+                    copy_engine: bool = False, chunk_split: int = 1):
+    """(generator, comm_info, lowered) for gathering ``[rows_per_rank, K]`` shards along dim 0.
+    ``chunk_split`` > 1 cuts every remote slab into that many row pieces, each with a flag and a
+    wave of its own (``split_transfers_along_axis``)."""
     shape = (rows_per_rank * world, K)
     if kind == "swizzle":
         plans = {r: build_all_gather_plan_1d_swizzle(shape, dtype, 0, world, r, "a", "pull") for r in range(world)}
@@ -44,14 +48,17 @@ def plan_all_gather(world: int, rows_per_rank: int, K: int, dtype: torch.dtype, 
         plans = {r: build_ring_all_gather_plan(shape, dtype, 0, world, r, "a") for r in range(world)}
     else:
         raise ValueError("kind must be 'swizzle' or 'ring'")
+    if chunk_split > 1:
+        plans = {r: split_transfers_along_axis(pl, chunk_split, 0) for r, pl in plans.items()}
     gen = CommGenerator(plans)
     gen.plan_signals(plan_compute_signals=True)
     info = gen.generate_code_for_plan(CodeGenOptions(copy_engine=copy_engine))
     return gen, info, lower_comm_plan_to_raw_schedules(gen)
 
 
-def plan_reduce_scatter(world: int, M: int, N: int, dtype: torch.dtype, kind: str = "direct"):
-    """(generator, comm_info, lowered) for reduce-scattering a partial ``[M, N]`` along dim 0."""
+def plan_reduce_scatter(world: int, M: int, N: int, dtype: torch.dtype, kind: str = "direct", chunk_split: int = 1):
+    """(generator, comm_info, lowered) for reduce-scattering a partial ``[M, N]`` along dim 0.
+    ``chunk_split`` > 1 sends every slab as that many row pieces."""
     if kind == "direct":
         plans = {
             r: build_reduce_scatter_direct_reduce_plan(
@@ -69,23 +76,46 @@ def plan_reduce_scatter(world: int, M: int, N: int, dtype: torch.dtype, kind: st
         }
     else:
         raise ValueError("kind must be 'direct' or 'a2a'")
+    if chunk_split > 1:
+        if kind != "direct":
+            raise ValueError("chunk_split needs the direct plan (its source and destination rows share one axis)")
+        plans = {r: split_transfers_along_axis(pl, chunk_split, 0) for r, pl in plans.items()}
     gen = CommGenerator(plans)
     gen.plan_signals(plan_compute_signals=True)
     info = gen.generate_code_for_plan(CodeGenOptions(copy_engine=False))
     return gen, info, lower_comm_plan_to_raw_schedules(gen)
 
 
+_HAZARD_NOTE = """
+
+    **Who may write what, and when.**  Peers read this rank's symmetric input (and write its
+    symmetric output) directly.  With ``lockstep=True`` (default) every call starts with a
+    device-side barrier over all ranks, placed so that no transfer of the call starts before every
+    rank has entered it: whatever a rank wrote into its symmetric input *before* the call, in stream
+    order, is what the peers see.  Nothing in a call tells a rank when the peers are done with that
+    input: rewrite it only after a barrier that follows the call (``ctx.barrier()`` on the same
+    stream), or construct the operator with ``sync_after=True``, which ends every call with a
+    second barrier so that inputs may be rewritten and outputs read as soon as the call has
+    returned in stream order.  With ``lockstep=False`` the caller provides both guarantees."""
+
+
 class AllGatherGemm:
     """``C[rows * world, N] = all_gather(A_shard)[rows * world, K] @ B[N, K]^T`` per rank.
 
     ``comm="sm"``: the kernel's comm warps pull the chunks (``CodeGenOptions(copy_engine=False)``
-    program); ``comm="ce"``: the rank's copy-engine program (``copy_engine=True``) runs on a side
-    stream through ``CommContext.execute`` while the flag-gated GEMM runs on the caller's stream,
-    as in the reference's tests/test_ag_gemm_gen.py:44-77."""
+    program); ``comm="ce"``: the rank's copy-engine program (``copy_engine=True``) runs on side
+    streams while the flag-gated GEMM runs on the caller's stream, as in the reference's
+    tests/test_ag_gemm_gen.py:44-77.  ``chunk_split`` cuts every remote slab into row pieces with
+    flags of their own: the first tiles of a slab start after a piece has arrived instead of the
+    whole slab, and the step ends one piece's GEMM after the last arrival."""
+
+    __doc__ += _HAZARD_NOTE
 
     def __init__(self, ctx: SymmetricContext, rows_per_rank: int, K: int, N: int, dtype=torch.bfloat16,
                  plan: str = "swizzle", num_sms: int = 0, block_n: int = 0, timeout_ns: int = 0, comm: str = "sm",
-                 copy_streams: int = 2, lockstep: bool = True):
+                 copy_streams: int = 2, lockstep: bool = True, chunk_split: int = 1, sync_after: bool = False):
+        if comm not in ("sm", "ce"):
+            raise ValueError("comm must be 'sm' or 'ce'")
         self.ctx = ctx
         self.world, self.rank = ctx.world, ctx.rank
         self.rows, self.K, self.N, self.dtype = rows_per_rank, K, N, dtype
@@ -94,62 +124,53 @@ class AllGatherGemm:
         self.comm = comm
         # The swizzled order gives every rank a different peer at every step only while the ranks
         # move in step; free-running ranks drift, two of them then load the same peer's link and
-        # the transfers slow down.  A device-side barrier (about 11 us) at the start of each call
-        # keeps them aligned and costs less than it saves at 8 GPUs.
+        # the transfers slow down.  A device-side barrier at the start of each call keeps them
+        # aligned (and orders the peers' shard writes before the pulls).
         self.lockstep = lockstep
+        self.sync_after = sync_after
+        self.chunk_split = chunk_split
         self.generator, self.info, lowered = plan_all_gather(self.world, rows_per_rank, K, dtype, plan,
-                                                             copy_engine=(comm == "ce"))
+                                                             copy_engine=(comm == "ce"), chunk_split=chunk_split)
         self.schedule = lowered[self.rank]["a"]
         self.epoch = 0
         self.trace = None  # optional uint64 stamp buffer handed to the kernel (see syn_gemm_args.trace)
-        if comm == "ce":
-            from .communication.comm_runtime.communication_context import CommContext
-
-            self.info.local_world_size = self.world
-            self.comm_ctx = CommContext(self.rank, self.info, symmetric=ctx, timeout_ns=timeout_ns)
-            self.a = self.comm_ctx._buffers["a"]
-            self.flags = self.comm_ctx._recv
-            self._wave_offsets = [[o[0], 0] for o in self.schedule.gen_block_offset_lists()]
-            self._wave_sizes = [[s[0], N] for s in self.schedule.gen_block_shape_lists()]
-            self._signals = self.schedule.gen_signal_lists()
-            self._sched = torch.zeros(2, dtype=torch.int32, device=ctx.device)
-            # One chunk copy does not fill the link while the GEMM is running; consecutive chunks
-            # are therefore issued round-robin on a few streams so that several are in flight.
-            # Each (copy, flag) pair stays in order on its stream; chunks are independent.
-            self._copy_streams = [torch.cuda.Stream() for _ in range(max(1, copy_streams))]
-            self._chunks = self._chunk_program()
-            return
         self.a = ctx.alloc((self.M, K), dtype)
         self.flags = ctx.alloc((max(self.info.recv_signal_num, 1),), torch.int64)
         self.counters = torch.zeros(NUM_COUNTERS, dtype=torch.int32, device=ctx.device)
+        if comm == "ce":
+            self._wave_offsets = [[o[0], 0] for o in self.schedule.gen_block_offset_lists()]
+            self._wave_sizes = [[s[0], N] for s in self.schedule.gen_block_shape_lists()]
+            self._signals = self.schedule.gen_signal_lists()
+            # One chunk copy does not fill the link while the GEMM is running; consecutive chunks
+            # are therefore issued round-robin on a few streams so that several are in flight.
+            # Each (copy, flag) pair stays in order on its stream; chunks are independent.
+            self._copy_streams = [torch.cuda.Stream(device=ctx.device) for _ in range(max(1, copy_streams))]
+            self._ev_start = torch.cuda.Event()
+            self._ev_go = torch.cuda.Event()
+            steps = self.copy_program()
+            self._program, self._program_len = _L.make_ce_program(steps), len(steps)
 
-    def _chunk_program(self):
-        """``[(dst_ptr, src_ptr, nbytes, flag_ptr)]``: the rank's copy-engine program (copy ops
-        followed by the flag they publish), resolved to addresses once."""
-        out, pending = [], []
-        bufs = self.comm_ctx.comm_buffers
+    def copy_program(self):
+        """``[(0, dst, src, nbytes, flag or 0, stream index)]``: the rank's copy-engine program (its
+        CopyEngineOp records, each group followed by the IntraNodeSignal that publishes it) with all
+        addresses resolved; groups go round-robin over the copy streams."""
+        steps, pending, group = [], [], 0
+        es = self.dtype.itemsize
+        assert es == self.a.local.element_size()
         for op in self.info.operations[self.rank][0]:
             kind = type(op).__name__
             if kind == "CopyEngineOp":
                 if op.src_rank == op.dst_rank:
                     continue
-                pending.append((bufs[op.dst][op.dst_rank].data_ptr() + op.dst_offset,
-                                bufs[op.src][op.src_rank].data_ptr() + op.src_offset, op.size))
+                pending.append((self.a.symm.ptrs[op.dst_rank] + op.dst_offset, self.a.symm.ptrs[op.src_rank] + op.src_offset,
+                                op.size))
             elif kind == "IntraNodeSignal" and pending:
-                flag = self.comm_ctx.recv_signal_bufs[op.rank].data_ptr() + 8 * op.offset
-                out.append((pending, flag))
+                flag = self.flags.symm.ptrs[op.rank] + 8 * op.offset
+                for i, (dst, src, nbytes) in enumerate(pending):
+                    steps.append((0, dst, src, nbytes, flag if i == len(pending) - 1 else 0, group))
                 pending = []
-        return out
-
-    def _issue_copies(self, cur) -> None:
-        lib = _raw_lib()
-        for s in self._copy_streams:
-            s.wait_stream(cur)
-        for i, (copies, flag) in enumerate(self._chunks):
-            sp = self._copy_streams[i % len(self._copy_streams)].cuda_stream
-            for dst, src, nbytes in copies:
-                lib.syn_memcpy_async(dst, src, nbytes, sp)
-            lib.syn_flag_set(flag, self.epoch, sp)
+                group += 1
+        return steps
 
     @property
     def shard(self) -> torch.Tensor:
@@ -163,38 +184,58 @@ class AllGatherGemm:
         if self.world == 1:
             return gemm(self.a.local, b, c, 1, self.num_sms, BLOCK_SIZE_N=self.block_n, status=self.ctx.status,
                         timeout_ns=self.timeout_ns, stream=stream)
-        if self.lockstep:
-            self.ctx.barrier(stream)
+        cur = stream or torch.cuda.current_stream()
         if self.comm == "ce":
-            cur = stream or torch.cuda.current_stream()
-            self._issue_copies(cur)
+            # The GEMM starts at once on the caller's stream (its first wave is the resident slab);
+            # the barrier sits on the copy streams, in front of the transfers it is there for.
+            side = self._copy_streams
+            self._ev_start.record(cur)
+            side[0].wait_event(self._ev_start)
+            if self.lockstep:
+                self.ctx.barrier(side[0])
+            self._ev_go.record(side[0])
+            for s in side[1:]:
+                s.wait_event(self._ev_go)
+            _L.ce_run(self._program, self._program_len, side, self.epoch)
             gemm(self.a.local, b, c, self.world, self.num_sms, BLOCK_SIZE_N=self.block_n,
                  cur_wave_sizes=self._wave_sizes, wave_offsets=self._wave_offsets, signal_ptr=self.flags.local,
                  signal_offsets=self._signals, signal_value=self.epoch, status=self.ctx.status,
                  timeout_ns=self.timeout_ns, trace=self.trace, stream=cur)
-            for s in self._copy_streams:
+            for s in side:
                 cur.wait_stream(s)
-            return c
-        return ag_gemm(self.a.symm, self.a.local, b, c, self.schedule, self.flags.local, self.counters,
-                       epoch=self.epoch, num_sms=self.num_sms, block_n=self.block_n, timeout_ns=self.timeout_ns,
-                       status=self.ctx.status, stream=stream)
+        else:
+            if self.lockstep:
+                self.ctx.barrier(cur)
+            ag_gemm(self.a.symm, self.a.local, b, c, self.schedule, self.flags.local, self.counters,
+                    epoch=self.epoch, num_sms=self.num_sms, block_n=self.block_n, timeout_ns=self.timeout_ns,
+                    status=self.ctx.status, trace=self.trace, stream=cur)
+        if self.sync_after:
+            self.ctx.barrier(cur)
+        return c
 
 
 class GemmReduceScatter:
-    """``out[M / world, N] = sum over ranks of (A_r[M, K_r] @ B_r[N, K_r]^T)[own rows]``."""
+    """``out[M / world, N] = sum over ranks of (A_r[M, K_r] @ B_r[N, K_r]^T)[own rows]``.
+
+    Inputs are private to the rank; the symmetric state (staging slabs, flags) is the operator's
+    own and alternates with the call's parity, so back-to-back calls need no barrier for
+    correctness (a rank can only be two calls ahead of a peer after that peer has read the half it
+    overwrites).  ``lockstep`` keeps the ranks' transfers aligned in time (see AllGatherGemm)."""
 
     def __init__(self, ctx: SymmetricContext, M: int, N: int, dtype=torch.bfloat16, plan: str = "direct",
                  num_sms: int = 0, block_n: int = 0, timeout_ns: int = 0, lockstep: bool = True, comm: str = "sm",
-                 copy_streams: int = 2):
+                 copy_streams: int = 2, chunk_split: int = 1):
         """``comm="sm"``: the GEMM's epilogue stores each tile straight into the target rank's staging
-        slab.  ``comm="ce"`` (experimental): the epilogue stores locally and raises a local flag per
-        slab; side streams wait for the flag (a stream memory operation), move the slab with a copy
-        engine and raise the target's flag."""
+        slab (TMA stores to peer memory).  ``comm="ce"``: the epilogue stores locally and raises a
+        local flag per wave; side streams wait for the flag (a stream memory operation), move the
+        rows with a copy engine and raise the target's flag.  ``chunk_split`` sends every slab as
+        that many row pieces; the rows kept here are then reduced piece by piece as the matching
+        pieces arrive."""
         if comm not in ("sm", "ce"):
             raise ValueError("comm must be 'sm' or 'ce'")
         self.ctx = ctx
         self.comm = comm
-        self.lockstep = lockstep  # see AllGatherGemm: keeps the ranks' push targets disjoint in time
+        self.lockstep = lockstep
         self.world, self.rank = ctx.world, ctx.rank
         self.M, self.N, self.dtype = M, N, dtype
         self.slab = M // self.world
@@ -202,7 +243,7 @@ class GemmReduceScatter:
         self.epoch = 0
         if self.world == 1:
             return
-        self.generator, self.info, lowered = plan_reduce_scatter(self.world, M, N, dtype, plan)
+        self.generator, self.info, lowered = plan_reduce_scatter(self.world, M, N, dtype, plan, chunk_split)
         self.src_schedule = lowered[self.rank]["src"]
         self.dst_schedule = lowered[self.rank]["dst"]
         self.remote_signals = rs_remote_signals(self.info, self.rank, self.src_schedule)
@@ -212,15 +253,21 @@ class GemmReduceScatter:
         self.send = self.send_flags = None
         if comm == "ce":
             self.send = torch.empty(self.world, self.slab, N, dtype=dtype, device=ctx.device)
-            self.send_flags = torch.zeros(self.world, dtype=torch.int64, device=ctx.device)
+            self.send_flags = torch.zeros(len(self.remote_signals), dtype=torch.int64, device=ctx.device)
             self._copy_streams = [torch.cuda.Stream(device=ctx.device) for _ in range(max(1, copy_streams))]
+            self._ev_start = torch.cuda.Event()
+            self._ev_go = torch.cuda.Event()
+            self._programs = []
+            for parity in (0, 1):
+                steps = [(lflag, dst, src, nbytes, rflag, i)
+                         for i, (lflag, src, dst, nbytes, rflag) in enumerate(self.transport_program(parity))]
+                self._programs.append((_L.make_ce_program(steps), len(steps)))
 
     def transport_program(self, epoch: int):
         """The side streams' work for the call with this epoch (see ``rs_transport_program``)."""
-        elem = torch.empty((), dtype=self.dtype).element_size()
-        return rs_transport_program(self.rank, self.world, self.slab * self.N * elem, epoch, self.src_schedule,
-                                    self.remote_signals, self.send.data_ptr(), self.send_flags.data_ptr(),
-                                    self.stage.symm.ptrs, self.flags.symm.ptrs)
+        return rs_transport_program(self.rank, self.world, self.slab, self.N * self.dtype.itemsize, epoch,
+                                    self.src_schedule, self.remote_signals, self.send.data_ptr(),
+                                    self.send_flags.data_ptr(), self.stage.symm.ptrs, self.flags.symm.ptrs)
 
     def __call__(self, a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, stream=None):
         if out is None:
@@ -229,28 +276,32 @@ class GemmReduceScatter:
         if self.world == 1:
             return gemm(a, b, out, 1, self.num_sms, BLOCK_SIZE_N=self.block_n, status=self.ctx.status,
                         timeout_ns=self.timeout_ns, stream=stream)
-        if self.lockstep:
-            self.ctx.barrier(stream)
+        cur = stream or torch.cuda.current_stream()
         if self.comm == "ce":
-            cur = stream or torch.cuda.current_stream()
             # the kernel first (a launch that fails must not leave stream waits behind), then the
-            # transport: wait for the slab's local flag, copy, raise the target's flag
+            # transport: wait for the wave's local flag, copy its rows, raise the target's flag
+            side = self._copy_streams
+            self._ev_start.record(cur)
             gemm_rs(a, b, out, self.src_schedule, self.dst_schedule, self.remote_signals, self.stage.symm,
                     self.flags.symm, self.counters, epoch=self.epoch, num_sms=self.num_sms, block_n=self.block_n,
                     timeout_ns=self.timeout_ns, status=self.ctx.status, stream=cur, send_buf=self.send,
                     send_flags=self.send_flags)
-            lib = _raw_lib()
-            for i, (lflag, src, dst, nbytes, rflag) in enumerate(self.transport_program(self.epoch)):
-                sp = self._copy_streams[i % len(self._copy_streams)].cuda_stream
-                _L.check(lib.syn_flag_wait_stream(lflag, self.epoch, sp), "syn_flag_wait_stream")
-                _L.check(lib.syn_memcpy_async(dst, src, nbytes, sp), "syn_memcpy_async")
-                _L.check(lib.syn_flag_set(rflag, self.epoch, sp), "syn_flag_set")
-            for s in self._copy_streams:
+            side[0].wait_event(self._ev_start)
+            if self.lockstep:
+                self.ctx.barrier(side[0])
+            self._ev_go.record(side[0])
+            for s in side[1:]:
+                s.wait_event(self._ev_go)
+            program, n = self._programs[self.epoch & 1]
+            _L.ce_run(program, n, side, self.epoch)
+            for s in side:
                 cur.wait_stream(s)  # the next call's kernel may overwrite the send slabs
             return out
+        if self.lockstep:
+            self.ctx.barrier(cur)
         return gemm_rs(a, b, out, self.src_schedule, self.dst_schedule, self.remote_signals, self.stage.symm,
                        self.flags.symm, self.counters, epoch=self.epoch, num_sms=self.num_sms,
-                       block_n=self.block_n, timeout_ns=self.timeout_ns, status=self.ctx.status, stream=stream)
+                       block_n=self.block_n, timeout_ns=self.timeout_ns, status=self.ctx.status, stream=cur)
 
 
 # ----------------------------------------------------------------------------------------------
@@ -258,7 +309,6 @@ class GemmReduceScatter:
 # ----------------------------------------------------------------------------------------------
 import ctypes as _C
 
-from . import _lib as _L
 from .communication.common_descriptors import (
     build_all_to_all_plan_dim,
     build_double_ring_all_gather_plan,
@@ -296,9 +346,14 @@ class UlyssesAttention:
     tests/test_all2all_attn_transform.py:58-117); the outbound one is an SM copy kernel launched
     behind it (tests/test_attn_all2all_transform.py is the reference's overlapped form)."""
 
+    __doc__ += _HAZARD_NOTE + """
+    The symmetric input is ``qkv_src``; the symmetric output ``out`` is written by the peers: read it
+    after ``wait_output`` and before the next call starts."""
+
     def __init__(self, ctx, B: int, H: int, S_local: int, D: int = 128, dtype=torch.bfloat16, causal: bool = True,
-                 sm_scale: Optional[float] = None, timeout_ns: int = 0):
+                 sm_scale: Optional[float] = None, timeout_ns: int = 0, lockstep: bool = True, sync_after: bool = False):
         self.ctx, self.world, self.rank = ctx, ctx.world, ctx.rank
+        self.lockstep, self.sync_after = lockstep, sync_after
         W = self.world
         self.B, self.H, self.S_local, self.D, self.dtype, self.causal = B, H, S_local, D, dtype, causal
         self.sm_scale = sm_scale if sm_scale is not None else D ** -0.5
@@ -349,6 +404,8 @@ class UlyssesAttention:
     def launch_attention(self, stream=None):
         """Inbound all-to-all fused with attention; fills ``attn_out``."""
         self.epoch += 1
+        if self.lockstep and self.world > 1:
+            self.ctx.barrier(stream)  # every peer's qkv_src is written before anybody pulls from it
         offs, sizes, sigs, _cum = self.waves
         q, k, v = self.qkv_dst[0], self.qkv_dst[1], self.qkv_dst[2]
         attention_forward(q, k, v, self.sm_scale, self.attn_out.permute(0, 2, 1, 3), wave_offsets=offs,
@@ -373,6 +430,8 @@ class UlyssesAttention:
         self.launch_attention(stream)
         self.launch_scatter(stream)
         self.wait_output(stream)
+        if self.sync_after and self.world > 1:
+            self.ctx.barrier(stream)
         return self.out.local
 
 
@@ -384,10 +443,14 @@ class ContextParallelAttention:
     test_double_ring_ag_attn.py in the reference).  Causal masking uses true token positions, so the
     zigzag placement (rank r holds chunks r and 2 * world - 1 - r) balances the work."""
 
+    __doc__ += _HAZARD_NOTE + """
+    The symmetric input is ``kv_shard``."""
+
     def __init__(self, ctx, B: int, Hq: int, Hkv: int, S_local: int, D: int = 128, dtype=torch.bfloat16,
                  causal: bool = True, zigzag: bool = True, plan: str = "swizzle", inner_mesh_size: int = 2,
-                 sm_scale: Optional[float] = None, timeout_ns: int = 0):
+                 sm_scale: Optional[float] = None, timeout_ns: int = 0, lockstep: bool = True, sync_after: bool = False):
         self.ctx, self.world, self.rank = ctx, ctx.world, ctx.rank
+        self.lockstep, self.sync_after = lockstep, sync_after
         W = self.world
         self.B, self.Hq, self.Hkv, self.S_local, self.D = B, Hq, Hkv, S_local, D
         self.dtype, self.causal, self.timeout_ns = dtype, causal, timeout_ns
@@ -434,7 +497,12 @@ class ContextParallelAttention:
         self.epoch += 1
         offs, sizes, sigs, _cum = self.waves
         comm = self.comm if self.ops else None
-        return attention_forward(q, self.kv.local[0], self.kv.local[1], self.sm_scale, out, wave_offsets=offs,
-                                 wave_sizes=sizes, signal_ptr=self.flags.local, signal_offsets=sigs, causal=self.causal,
-                                 q_pos=self.q_pos, kv_pos=self.kv_pos, state=self.state, signal_value=self.epoch,
-                                 comm=comm, timeout_ns=self.timeout_ns, status=self.ctx.status, stream=stream)
+        if self.lockstep and self.world > 1 and comm is not None:
+            self.ctx.barrier(stream)  # every peer's K/V shard is written before anybody pulls from it
+        attention_forward(q, self.kv.local[0], self.kv.local[1], self.sm_scale, out, wave_offsets=offs,
+                          wave_sizes=sizes, signal_ptr=self.flags.local, signal_offsets=sigs, causal=self.causal,
+                          q_pos=self.q_pos, kv_pos=self.kv_pos, state=self.state, signal_value=self.epoch,
+                          comm=comm, timeout_ns=self.timeout_ns, status=self.ctx.status, stream=stream)
+        if self.sync_after and self.world > 1 and comm is not None:
+            self.ctx.barrier(stream)
+        return out

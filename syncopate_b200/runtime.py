@@ -54,10 +54,25 @@ class SymmetricTensor:
         self.local = self.peers[symm.rank]
 
 
+_CURRENT = None  # the context most recently opened in this process
+
+
+def current_context():
+    """The process's symmetric context: the one ``init_from_env`` (or the latest ``SymmetricContext``
+    constructor) opened.  Plays the role of the reference's process-wide NVSHMEM heap, which its
+    ``CommContext(rank, info)`` allocates from without being handed anything."""
+    if _CURRENT is None:
+        raise RuntimeError("no symmetric context is open in this process: call "
+                           "syncopate_b200.runtime.init_from_env() (one process per GPU) first")
+    return _CURRENT
+
+
 class SymmetricContext:
     """Owner of this rank's ``syn_ctx``."""
 
     def __init__(self, rank: int, world: int, device: Optional[int] = None, rendezvous_dir: Optional[str] = None):
+        global _CURRENT
+        _CURRENT = self
         self.rank, self.world = rank, world
         self.device_index = torch.cuda.current_device() if device is None else device
         self.device = torch.device("cuda", self.device_index)
@@ -96,8 +111,20 @@ class SymmetricContext:
             raise L.SynError(rc, "device status", f"wave={words[1]} flag={words[2]} block={words[3]}")
 
     def close(self) -> None:
+        """Collective: every rank calls it, after its last kernel that touches a peer has been
+        issued.  The ranks meet at a device barrier first, so that no rank unmaps or frees a buffer
+        that a peer's kernel may still be using."""
+        global _CURRENT
         if not self._closed:
             self._closed = True
+            if _CURRENT is self:
+                _CURRENT = None
+            if self.world > 1:
+                try:
+                    self.barrier()
+                    torch.cuda.synchronize(self.device)
+                except Exception:
+                    pass
             self._allocs.clear()
             L.lib().syn_ctx_destroy(self._handle)
             if self._dir and self.rank == 0:

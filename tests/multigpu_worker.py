@@ -37,11 +37,25 @@ def main():
     dt = torch.bfloat16
     failures = []
 
-    for kind, comm, rows, K, N in (("swizzle", "sm", 256, 512, 512), ("ring", "sm", 128, 256, 512),
-                                   ("swizzle", "ce", 256, 512, 512),
-                                   ("swizzle", "sm", 1024, 8192, 28672 // world),
-                                   ("swizzle", "ce", 1024, 8192, 28672 // world)):
-        op = AllGatherGemm(ctx, rows, K, N, dt, plan=kind, comm=comm, timeout_ns=2_000_000_000)
+    def tile_ok(x, ref):
+        """relative Frobenius error of the whole output and of its worst 128 x 256 tile"""
+        xf, rf = x.float(), ref.float()
+        M_, N_ = rf.shape
+        pm, pn = (-M_) % 128, (-N_) % 256
+        xp = torch.nn.functional.pad(xf, (0, pn, 0, pm))
+        rp = torch.nn.functional.pad(rf, (0, pn, 0, pm))
+        gm, gn = xp.shape[0] // 128, xp.shape[1] // 256
+        d = (xp - rp).reshape(gm, 128, gn, 256).permute(0, 2, 1, 3).reshape(gm, gn, -1)
+        r = rp.reshape(gm, 128, gn, 256).permute(0, 2, 1, 3).reshape(gm, gn, -1)
+        return rel(x, ref), (d.norm(dim=-1) / r.norm(dim=-1).clamp_min(1e-30)).max().item()
+
+    for kind, comm, rows, K, N, split in (("swizzle", "sm", 256, 512, 512, 1), ("ring", "sm", 128, 256, 512, 1),
+                                          ("swizzle", "ce", 256, 512, 512, 1), ("swizzle", "sm", 512, 512, 512, 2),
+                                          ("swizzle", "ce", 512, 256, 768, 4),
+                                          ("swizzle", "sm", 1024, 8192, 28672 // world, 1),
+                                          ("swizzle", "sm", 1024, 8192, 28672 // world, 2),
+                                          ("swizzle", "ce", 1024, 8192, 28672 // world, 2)):
+        op = AllGatherGemm(ctx, rows, K, N, dt, plan=kind, comm=comm, timeout_ns=2_000_000_000, chunk_split=split)
         shards = [seeded(1000 + r, (rows, K), 1.0, dt, dev) for r in range(world)]
         b = seeded(5000 + rank, (N, K), 0.02, dt, dev)
         full = torch.cat(shards, 0)
@@ -53,18 +67,43 @@ def main():
             ctx.barrier()
             c = op(b)
             ctx.check()
-            e = rel(c, ref)
+            e, et = tile_ok(c, ref)
             same = torch.equal(op.a.local, full)
-            if not (e < TOL and same):
-                failures.append(f"ag_gemm {kind}/{comm} rows={rows} it={it} rank={rank}: relerr={e:.3e} gathered_ok={same}")
+            if not (e < TOL and et < TOL and same):
+                failures.append(f"ag_gemm {kind}/{comm}/split{split} rows={rows} it={it} rank={rank}: relerr={e:.3e} "
+                                f"tile={et:.3e} gathered_ok={same}")
             ctx.barrier()  # nobody may overwrite its shard while a peer still pulls it
             torch.cuda.synchronize()
+        del op, ref
+
+    # the shard is rewritten before every call and nothing but the operator synchronises the ranks
+    # (leading barrier of every call + sync_after): each call must see the peers' new shards
+    for comm in ("sm", "ce"):
+        rows, K, N = 256, 512, 512
+        op = AllGatherGemm(ctx, rows, K, N, dt, comm=comm, timeout_ns=2_000_000_000, sync_after=True)
+        b = seeded(5100 + rank, (N, K), 0.02, dt, dev)
+        for it in range(6):
+            shards = [seeded(1200 + 10 * it + r, (rows, K), 1.0, dt, dev) for r in range(world)]
+            op.shard.copy_(shards[rank])
+            c = op(b)
+            full = torch.cat(shards, 0)
+            ctx.check()
+            e = rel(c, full.float() @ b.float().t())
+            same = torch.equal(op.a.local, full)
+            if not (e < TOL and same):
+                failures.append(f"ag_gemm rewrite-loop {comm} it={it} rank={rank}: relerr={e:.3e} gathered_ok={same}")
+        del op
 
     # comm "sm": the epilogue pushes tiles to the peers; "ce": local slabs moved by copy engines
-    for kind, M, N, Kl, comm in (("direct", 256 * world, 512, 256, "sm"), ("a2a", 128 * world, 1024, 512, "sm"),
-                                 ("direct", 8192, 8192, 28672 // world, "sm"), ("direct", 256 * world, 512, 256, "ce"),
-                                 ("a2a", 128 * world, 1024, 512, "ce")):
-        op = GemmReduceScatter(ctx, M, N, dt, plan=kind, timeout_ns=2_000_000_000, comm=comm)
+    for kind, M, N, Kl, comm, split in (("direct", 256 * world, 512, 256, "sm", 1), ("a2a", 128 * world, 1024, 512, "sm", 1),
+                                        ("direct", 8192, 8192, 28672 // world, "sm", 1),
+                                        ("direct", 256 * world, 512, 256, "ce", 1), ("a2a", 128 * world, 1024, 512, "ce", 1),
+                                        ("direct", 512 * world, 512, 256, "sm", 2), ("direct", 512 * world, 512, 256, "ce", 2),
+                                        ("direct", 8192, 8192, 28672 // world, "sm", 2),
+                                        ("direct", 8192, 8192, 28672 // world, "ce", 2)):
+        if split > 1 and (M // world) % (split * 128):
+            continue
+        op = GemmReduceScatter(ctx, M, N, dt, plan=kind, timeout_ns=2_000_000_000, comm=comm, chunk_split=split)
         a = seeded(2000 + rank, (M, Kl), 1.0, dt, dev)
         b = seeded(3000 + rank, (N, Kl), 0.02, dt, dev)
         part = a.float() @ b.float().t()
@@ -73,9 +112,10 @@ def main():
         for it in range(3):
             out = op(a, b)
             ctx.check()
-            e = rel(out, ref)
-            if not e < TOL:
-                failures.append(f"gemm_rs {kind}/{comm} M={M} it={it} rank={rank}: relerr={e:.3e}")
+            e, et = tile_ok(out, ref)
+            if not (e < TOL and et < TOL):
+                failures.append(f"gemm_rs {kind}/{comm}/split{split} M={M} it={it} rank={rank}: relerr={e:.3e} tile={et:.3e}")
+        del op, part, ref
 
     # ---- attention operators (reference: gather with torch.distributed, dense fp32 attention per head)
     def dense(q, k, v, causal, q_pos=None, k_pos=None):

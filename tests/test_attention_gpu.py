@@ -19,7 +19,8 @@ DT = torch.bfloat16
 @pytest.fixture(autouse=True, params=["one_tile", "two_tile"])
 def kernel_choice(request, monkeypatch):
     """Every test runs once with the one-tile kernel and once with the two-tile kernel forced
-    (the library would pick by problem size; the test shapes are small)."""
+    (the library would pick by problem size; the test shapes are small).  The benchmark-shape
+    tests at the end of the file run once, with the kernel the library picks for them."""
     monkeypatch.setenv("SYNCOPATE_B200_ATTN_TWO_TILE", "0" if request.param == "one_tile" else "2")
     return request.param
 
@@ -208,3 +209,125 @@ def test_context_parallel_operator_emulated_ranks(world, Hq, Hkv, plan, zigzag):
             k_pos = (op.kv_pos.cpu()[:, None] + steps[None, :]).reshape(-1) if op.kv_pos is not None else None
             want = _dense(q[r], full[0], full[1], True, q_pos, k_pos)
             assert (outs[r].float().cpu() - want).abs().max().item() < TOL
+
+
+# ----------------------------------------------------------------------------------------------
+# the shapes the benchmark times
+# ----------------------------------------------------------------------------------------------
+def _sampled_rows_error(out_h, q_h, k_h, v_h, rows, q_pos=None, k_pos=None):
+    """max-abs error of ``out_h[rows]`` (one head, [S, D]) against fp32 dense causal attention of those
+    query rows over all keys, computed on the device."""
+    qs = q_h[rows].float()
+    s = (qs @ k_h.float().t()) * (q_h.shape[-1] ** -0.5)
+    qp = rows if q_pos is None else q_pos[rows]
+    kp = torch.arange(k_h.shape[0], device=k_h.device) if k_pos is None else k_pos
+    s = s.masked_fill(kp[None, :] > qp[:, None], float("-inf"))
+    ref = torch.softmax(s, dim=-1) @ v_h.float()
+    return (out_h[rows].float() - ref).abs().max().item()
+
+
+def _sample_tiles(n_tiles: int, seed: int, extra: int = 3):
+    g = torch.Generator().manual_seed(seed)
+    picks = {0, 1, n_tiles // 2, n_tiles // 2 + 1, n_tiles - 2, n_tiles - 1}
+    picks.update(int(x) for x in torch.randint(0, n_tiles, (extra,), generator=g))
+    return sorted(picks)
+
+
+@pytest.mark.parametrize("kernel_choice", ["two_tile"], indirect=True)
+def test_cfg3_local_shape_sampled_rows(kernel_choice):
+    """The per-rank attention of the Ulysses benchmark (4 heads over the full 32768-token sequence,
+    causal, planned ownership: 256 key blocks per row, so the lazy rescale of O runs many times):
+    sampled query tiles of two heads against fp32 dense attention."""
+    from syncopate_b200.computation.attn import AttentionState, attention_forward
+
+    S, H = 32768, 4
+    g = torch.Generator(device="cuda").manual_seed(7000)
+    qkv = torch.randn(3, 1, H, S, 128, generator=g, device="cuda", dtype=torch.float32).to(DT)
+    out = torch.empty(1, H, S, 128, dtype=DT, device="cuda")
+    status = torch.zeros(4, dtype=torch.int32, device="cuda")
+    attention_forward(qkv[0], qkv[1], qkv[2], 128 ** -0.5, out, causal=True, state=AttentionState(1, H, S, "cuda"),
+                      status=status)
+    torch.cuda.synchronize()
+    assert status.tolist() == [0, 0, 0, 0]
+    worst = 0.0
+    for h in (0, 3):
+        for t in _sample_tiles(S // 128, 11 + h):
+            rows = torch.arange(t * 128, (t + 1) * 128, device="cuda")
+            worst = max(worst, _sampled_rows_error(out[0, h], qkv[0, 0, h], qkv[1, 0, h], qkv[2, 0, h], rows))
+    print(f"cfg3 local attention, sampled tiles: max-abs {worst:.2e}")
+    assert worst < TOL
+
+
+@pytest.mark.parametrize("kernel_choice", ["two_tile"], indirect=True)
+def test_cfg3_ulysses_world8_emulated_sampled_rows(kernel_choice):
+    """The Ulysses benchmark configuration itself on eight emulated ranks (32 heads, 4096 tokens per
+    rank): 64 (Q slab, KV slab) waves per rank gated by the in-kernel all-to-all, outbound copy,
+    and every rank's sampled output rows against fp32 dense attention over the full sequence."""
+    from syncopate_b200.operators import UlyssesAttention
+    from syncopate_b200.runtime import EmulatedWorld
+
+    W, H, Sl = 8, 32, 4096
+    ew = EmulatedWorld(W)
+    ops = [UlyssesAttention(c, 1, H, Sl, 128, DT, causal=True, timeout_ns=2_000_000_000) for c in ew.contexts]
+    g = torch.Generator(device="cuda").manual_seed(7100)
+    for op in ops:
+        op.qkv_src.local.copy_(torch.randn(3, 1, H, Sl, 128, generator=g, device="cuda", dtype=torch.float32).to(DT))
+    for op in ops:
+        op.launch_attention()
+    torch.cuda.synchronize()
+    for op in ops:
+        op.launch_scatter()
+    torch.cuda.synchronize()
+    full = torch.cat([op.qkv_src.local for op in ops], dim=3)  # [3, 1, H, S, D]
+    worst = 0.0
+    for r, op in enumerate(ops):
+        op.wait_output()
+        op.ctx.check()
+        got = op.out.local  # [1, S/W, H, D]
+        for h in (r, (r * 5 + 3) % H):
+            for t in _sample_tiles(Sl // 128, 100 + r, extra=1)[::2]:
+                rows = torch.arange(r * Sl + t * 128, r * Sl + (t + 1) * 128, device="cuda")
+                qs = full[0, 0, h, rows].float()
+                s = (qs @ full[1, 0, h].float().t()) * (128 ** -0.5)
+                s = s.masked_fill(torch.arange(W * Sl, device="cuda")[None, :] > rows[:, None], float("-inf"))
+                ref = torch.softmax(s, dim=-1) @ full[2, 0, h].float()
+                worst = max(worst, (got[0, t * 128 : (t + 1) * 128, h].float() - ref).abs().max().item())
+    print(f"cfg3 Ulysses on 8 emulated ranks, sampled tiles: max-abs {worst:.2e}")
+    assert worst < TOL
+
+
+@pytest.mark.parametrize("kernel_choice", ["two_tile"], indirect=True)
+def test_cfg4_rank0_sampled_rows(kernel_choice):
+    """Rank 0 of the context-parallel benchmark (64 query / 8 KV heads, 8192 local queries against
+    65536 keys, zigzag positions, eight waves gated by the in-kernel K/V gather from eight emulated
+    ranks): gathered K/V bit-exact, sampled query tiles against fp32 dense attention with the true
+    positions."""
+    from syncopate_b200.operators import ContextParallelAttention
+    from syncopate_b200.runtime import EmulatedWorld
+
+    W, Hq, Hkv, Sl = 8, 64, 8, 8192
+    ew = EmulatedWorld(W)
+    g = torch.Generator(device="cuda").manual_seed(8000)
+    ops = [ContextParallelAttention(c, 1, Hq, Hkv, Sl, 128, DT, causal=True, zigzag=True, plan="swizzle",
+                                    timeout_ns=2_000_000_000) for c in ew.contexts]
+    for op in ops:
+        op.kv.local.fill_(float("nan"))
+        op.kv_shard.copy_(torch.randn(2, 1, Hkv, Sl, 128, generator=g, device="cuda", dtype=torch.float32).to(DT))
+    q = torch.randn(1, Hq, Sl, 128, generator=g, device="cuda", dtype=torch.float32).to(DT)
+    op = ops[0]
+    out = op(q)
+    torch.cuda.synchronize()
+    op.ctx.check()
+    full = torch.cat([o.kv_shard for o in ops], dim=3)  # [2, 1, Hkv, S, D]
+    assert torch.equal(op.kv.local, full)
+    steps = torch.arange(128, device="cuda")
+    q_pos = (op.q_pos[:, None] + steps[None, :]).reshape(-1)
+    k_pos = (op.kv_pos[:, None] + steps[None, :]).reshape(-1)
+    worst = 0.0
+    for h in (0, 37, 63):
+        for t in _sample_tiles(Sl // 128, 200 + h, extra=2):
+            rows = torch.arange(t * 128, (t + 1) * 128, device="cuda")
+            worst = max(worst, _sampled_rows_error(out[0, h], q[0, h], full[0, 0, h // (Hq // Hkv)],
+                                                   full[1, 0, h // (Hq // Hkv)], rows, q_pos, k_pos))
+    print(f"cfg4 rank 0 (8 waves per row), sampled tiles: max-abs {worst:.2e}")
+    assert worst < TOL

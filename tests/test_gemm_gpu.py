@@ -1,7 +1,8 @@
 """GPU parity of the tcgen05 GEMM and of the fused operators, through the C ABI, against the CPU
 oracle (same seeded inputs).  Tolerance: relative Frobenius error <= 1e-2 for 16-bit outputs of an
-fp32-accumulated product (the bound the operators are specified to); the values seen are ~2e-3,
-i.e. output rounding."""
+fp32-accumulated product (the bound the operators are specified to), applied to the whole output
+AND to every 128 x 256 tile of it, plus an element-wise bound of a few output rounding steps
+(tests/parity.py); the values seen are ~2e-3, i.e. output rounding."""
 import os
 import sys
 
@@ -10,6 +11,7 @@ import torch
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 from oracle import emulate as E  # noqa: E402
+from parity import assert_gemm_close, gemm_errors  # noqa: E402
 
 pytestmark = pytest.mark.gpu
 TOL = 1e-2
@@ -50,7 +52,7 @@ def test_local_gemm_matches_oracle(M, N, K, bn, dtype, status):
     torch.cuda.synchronize()
     assert status.tolist() == [0, 0, 0, 0]
     ref = a.float() @ b.float().t()
-    assert _rel(c, ref) < TOL
+    assert_gemm_close(c, ref)
 
 
 def test_pair_kernel_with_split_tail(status):
@@ -67,7 +69,7 @@ def test_pair_kernel_with_split_tail(status):
         gemm(ad, bd, c, BLOCK_SIZE_N=256, status=status)
         torch.cuda.synchronize()
         assert status.tolist() == [0, 0, 0, 0]
-        assert _rel(c, ref) < TOL
+        assert_gemm_close(c, ref)
 
 
 def test_gemm_rejects_bad_arguments(status):
@@ -100,7 +102,7 @@ def test_wave_schedule_with_consumer_flags(status):
          signal_offsets=sched["signals"], status=status)
     torch.cuda.synchronize()
     assert status.tolist() == [0, 0, 0, 0]
-    assert _rel(c, a.float() @ b.float().t()) < TOL
+    assert_gemm_close(c, a.float() @ b.float().t())
 
 
 def test_flag_that_is_never_set_times_out_cleanly():
@@ -140,7 +142,7 @@ def test_producer_flags_are_raised_after_each_wave(status):
         torch.cuda.synchronize()
         assert flags.tolist() == [epoch, 0, epoch, epoch]
         assert int(counters.abs().sum()) == 0
-    assert _rel(c, a.float() @ b.float().t()) < TOL
+    assert_gemm_close(c, a.float() @ b.float().t())
 
 
 def _front_end(builder_kwargs, builder):
@@ -193,7 +195,7 @@ def test_fused_ag_gemm_emulated_ranks(world, rows, K, N, kind, status):
             assert status.tolist() == [0, 0, 0, 0]
             assert torch.equal(bufs[r].cpu(), o_gather)          # bytes moved: bit-exact
             assert torch.equal(bufs[r].cpu(), full)
-            assert _rel(c, o_c) < TOL
+            assert_gemm_close(c, o_c)
             assert flags.tolist() == [epoch] * info.recv_signal_num
             assert int(counters.abs().sum()) == 0
 
@@ -238,7 +240,7 @@ def test_fused_gemm_rs_emulated_ranks(world, M, N, Kl, kind, status):
                 torch.cuda.synchronize()
                 assert status.tolist() == [0, 0, 0, 0]
         for r in range(world):
-            assert _rel(outs[r], want[r]) < TOL
+            assert_gemm_close(outs[r], want[r])
             outs[r].zero_()
 
 
@@ -261,10 +263,148 @@ def test_full_size_cfg1_local_shape_against_fp32_reference(status):
     prev = torch.backends.cuda.matmul.allow_tf32
     torch.backends.cuda.matmul.allow_tf32 = False
     try:
-        err = 0.0
+        worst = [0.0, 0.0, 0.0]
         for r0 in range(0, M, 2048):  # fp32 reference in row blocks to bound memory
             ref = a[r0 : r0 + 2048].float() @ b.float().t()
-            err = max(err, ((c[r0 : r0 + 2048].float() - ref).norm() / ref.norm()).item())
+            glob, tile, maxabs, allowed = gemm_errors(c[r0 : r0 + 2048], ref)
+            worst = [max(worst[0], glob), max(worst[1], tile), max(worst[2], maxabs / allowed)]
     finally:
         torch.backends.cuda.matmul.allow_tf32 = prev
-    assert err < TOL
+    print(f"cfg1 local shape: relative Frobenius {worst[0]:.2e}, worst 128x256 tile {worst[1]:.2e}, "
+          f"max-abs / allowed {worst[2]:.2f}")
+    assert worst[0] < TOL and worst[1] < TOL and worst[2] <= 1.0
+
+
+def test_timed_out_launch_leaves_the_tail_workspace_usable(status):
+    """A launch that gives up on a flag (1 ms bound) on a shape whose left-over tiles are split
+    along K, then the same shape without the flag: every CTA of a split tile still arrives and
+    departs once on the give-up path, so the workspace counters rewind and the next launch is
+    exact."""
+    from syncopate_b200.computation.gemm import gemm
+
+    M, N, K = 4864, 1024, 2048
+    a, b = _seeded(7, (M, K), 1.0, torch.bfloat16).cuda(), _seeded(8, (N, K), 0.02, torch.bfloat16).cuda()
+    c = torch.zeros(M, N, dtype=torch.bfloat16, device="cuda")
+    flags = torch.zeros(1, dtype=torch.int64, device="cuda")
+    st = torch.zeros(4, dtype=torch.int32, device="cuda")
+    gemm(a, b, c, BLOCK_SIZE_N=256, cur_wave_sizes=[[M, N]], wave_offsets=[[0, 0]], signal_ptr=flags,
+         signal_offsets=[0], timeout_ns=1_000_000, status=st)
+    torch.cuda.synchronize()
+    assert st.tolist()[0] == 1           # the flag wait ran out
+    c.zero_()
+    gemm(a, b, c, BLOCK_SIZE_N=256, status=status)
+    torch.cuda.synchronize()
+    assert status.tolist() == [0, 0, 0, 0]
+    assert_gemm_close(c, a.float() @ b.float().t(), "after a timed-out launch")
+
+
+@pytest.mark.parametrize("world,rows,K,N,split,comm_pair", [(2, 512, 512, 768, 2, True), (4, 1024, 256, 512, 4, True),
+                                                            (2, 384, 256, 256, 3, False)])
+def test_fused_ag_gemm_with_split_chunks(world, rows, K, N, split, comm_pair, status):
+    """Every remote slab arrives as ``split`` row pieces with flags of their own; with 256-row pieces
+    the CTA-pair kernel runs with its comm warps, otherwise the one-CTA kernel."""
+    from syncopate_b200 import _lib as L
+    from syncopate_b200.computation.gemm import ag_gemm
+    from syncopate_b200.operators import plan_all_gather
+
+    dt = torch.bfloat16
+    _gen, info, low = plan_all_gather(world, rows, K, dt, "swizzle", chunk_split=split)
+    assert info.recv_signal_num == (world - 1) * split
+    shards = [_seeded(10 + r, (rows, K), 1.0, dt) for r in range(world)]
+    full = torch.cat(shards, 0)
+    bufs = []
+    for r in range(world):
+        buf = torch.full((world * rows, K), float("nan"), dtype=dt, device="cuda")
+        buf[r * rows : (r + 1) * rows] = shards[r].cuda()
+        bufs.append(buf)
+    for r in range(world):
+        b = _seeded(20 + r, (N, K), 0.02, dt)
+        sched = low[r]["a"]
+        assert len(sched.gen_signal_lists()) == 1 + (world - 1) * split
+        c = torch.zeros(world * rows, N, dtype=dt, device="cuda")
+        flags = torch.zeros(info.recv_signal_num, dtype=torch.int64, device="cuda")
+        counters = torch.zeros(130, dtype=torch.int32, device="cuda")
+        for epoch in (1, 2):
+            bufs[r][:] = float("nan")
+            bufs[r][r * rows : (r + 1) * rows] = shards[r].cuda()
+            ag_gemm(L.Symm.of(r, [x.data_ptr() for x in bufs]), bufs[r], b.cuda(), c, sched, flags, counters,
+                    epoch=epoch, timeout_ns=500_000_000, status=status)
+            torch.cuda.synchronize()
+            assert status.tolist() == [0, 0, 0, 0]
+            assert torch.equal(bufs[r].cpu(), full)              # bytes moved: bit-exact
+            assert_gemm_close(c, full.float() @ b.float().t())
+            assert flags.tolist() == [epoch] * info.recv_signal_num
+            assert int(counters.abs().sum()) == 0
+
+
+def _rs_phase_schedule(src, rsig, rank, own: bool):
+    cols = (src.gen_block_offset_lists(), src.gen_block_shape_lists(), src.gen_signal_lists(),
+            src.gen_target_rank_list(), src.gen_dst_offset_lists())
+    tgt = cols[3]
+    sel = [i for i in range(len(tgt)) if (tgt[i] < 0 or tgt[i] == rank) == own]
+    return tuple([col[i] for i in sel] for col in cols), [rsig[i] for i in sel], sel
+
+
+@pytest.mark.parametrize("world,M,N,Kl,split,transport", [(2, 1024, 512, 256, 2, "push"), (4, 2048, 256, 128, 2, "push"),
+                                                          (2, 1024, 512, 256, 2, "local"), (4, 1536, 256, 128, 3, "push")])
+def test_fused_gemm_rs_with_split_slabs(world, M, N, Kl, split, transport, status):
+    """Every slab leaves as ``split`` row pieces (flags of their own) and the rows kept by a rank are
+    reduced piece by piece.  ``push``: the epilogue's TMA stores write the peers' staging slabs;
+    ``local``: the epilogue fills the local send buffer and raises the local per-wave flags, and the
+    test plays the transport (copy the rows, raise the receiver's flag).  256-row pieces run on the
+    CTA-pair kernel, 128-row pieces on the one-CTA kernel."""
+    from syncopate_b200 import _lib as L
+    from syncopate_b200.computation.gemm import gemm_rs
+    from syncopate_b200.computation.gemm.plan import rs_remote_signals, rs_transport_program
+    from syncopate_b200.operators import plan_reduce_scatter
+
+    dt = torch.bfloat16
+    slab = M // world
+    _gen, info, low = plan_reduce_scatter(world, M, N, dt, "direct", chunk_split=split)
+    A = [_seeded(30 + r, (M, Kl), 1.0, dt) for r in range(world)]
+    B = [_seeded(40 + r, (N, Kl), 0.02, dt) for r in range(world)]
+    scheds = [{"offsets": low[r]["src"].gen_block_offset_lists(), "shapes": low[r]["src"].gen_block_shape_lists()}
+              for r in range(world)]
+    want = E.gemm_rs(scheds, A, B, out_dtype=torch.float32)
+    Ad, Bd = [x.cuda() for x in A], [x.cuda() for x in B]
+    stages = [torch.full((2, world, slab, N), float("nan"), dtype=dt, device="cuda") for _ in range(world)]
+    flags = [torch.zeros(max(info.recv_signal_num, 1), dtype=torch.int64, device="cuda") for _ in range(world)]
+    outs = [torch.zeros(slab, N, dtype=dt, device="cuda") for _ in range(world)]
+    counters = torch.zeros(130, dtype=torch.int32, device="cuda")
+    stage_symm = lambda r: L.Symm.of(r, [x.data_ptr() for x in stages])
+    flag_symm = lambda r: L.Symm.of(r, [x.data_ptr() for x in flags])
+    for epoch in (1, 2):
+        for own in (False, True):
+            for r in range(world):
+                src, dst = low[r]["src"], low[r]["dst"]
+                rsig = rs_remote_signals(info, r, src)
+                sched, sig_sel, sel = _rs_phase_schedule(src, rsig, r, own)
+                kw = {}
+                if transport == "local" and not own:
+                    send = torch.full((world, slab, N), float("nan"), dtype=dt, device="cuda")
+                    send_flags = torch.zeros(len(sel), dtype=torch.int64, device="cuda")
+                    kw = dict(send_buf=send, send_flags=send_flags)
+                gemm_rs(Ad[r], Bd[r], outs[r], sched, dst, sig_sel, stage_symm(r), flag_symm(r), counters, epoch=epoch,
+                        timeout_ns=500_000_000, status=status, **kw)
+                torch.cuda.synchronize()
+                assert status.tolist() == [0, 0, 0, 0]
+                assert int(counters.abs().sum()) == 0
+                if kw:
+                    assert send_flags.tolist() == [epoch] * len(sel)   # one local flag per wave
+                    # the transport program addresses waves by their index in the schedule it is given
+                    class _Sub:
+                        gen_block_offset_lists = staticmethod(lambda: sched[0])
+                        gen_block_shape_lists = staticmethod(lambda: sched[1])
+                        gen_target_rank_list = staticmethod(lambda: sched[3])
+                    prog = rs_transport_program(r, world, slab, N * 2, epoch, _Sub, sig_sel, send.data_ptr(),
+                                                send_flags.data_ptr(), [x.data_ptr() for x in stages],
+                                                [x.data_ptr() for x in flags])
+                    assert len(prog) == len(sel)
+                    for lflag, src_addr, dst_addr, nbytes, rflag in prog:
+                        t = next(i for i in range(world) if stages[i].data_ptr() <= dst_addr < stages[i].data_ptr() + stages[i].numel() * 2)
+                        so, do = (src_addr - send.data_ptr()) // 2, (dst_addr - stages[t].data_ptr()) // 2
+                        stages[t].view(-1)[do : do + nbytes // 2] = send.view(-1)[so : so + nbytes // 2]
+                        flags[t][(rflag - flags[t].data_ptr()) // 8] = epoch
+        for r in range(world):
+            assert_gemm_close(outs[r], want[r], f"rank {r} epoch {epoch}")
+            outs[r].zero_()

@@ -73,14 +73,15 @@ def _worker(rank, world, port, results):
         partial = torch.randn(M, Nn, generator=g2).to(dt)             # this rank's partial product
         BASE = 1 << 20                                                 # "address" of a rank's staging / flag arrays
         for epoch in (1, 2):
-            prog = rs_transport_program(rank, world, slab_bytes, epoch, rs_low[rank]["src"], sent,
+            prog = rs_transport_program(rank, world, slab, Nn * 2, epoch, rs_low[rank]["src"], sent,
                                         send_ptr=0, send_flags_ptr=0, stage_ptrs=[BASE * (t + 1) for t in range(world)],
                                         flag_ptrs=[BASE * (t + 1) for t in range(world)])
             assert len(prog) == world - 1
             moves = []
+            src_targets = rs_low[rank]["src"].gen_target_rank_list()
             for lflag, src_addr, dst_addr, nbytes, rflag in prog:
                 tgt = dst_addr // BASE - 1
-                assert lflag == 8 * tgt and src_addr == tgt * slab_bytes and nbytes == slab_bytes
+                assert lflag == 8 * src_targets.index(tgt) and src_addr == tgt * slab_bytes and nbytes == slab_bytes
                 slot = (dst_addr - BASE * (tgt + 1)) // slab_bytes
                 assert slot == (epoch & 1) * world + rank
                 moves.append((tgt, slot, (rflag - BASE * (tgt + 1)) // 8, partial[tgt * slab:(tgt + 1) * slab].clone()))
