@@ -7,7 +7,7 @@ here.  A fused kernel needs pieces that are still boxes, so that each piece lowe
 a flag of its own.  ``split_transfers_along_axis`` therefore cuts every push / pull of a plan into
 ``num_splits`` boxes along one axis (``BufferRegion.split(n, axis)``,
 syncopate/communication/descriptor.py:254-335) and keeps everything else (op kind, peer, reduce
-op, local copies, resident regions) as it is.  Call it on every rank's plan before
+op, what the transfer depends on, local copies, resident regions) as it is.  Call it on every rank's plan before
 ``CommGenerator.plan_signals``: smaller chunks raise their flags earlier, which shortens the
 non-overlapped head and tail of a fused operator at the price of more flags and waves.
 """
@@ -33,7 +33,7 @@ def split_transfers_along_axis(plan: DevicePlan, num_splits: int, axis: int = 0)
                 continue
             if op.src_region is None or op.dst_region is None:
                 raise ValueError("cannot split a transfer with dynamic regions")
-            if op.dependency or op.set_signals:
+            if op.set_signals:
                 raise ValueError("split the plan before signals are planned")
             src_parts = op.src_region.split(num_splits, axis)
             dst_parts = op.dst_region.split(num_splits, axis)
@@ -41,7 +41,8 @@ def split_transfers_along_axis(plan: DevicePlan, num_splits: int, axis: int = 0)
                 raise ValueError("source and destination splits differ in count")
             for i, (src, dst) in enumerate(zip(src_parts, dst_parts)):
                 out.append(Transfer(op=op.op, src_buf=op.src_buf, src_region=src, dst_buf=op.dst_buf, dst_region=dst,
-                                    chunk_idx=op.chunk_idx * num_splits + i, peer=op.peer, reduce_op=op.reduce_op))
+                                    chunk_idx=op.chunk_idx * num_splits + i, peer=op.peer, reduce_op=op.reduce_op,
+                                    dependency=copy.deepcopy(op.dependency)))
         streams.append(out)
     return DevicePlan(dev=plan.dev, xfer=streams, local_regions=copy.deepcopy(plan.local_regions),
                       transit_signals=copy.deepcopy(plan.transit_signals),

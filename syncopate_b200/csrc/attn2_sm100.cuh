@@ -111,7 +111,8 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
   uint64_t* o_empty = bars + 20;      // [2] per tile, softmax -> MMA, once per unit
   uint64_t* turn = bars + 22;         // [2] per tile: its softmax warpgroup may exponentiate
   uint64_t* comm_bar = bars + 24;     // [COMM_NBUF]
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 24 + COMM_NBUF);
+  uint64_t* done_bar = bars + 24 + COMM_NBUF;  // [2] per issuing warp: its products have completed (give-up path)
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 26 + COMM_NBUF);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_holder + 1);
   int* abort_info = const_cast<int*>(abort_word) + 1;
 
@@ -132,6 +133,8 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
       mbar_init(&turn[i], 128);
     }
     for (int i = 0; i < COMM_NBUF; ++i) mbar_init(&comm_bar[i], 1);
+    mbar_init(&done_bar[0], 1);
+    mbar_init(&done_bar[1], 1);
     *abort_word = 0;
     abort_info[0] = -1;
     abort_info[1] = -1;
@@ -262,6 +265,15 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
       const uint32_t s_tmem = tmem_base + static_cast<uint32_t>(x) * 128u;  // S_x, then P_x
       const uint32_t o_tmem = tmem_base + 256u + static_cast<uint32_t>(x) * 128u;
       const uint32_t idesc_qk = p.idesc_qk, idesc_pv = p.idesc_pv;
+      // A wait that fails (the CTA gave up somewhere) ends this role at once: nothing more is
+      // issued on operands that never arrived.  All 32 lanes poll the same barrier, abort word and
+      // timer in the same instructions, so the verdict is the same in every lane (the
+      // elected-lane instructions below need the whole warp).
+      bool ok = true;
+      auto wait = [&](uint64_t* bar, uint32_t parity) -> bool {
+        if (ok) ok = mbar_wait(bar, parity, abort_word, timeout_ns);
+        return ok;
+      };
       // S_x = Q_x K^T for the block in K stage `st`
       auto issue_qk = [&](int st) {
         const uint32_t b0 = k_lo + static_cast<uint32_t>(st) * TILE_UNITS;
@@ -298,7 +310,7 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
           }
         }
       };
-      while (cur.next(p, z, h, un)) {
+      while (ok && cur.next(p, z, h, un)) {
         if (*abort_word != 0) break;
         const AttnWave& w = p.waves[cur.wave];
         const TileRole tr[2] = {tile_role(p, w, 2 * un), tile_role(p, w, 2 * un + 1)};
@@ -308,7 +320,7 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
           act[1] += tile_mode(p, tr[1], kb) != 0;
         }
         if (act[0] + act[1] == 0) continue;
-        if (act[x]) mbar_wait(&q_full[x], uqx & 1u, abort_word, timeout_ns);
+        if (act[x] && !wait(&q_full[x], uqx & 1u)) break;
         int m[2], n[2];
         int kb = next_shared_block(p, w, tr[0], tr[1], w.kb0, m[0], m[1]);
         // the unit's first block
@@ -316,7 +328,7 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
           const int st = g % ATTN_KV_STAGES;
           // (a warp whose tile skips the block still waits for the stage to be full before it
           // releases it: otherwise it could run ahead and arrive twice in one phase)
-          mbar_wait(&k_full[st], (g / ATTN_KV_STAGES) & 1u, abort_word, timeout_ns);
+          if (!wait(&k_full[st], (g / ATTN_KV_STAGES) & 1u)) break;
           if (m[x]) {
             tc_fence_after();
             issue_qk(st);
@@ -324,23 +336,21 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
           release(&k_empty[st], m[x] != 0);
         }
         bool started = false;
-        while (kb >= 0) {
+        while (ok && kb >= 0) {
           const int kn = next_shared_block(p, w, tr[0], tr[1], kb + 1, n[0], n[1]);
           const int st = g % ATTN_KV_STAGES, st_n = (g + 1) % ATTN_KV_STAGES;
           const uint32_t par = (g / ATTN_KV_STAGES) & 1u, par_n = ((g + 1) / ATTN_KV_STAGES) & 1u;
           if (m[x]) {
-            mbar_wait(&p_full[2 * x], cbx & 1u, abort_word, timeout_ns);
-            if (!started) {
-              // the first product of a unit overwrites O_x: the previous unit's result must have been read
-              mbar_wait(&o_empty[x], (uqx & 1u) ^ 1u, abort_word, timeout_ns);
-            }
-            mbar_wait(&v_full[st], par, abort_word, timeout_ns);
+            if (!wait(&p_full[2 * x], cbx & 1u)) break;
+            // the first product of a unit overwrites O_x: the previous unit's result must have been read
+            if (!started && !wait(&o_empty[x], (uqx & 1u) ^ 1u)) break;
+            if (!wait(&v_full[st], par)) break;
             tc_fence_after();
             issue_pv(st, 0, started);
             // the next K block has long landed; looking now keeps this wait off the path from the
             // second half of P to the next S
-            if (kn >= 0) mbar_wait(&k_full[st_n], par_n, abort_word, timeout_ns);
-            mbar_wait(&p_full[2 * x + 1], cbx & 1u, abort_word, timeout_ns);
+            if (kn >= 0 && !wait(&k_full[st_n], par_n)) break;
+            if (!wait(&p_full[2 * x + 1], cbx & 1u)) break;
             tc_fence_after();
             issue_pv(st, 1, true);
             ++cbx;
@@ -352,10 +362,10 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
             release(&v_empty[st], true);
             if (kn >= 0) release(&k_empty[st_n], n[x] != 0);
           } else {
-            mbar_wait(&v_full[st], par, abort_word, timeout_ns);
+            if (!wait(&v_full[st], par)) break;
             release(&v_empty[st], false);
             if (kn >= 0) {
-              mbar_wait(&k_full[st_n], par_n, abort_word, timeout_ns);
+              if (!wait(&k_full[st_n], par_n)) break;
               if (n[x]) {
                 tc_fence_after();
                 issue_qk(st_n);
@@ -368,6 +378,7 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
           m[1] = n[1];
           ++g;
         }
+        if (!ok) break;
         if (act[x]) {
           if (elect_one()) {
             umma_commit(&o_full[x]);
@@ -375,6 +386,12 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
           }
           ++uqx;
         }
+      }
+      if (__any_sync(0xffffffffu, *abort_word != 0)) {
+        // products already issued still use shared and tensor memory: wait (bounded) until they
+        // have completed before the CTA gives both back
+        if (elect_one()) umma_commit(&done_bar[x]);
+        drain_wait(&done_bar[x], 0, timeout_ns);
       }
     }
   } else if (warp == 3) {
@@ -398,7 +415,15 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
     uint32_t cbx = 0;  // key blocks this tile has processed (S / P barrier parity)
     uint32_t ux = 0;   // units this tile has taken part in
     uint32_t turns = 0;  // blocks both tiles have worked on (parity of the turn barriers)
-    while (cur.next(p, z, h, un)) {
+    // a wait that fails ends this role at once (the same verdict in every lane of a warp, which
+    // polls in the same instructions; the tensor-memory instructions below are warp-wide);
+    // nothing is stored for a unit that was not finished
+    bool ok = true;
+    auto wait = [&](uint64_t* bar, uint32_t parity) -> bool {
+      if (ok) ok = mbar_wait(bar, parity, abort_word, p.timeout_ns);
+      return ok;
+    };
+    while (ok && cur.next(p, z, h, un)) {
       if (*abort_word != 0) break;
       const AttnWave& w = p.waves[cur.wave];
       const TileRole t = tile_role(p, w, 2 * un + x), other = tile_role(p, w, 2 * un + (x ^ 1));
@@ -419,7 +444,7 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
           const int kpos0 = p.kv_pos ? __ldg(p.kv_pos + kb) : kb * ATTN_BN;
           lim = min(ATTN_BN - 1, qpos0 + row - kpos0);
         }
-        mbar_wait(&s_full[x], cbx & 1u, abort_word, p.timeout_ns);
+        if (!wait(&s_full[x], cbx & 1u)) break;
         ++cbx;
         tc_fence_after();
         uint32_t sr[ATTN_BN / 32][32];
@@ -470,7 +495,7 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
         // work on): the special-function unit serves one of them at full rate instead of both at
         // half, and the tiles settle half a period apart, so that one tile's products run on the
         // tensor pipe during the other tile's softmax.
-        if (both) mbar_wait(&turn[x], x == 0 ? ((turns & 1u) ^ 1u) : (turns & 1u), abort_word, p.timeout_ns);
+        if (both && !wait(&turn[x], x == 0 ? ((turns & 1u) ^ 1u) : (turns & 1u))) break;
         const uint64_t scale2 = f2_pack(p.scale_log2, p.scale_log2), negm2 = f2_pack(neg_m, neg_m);
         uint64_t ls2[2] = {0ull, 0ull};  // packed (0.f, 0.f)
 #pragma unroll
@@ -513,8 +538,9 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
         }
         ++j;
       }
+      if (!ok) break;
       // the unit's last product into O_x
-      mbar_wait(&o_full[x], ux & 1u, abort_word, p.timeout_ns);
+      if (!wait(&o_full[x], ux & 1u)) break;
       tc_fence_after();
 
       attn_finish_row<BF16>(p, z, h, qt, row, m, l, o_tmem);

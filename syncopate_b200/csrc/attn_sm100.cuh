@@ -254,7 +254,8 @@ __global__ void __launch_bounds__(256, 1) attn_kernel(const __grid_constant__ At
   uint64_t* o_full = bars + 16;       // [2] MMA -> softmax
   uint64_t* o_empty = bars + 18;      // [2] softmax -> MMA
   uint64_t* comm_bar = bars + 20;     // [COMM_NBUF]
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 20 + COMM_NBUF);
+  uint64_t* done_bar = bars + 20 + COMM_NBUF;  // the issuing warp's products have completed (give-up path)
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 21 + COMM_NBUF);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_holder + 1);
   int* abort_info = const_cast<int*>(abort_word) + 1;
 
@@ -273,6 +274,7 @@ __global__ void __launch_bounds__(256, 1) attn_kernel(const __grid_constant__ At
       mbar_init(&o_empty[i], 128);
     }
     for (int i = 0; i < COMM_NBUF; ++i) mbar_init(&comm_bar[i], 1);
+    mbar_init(done_bar, 1);
     *abort_word = 0;
     abort_info[0] = -1;
     abort_info[1] = -1;
@@ -376,9 +378,18 @@ __global__ void __launch_bounds__(256, 1) attn_kernel(const __grid_constant__ At
       const uint32_t v_lo = static_cast<uint32_t>(make_smem_desc_sw128(smem_u32(sV), ATTN_TILE_BYTES / 2, 1024));
       const uint32_t idesc_qk = p.idesc_qk, idesc_pv = p.idesc_pv;
       const uint64_t timeout_ns = p.timeout_ns;
+      // A wait that fails (the CTA gave up somewhere) ends this role at once: nothing more is
+      // issued on operands that never arrived.  All 32 lanes poll the same barrier, abort word and
+      // timer in the same instructions, so the verdict is the same in every lane (the
+      // elected-lane instructions below need the whole warp).
+      bool ok = true;
+      auto wait = [&](uint64_t* bar, uint32_t parity) -> bool {
+        if (ok) ok = mbar_wait(bar, parity, abort_word, timeout_ns);
+        return ok;
+      };
       auto issue_qk = [&](uint32_t gi, int qb) {
         const int st = gi % ATTN_KV_STAGES;
-        mbar_wait(&k_full[st], (gi / ATTN_KV_STAGES) & 1u, abort_word, timeout_ns);
+        if (!wait(&k_full[st], (gi / ATTN_KV_STAGES) & 1u)) return;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (gi & 1u) * 128u;
         const uint32_t a0 = q_lo + static_cast<uint32_t>(qb) * TILE_UNITS;
@@ -394,7 +405,7 @@ __global__ void __launch_bounds__(256, 1) attn_kernel(const __grid_constant__ At
           umma_commit(&s_full[gi & 1u]);
         }
       };
-      while (cur.next(p, z, h, qt)) {
+      while (ok && cur.next(p, z, h, qt)) {
         if (*abort_word != 0) break;
         const AttnWave& w = p.waves[cur.wave];
         const int qpos0 = p.q_pos ? __ldg(p.q_pos + qt) : qt * ATTN_BM;
@@ -402,19 +413,17 @@ __global__ void __launch_bounds__(256, 1) attn_kernel(const __grid_constant__ At
         for (int kb = w.kb0; kb < w.kb1; ++kb) active += block_mode(p, qpos0, kb) != 0;
         if (active == 0) continue;
         const int qb = u & 1;
-        mbar_wait(&q_full[qb], (u >> 1) & 1u, abort_word, timeout_ns);
+        if (!wait(&q_full[qb], (u >> 1) & 1u)) break;
         issue_qk(g, qb);
-        for (int j = 0; j < active; ++j) {
+        for (int j = 0; ok && j < active; ++j) {
           const uint32_t gi = g + j;
           if (j + 1 < active) issue_qk(gi + 1, qb);
           // P_j is in tensor memory (and O has been rescaled if the row maximum jumped)
-          mbar_wait(&p_full[gi & 1u], (gi >> 1) & 1u, abort_word, timeout_ns);
-          if (j == 0) {
-            // the first product of a unit overwrites O: the previous unit's result must have been read
-            mbar_wait(&o_empty[0], (u & 1u) ^ 1u, abort_word, timeout_ns);
-          }
+          if (!wait(&p_full[gi & 1u], (gi >> 1) & 1u)) break;
+          // the first product of a unit overwrites O: the previous unit's result must have been read
+          if (j == 0 && !wait(&o_empty[0], (u & 1u) ^ 1u)) break;
           const int st = gi % ATTN_KV_STAGES;
-          mbar_wait(&v_full[st], (gi / ATTN_KV_STAGES) & 1u, abort_word, timeout_ns);
+          if (!wait(&v_full[st], (gi / ATTN_KV_STAGES) & 1u)) break;
           tc_fence_after();
           const uint32_t p_tmem = tmem_base + (gi & 1u) * 128u;  // bf16 pairs over the first 64 columns of S
           const uint32_t o_tmem = tmem_base + 256u;
@@ -432,9 +441,16 @@ __global__ void __launch_bounds__(256, 1) attn_kernel(const __grid_constant__ At
             umma_commit(&o_full[gi & 1u]);
           }
         }
+        if (!ok) break;
         if (elect_one()) umma_commit(&q_empty[qb]);
         g += active;
         ++u;
+      }
+      if (__any_sync(0xffffffffu, *abort_word != 0)) {
+        // products already issued still use shared and tensor memory: wait (bounded) until they
+        // have completed before the CTA gives both back
+        if (elect_one()) umma_commit(done_bar);
+        drain_wait(done_bar, 0, timeout_ns);
       }
     }
   } else if (warp == 3) {
@@ -451,7 +467,15 @@ __global__ void __launch_bounds__(256, 1) attn_kernel(const __grid_constant__ At
     int z, h, qt;
     uint32_t g = 0;
     uint32_t u = 0;  // units processed (parity of the O hand-over barrier)
-    while (cur.next(p, z, h, qt)) {
+    // a wait that fails ends this role at once (the same verdict in every lane of a warp, which
+    // polls in the same instructions; the tensor-memory instructions below are warp-wide);
+    // nothing is stored for a unit that was not finished
+    bool ok = true;
+    auto wait = [&](uint64_t* bar, uint32_t parity) -> bool {
+      if (ok) ok = mbar_wait(bar, parity, abort_word, p.timeout_ns);
+      return ok;
+    };
+    while (ok && cur.next(p, z, h, qt)) {
       const AttnWave& w = p.waves[cur.wave];
       const int qpos0 = p.q_pos ? __ldg(p.q_pos + qt) : qt * ATTN_BM;
       int active = 0;
@@ -472,7 +496,7 @@ __global__ void __launch_bounds__(256, 1) attn_kernel(const __grid_constant__ At
           const int kpos0 = p.kv_pos ? __ldg(p.kv_pos + kb) : kb * ATTN_BN;
           lim = min(ATTN_BN - 1, qpos0 + row - kpos0);
         }
-        mbar_wait(&s_full[gi & 1u], (gi >> 1) & 1u, abort_word, p.timeout_ns);
+        if (!wait(&s_full[gi & 1u], (gi >> 1) & 1u)) break;
         tc_fence_after();
         // all of S for this row in one go: four loads in flight, one wait
         uint32_t sr[ATTN_BN / 32][32];
@@ -538,10 +562,11 @@ __global__ void __launch_bounds__(256, 1) attn_kernel(const __grid_constant__ At
         mbar_arrive(&p_full[gi & 1u]);
         ++j;
       }
+      if (!ok) break;
       // the unit's last product
       {
         const uint32_t gp = g + active - 1;
-        mbar_wait(&o_full[gp & 1u], (gp >> 1) & 1u, abort_word, p.timeout_ns);
+        if (!wait(&o_full[gp & 1u], (gp >> 1) & 1u)) break;
         tc_fence_after();
       }
       g += active;
