@@ -315,6 +315,28 @@ def run_own_arm(args):
         return {"ms": statistics.median(per_block), "ms_min": min(per_block), "ms_max": max(per_block),
                 "blocks": n_blocks, "steps_per_block": n_steps}
 
+    def capture_trace(operator, call, rows, signals):
+        """Runs ``call`` three times with the kernel's wait stamps switched on and returns the last
+        call's per-wave rows and the kernel's duration (us)."""
+        nw = len(rows)
+        big = torch.iinfo(torch.int64).max
+        tr = None
+        for _ in range(3):
+            tr = torch.zeros(2 + 3 * nw, dtype=torch.int64, device=dev)
+            tr[0] = big
+            tr[2::3] = big
+            operator.trace = tr
+            sync_all()
+            call()
+            torch.cuda.synchronize()
+        operator.trace = None
+        t = tr.tolist()
+        out = [{"wave": w, "rows": rows[w], "flag": signals[w],
+                "wait_begin_us": (t[2 + 3 * w] - t[0]) / 1e3 if t[2 + 3 * w] != big else None,
+                "wait_end_us": (t[3 + 3 * w] - t[0]) / 1e3 if t[3 + 3 * w] else None,
+                "summed_wait_us": t[4 + 3 * w] / 1e3} for w in range(nw)]
+        return out, (t[1] - t[0]) / 1e3
+
     sampler = ClockSampler(ctx.device_index)
     if rank == 0:
         sampler.start()
@@ -383,23 +405,7 @@ def run_own_arm(args):
         compute_only = timed(lambda: gemm(op.a.local, b, c, cur_wave_sizes=sizes, wave_offsets=offs, signal_ptr=ones,
                                           signal_offsets=sigs, status=ctx.status), n_blocks=max(3, blocks // 2), n_warm=3)
         # per-wave flag waits of one call (kernel time stamps): where the non-overlapped time sits
-        nw = len(sigs)
-        big = torch.iinfo(torch.int64).max
-        for _ in range(3):
-            tr = torch.zeros(2 + 3 * nw, dtype=torch.int64, device=dev)
-            tr[0] = big
-            tr[2::3] = big
-            op.trace = tr
-            sync_all()
-            step()
-            torch.cuda.synchronize()
-        op.trace = None
-        t = tr.tolist()
-        trace_rows = [{"wave": w, "rows": sizes[w][0], "flag": sigs[w],
-                       "wait_begin_us": (t[2 + 3 * w] - t[0]) / 1e3 if t[2 + 3 * w] != big else None,
-                       "wait_end_us": (t[3 + 3 * w] - t[0]) / 1e3 if t[3 + 3 * w] else None,
-                       "summed_wait_us": t[4 + 3 * w] / 1e3} for w in range(nw)]
-        kernel_us = (t[1] - t[0]) / 1e3
+        trace_rows, kernel_us = capture_trace(op, step, [s_[0] for s_ in sizes], sigs)
         # the other transport, for the record
         alt = "sm" if args.comm == "ce" else "ce"
         if not args.skip_alt_comm:
@@ -489,6 +495,7 @@ def run_own_arm(args):
     rb = seeded(3000 + rank, (RS_N, rs_k), 0.02, dt).to(dev)
     rs_other = None
     rs_compute_only = None
+    rs_trace_rows = None
     if world > 1:
         rs = GemmReduceScatter(ctx, RS_M, RS_N, dt, plan="direct", comm=args.rs_comm, chunk_split=args.rs_split,
                                copy_streams=args.copy_streams)
@@ -504,6 +511,13 @@ def run_own_arm(args):
         glob, tile = gemm_parity(rout, ref_slab)
         parity["gemm_rs"] = {"rel_frobenius": glob, "worst_tile_rel_frobenius": tile, "tol": GEMM_TOL}
         del ref_slab
+        # the kernel walks the remote waves of the plan, then the locally kept slab cut into its row pieces
+        rs_rows = [s_[0] for s_, t_ in zip(rs.src_schedule.gen_block_shape_lists(), rs.src_schedule.gen_target_rank_list())
+                   if t_ >= 0 and t_ != rank]
+        own_pieces = max(args.rs_split, 1)
+        rs_rows += [RS_M // world // own_pieces] * own_pieces
+        rs_trace_rows, rs_kernel_us = capture_trace(rs, lambda: rs(ra, rb, rout), rs_rows,
+                                                    ["remote"] * (len(rs_rows) - own_pieces) + ["reduce"] * own_pieces)
         rfull = torch.empty(RS_M, RS_N, dtype=dt, device=dev)
         rs_compute_only = timed(lambda: gemm(ra, rb, rfull, status=ctx.status), n_blocks=max(3, blocks // 2), n_warm=3)
         del rfull
@@ -704,6 +718,10 @@ def run_own_arm(args):
                                      "note": "one call of the headline operator on rank 0: per wave, earliest flag-wait "
                                              "begin and latest end over CTAs (us from the kernel's start) and the wait "
                                              "summed over CTAs"}
+        if rs_trace_rows is not None:
+            line["other_ops"]["gemm_rs"]["overlap_trace"] = {
+                "kernel_us": rs_kernel_us, "waves": rs_trace_rows,
+                "note": "one call on rank 0: the reduce waves' waits for the staged partial sums of their rows"}
         if cpu_val is not None:
             line["cpu_baseline"] = {"value": cpu_val, "unit": "TFLOP/s", "cores": cores, "kind": "port",
                                     "sample": sample}

@@ -103,7 +103,9 @@ typedef struct syn_gemm_args {
   /* Optional device uint64[2 + 3 * num_waves] of %globaltimer stamps (ns) for the non-overlapped-time
    * breakdown: [0] earliest CTA start (initialise to UINT64_MAX), [1] latest CTA end (0); per wave w:
    * [2+3w] earliest flag-wait begin (UINT64_MAX), [3+3w] latest flag-wait end (0), [4+3w] summed wait
-   * over CTAs (0). */
+   * over CTAs (0).  A wave waits either for its consumer flag (before its first load) or, in GEMM +
+   * reduce-scatter, for the flags of the staged partial sums it adds (w then counts the waves the
+   * kernel walks: those of src_sched with the locally kept one cut into its row pieces). */
   uint64_t* trace;
   /* Optional device scratch, 256-byte aligned, its first 256 bytes zero before the first call (every
    * call leaves them zero): lets the CTA-pair kernel cut the few tiles left over after the last full

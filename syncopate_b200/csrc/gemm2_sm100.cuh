@@ -378,6 +378,8 @@ gemm2_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUten
               __syncwarp();
             }
             if (reduce) {
+              // the staged partial sums of this wave's rows: one flag per contributing rank
+              const unsigned long long t_wait0 = p.trace != nullptr ? globaltimer_ns() : 0ull;
               if (lane < p.num_red) {
                 if (!flag_wait_ge(p.red_flags + rt.red_sig[lane], p.signal_value, abort_word, p.timeout_ns)) {
                   abort_info[0] = cur.wave;
@@ -385,6 +387,12 @@ gemm2_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUten
                 }
               }
               __syncwarp();
+              if (p.trace != nullptr && q == 0 && lane == 0) {
+                const unsigned long long t_wait1 = globaltimer_ns();
+                atomicMin(&p.trace[2 + 3 * cur.wave], t_wait0);
+                atomicMax(&p.trace[3 + 3 * cur.wave], t_wait1);
+                atomicAdd(&p.trace[4 + 3 * cur.wave], t_wait1 - t_wait0);
+              }
             }
           }
         }

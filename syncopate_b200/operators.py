@@ -241,6 +241,7 @@ class GemmReduceScatter:
         self.slab = M // self.world
         self.num_sms, self.block_n, self.timeout_ns = num_sms, block_n, timeout_ns
         self.epoch = 0
+        self.trace = None  # optional uint64 stamp buffer (see syn_gemm_args.trace): waits of the reduce waves
         if self.world == 1:
             return
         self.generator, self.info, lowered = plan_reduce_scatter(self.world, M, N, dtype, plan, chunk_split)
@@ -285,7 +286,7 @@ class GemmReduceScatter:
             gemm_rs(a, b, out, self.src_schedule, self.dst_schedule, self.remote_signals, self.stage.symm,
                     self.flags.symm, self.counters, epoch=self.epoch, num_sms=self.num_sms, block_n=self.block_n,
                     timeout_ns=self.timeout_ns, status=self.ctx.status, stream=cur, send_buf=self.send,
-                    send_flags=self.send_flags)
+                    send_flags=self.send_flags, trace=self.trace)
             side[0].wait_event(self._ev_start)
             if self.lockstep:
                 self.ctx.barrier(side[0])
@@ -301,7 +302,8 @@ class GemmReduceScatter:
             self.ctx.barrier(cur)
         return gemm_rs(a, b, out, self.src_schedule, self.dst_schedule, self.remote_signals, self.stage.symm,
                        self.flags.symm, self.counters, epoch=self.epoch, num_sms=self.num_sms,
-                       block_n=self.block_n, timeout_ns=self.timeout_ns, status=self.ctx.status, stream=cur)
+                       block_n=self.block_n, timeout_ns=self.timeout_ns, status=self.ctx.status, stream=cur,
+                       trace=self.trace)
 
 
 # ----------------------------------------------------------------------------------------------
