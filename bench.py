@@ -496,6 +496,8 @@ def run_own_arm(args):
     rs_other = None
     rs_compute_only = None
     rs_trace_rows = None
+    ar_result = None
+    rs_bytes_per_rank = (world - 1) * (RS_M // world) * RS_N * 2 if world > 1 else 0
     if world > 1:
         rs = GemmReduceScatter(ctx, RS_M, RS_N, dt, plan="direct", comm=args.rs_comm, chunk_split=args.rs_split,
                                copy_streams=args.copy_streams)
@@ -521,6 +523,30 @@ def run_own_arm(args):
         rfull = torch.empty(RS_M, RS_N, dtype=dt, device=dev)
         rs_compute_only = timed(lambda: gemm(ra, rb, rfull, status=ctx.status), n_blocks=max(3, blocks // 2), n_warm=3)
         del rfull
+        # GEMM + all-reduce on the same shape: reduce-scatter in the kernel + all-gather of the reduced rows
+        from syncopate_b200.operators import GemmAllReduce
+
+        ar = GemmAllReduce(ctx, RS_M, RS_N, dt, num_splits=args.ar_splits, chunk_split=1, comm=args.rs_comm,
+                           copy_streams=args.copy_streams, sync_after=True)
+        ar_t = timed(lambda: ar(ra, rb), n_blocks=max(3, blocks // 2), n_warm=3)
+        ar_ref = torch.empty(RS_M, RS_N, dtype=torch.float32, device=dev)
+        for r0, blk in matmul_blocks(ra, rb):
+            ar_ref[r0:r0 + blk.shape[0]] = blk
+        dist.all_reduce(ar_ref)
+        glob, tile = gemm_parity(ar.out.local, ar_ref)
+        parity["gemm_ar"] = {"rel_frobenius": glob, "worst_tile_rel_frobenius": tile, "tol": GEMM_TOL}
+        del ar_ref
+        ar_bytes = 2 * rs_bytes_per_rank
+        ar_result = {"workload": f"GEMM+AR bf16 TP={tp}: A [{RS_M},{rs_k}], B [{RS_N},{rs_k}], out [{RS_M},{RS_N}] on every rank, "
+                                 f"{args.ar_splits} row slices (reduce-scatter in the kernel, all-gather by copy engines; "
+                                 "includes the closing barrier that makes the output reusable)",
+                     "ms_per_step": ar_t["ms"], "ms_min": ar_t["ms_min"], "ms_max": ar_t["ms_max"],
+                     "per_gpu_tflops": 2.0 * RS_M * RS_N * rs_k / (ar_t["ms"] * 1e-3) / 1e12,
+                     "nvlink_gbs_achieved": ar_bytes / (ar_t["ms"] * 1e-3) / 1e9,
+                     "fused_roofline_ms": max(2.0 * RS_M * RS_N * rs_k / (peaks["bf16_tflops"] * 1e12),
+                                              ar_bytes / (NVLINK_GBS_NOMINAL * 1e9)) * 1e3}
+        ar_result["frac_of_fused_roofline"] = ar_result["fused_roofline_ms"] / ar_t["ms"]
+        del ar
         if not args.skip_alt_comm:
             alt = "sm" if args.rs_comm == "ce" else "ce"
             rs2 = GemmReduceScatter(ctx, RS_M, RS_N, dt, plan="direct", comm=alt, chunk_split=args.rs_split,
@@ -640,13 +666,18 @@ def run_own_arm(args):
             "frac_of_peak": c_flop / (c_t["ms"] * 1e-3) / 1e12 / peaks["bf16_tflops"]}
 
     # ---------------- verdict on parity (all ranks agree: the figures above are maxima over ranks)
+    ar_p = parity.get("gemm_ar", {"rel_frobenius": 0.0, "worst_tile_rel_frobenius": 0.0})
     flat = max_over_ranks([parity["ag_gemm"]["rel_frobenius"], parity["ag_gemm"]["worst_tile_rel_frobenius"],
                            parity["gemm_rs"]["rel_frobenius"], parity["gemm_rs"]["worst_tile_rel_frobenius"],
-                           0.0 if parity["gathered_bit_exact"] and parity.get("cp_gathered_bit_exact", True) else 1.0])
+                           0.0 if parity["gathered_bit_exact"] and parity.get("cp_gathered_bit_exact", True) else 1.0,
+                           ar_p["rel_frobenius"], ar_p["worst_tile_rel_frobenius"]])
+    if "gemm_ar" in parity:
+        parity["gemm_ar"]["rel_frobenius"], parity["gemm_ar"]["worst_tile_rel_frobenius"] = flat[5], flat[6]
     parity["ag_gemm"]["rel_frobenius"], parity["ag_gemm"]["worst_tile_rel_frobenius"] = flat[0], flat[1]
     parity["gemm_rs"]["rel_frobenius"], parity["gemm_rs"]["worst_tile_rel_frobenius"] = flat[2], flat[3]
     parity["gathered_bit_exact"] = flat[4] == 0.0
     ok = (flat[0] < GEMM_TOL and flat[1] < GEMM_TOL and flat[2] < GEMM_TOL and flat[3] < GEMM_TOL and flat[4] == 0.0
+          and flat[5] < GEMM_TOL and flat[6] < GEMM_TOL
           and all(parity[k]["max_abs_sampled_rows"] < ATTN_TOL for k in ("ulysses", "cp") if k in parity))
     parity["ok"] = bool(ok)
     parity["how"] = ("checked on the device after the timed regions: AG+GEMM against an fp32 product of the gathered "
@@ -710,6 +741,7 @@ def run_own_arm(args):
                             "nvlink_gbs_achieved": rs_bytes / (rs_ms * 1e-3) / 1e9 if world > 1 else None,
                             "compute_only_ms": rs_compute_only["ms"] if rs_compute_only else None,
                             "other_comm_mode": rs_other},
+                **({"gemm_ar": ar_result} if ar_result is not None else {}),
                 **attn_results,
             },
         }
@@ -750,6 +782,7 @@ def main():
     ap.add_argument("--rs-comm", default="ce", choices=["sm", "ce"],
                     help="GEMM+RS transport: the epilogue's TMA stores (sm) or copy engines (ce)")
     ap.add_argument("--rs-split", type=int, default=2, help="row pieces per reduce-scatter slab")
+    ap.add_argument("--ar-splits", type=int, default=4, help="row slices of GEMM+AR (separate launches)")
     ap.add_argument("--copy-streams", type=int, default=2)
     args = ap.parse_args()
     if args.impl == "reference":

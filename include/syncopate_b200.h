@@ -246,6 +246,12 @@ typedef struct syn_gemm_rs_args {
    * such a stream cannot be left waiting; the error is in the status block. */
   void* send_buf;
   uint64_t* send_flags;         /* device uint64[num_waves of src_sched] */
+  /* Optional device uint64[row pieces of the locally kept slab, in row order]: out_flags[g] is
+   * raised (locally) to the epoch once piece g of `out` is complete, so that somebody else can
+   * pass the reduced rows on while the kernel still runs (GEMM + all-reduce = this operator plus an
+   * all-gather of the reduced slabs; the reference runs a library all-reduce per slice behind the
+   * producer GEMM instead, tests/test_gemm_ar_collective.py:97-160). */
+  uint64_t* out_flags;
 } syn_gemm_rs_args;
 int syn_gemm_rs(const syn_gemm_rs_args* args, const syn_schedule* src_sched, const syn_schedule* dst_sched,
                 void* stream);

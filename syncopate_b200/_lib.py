@@ -124,6 +124,7 @@ class GemmRsArgs(C.Structure):
         ("counters", C.c_void_p),
         ("send_buf", C.c_void_p),
         ("send_flags", C.c_void_p),
+        ("out_flags", C.c_void_p),
     ]
 
 

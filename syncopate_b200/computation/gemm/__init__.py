@@ -212,6 +212,7 @@ def gemm_rs(
     send_buf: Optional[torch.Tensor] = None,
     send_flags: Optional[torch.Tensor] = None,
     trace=None,
+    out_flags: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
     """GEMM + reduce-scatter.  ``a`` ``[M, K_local]``, ``b`` ``[N, K_local]``; ``out``
     ``[M / world, N]`` receives the fp32 sum over ranks of this rank's row slab.  With ``send_buf``
@@ -233,6 +234,8 @@ def gemm_rs(
     if send_buf is not None:
         args.send_buf = send_buf.data_ptr()
         args.send_flags = send_flags.data_ptr()
+    if out_flags is not None:
+        args.out_flags = out_flags.data_ptr()  # int64, one word per row piece of the slab kept here
     s, keep1 = _schedule_struct(src_schedule)
     d, keep2 = _schedule_struct(dst_schedule)
     rc = L.lib().syn_gemm_rs(C.byref(args), C.byref(s), C.byref(d), _stream_ptr(stream))

@@ -263,7 +263,8 @@ int syn_gemm_rs(const syn_gemm_rs_args* args, const syn_schedule* src_sched, con
     if (tgt == rank) {
       slab0 = static_cast<char*>(args->out);
       slab_ld = ldo;
-      rt.flag = nullptr;
+      rt.flag = args->out_flags != nullptr ? args->out_flags + pc.group : nullptr;
+      rt.raise_on_abort = 1;
       rt.reduce = 1;
       for (int i = 0; i < n_red; ++i) rt.red_sig[i] = static_cast<int16_t>(groups[pc.group].sig[i]);
     } else if (args->send_buf != nullptr) {
@@ -271,6 +272,7 @@ int syn_gemm_rs(const syn_gemm_rs_args* args, const syn_schedule* src_sched, con
       slab0 = static_cast<char*>(args->send_buf) + static_cast<size_t>(tgt) * slab_elems * 2;
       slab_ld = g.N;
       rt.flag = args->send_flags + pc.orig;
+      rt.raise_on_abort = 1;
       rt.reduce = 0;
     } else {
       slab0 = static_cast<char*>(args->stage.ptrs[tgt]) + (half + rank) * slab_elems * 2;
@@ -306,7 +308,6 @@ int syn_gemm_rs(const syn_gemm_rs_args* args, const syn_schedule* src_sched, con
   p.counters = args->counters;
   p.c = args->out;
   p.ldc = ldo;
-  p.raise_flags_on_abort = args->send_buf != nullptr ? 1 : 0;
   if (want_pair && pair_eligible(p, bn, grid))
     return gemm_launch_pair(p, &g, bn, grid, /*fused=*/true, static_cast<cudaStream_t>(stream));
   if (dynamic_sched()) p.sched = args->counters + SYN_MAX_WAVES + SYN_MAX_COMM_OPS;

@@ -530,10 +530,11 @@ gemm2_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUten
     }
   }
   if constexpr (FUSED) {
-    if (threadIdx.x == 0 && *abort_word != 0 && p.raise_flags_on_abort) {
+    if (threadIdx.x == 0 && *abort_word != 0) {
       for (int w = 0; w < p.num_waves; ++w) {
         const int r = p.waves[w].route;
-        if (r >= 0 && p.routes[r].flag != nullptr) st_release_sys_u64(p.routes[r].flag, p.signal_value);
+        if (r >= 0 && p.routes[r].flag != nullptr && p.routes[r].raise_on_abort)
+          st_release_sys_u64(p.routes[r].flag, p.signal_value);
       }
     }
   }

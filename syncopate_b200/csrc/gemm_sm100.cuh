@@ -56,7 +56,8 @@ struct GemmRoute {
   int32_t tmap_row0;      // row of the wave's first tile row in that map's coordinates
   int16_t red_sig[GEMM_MAX_RED];  // reduce waves: flag index (in GemmParams::red_flags) guarding the rows of this
                                   // wave in staged slab s
-  int16_t pad_;
+  int16_t raise_on_abort;  // 1: the flag is local and somebody may wait for it without a bound of its own (a stream
+                           // memory operation): a CTA that gave up raises it before it leaves
 };
 
 // One 2-D strided copy between mapped buffers, executed cooperatively by all comm warps.
@@ -83,7 +84,6 @@ struct GemmParams {
   int32_t total_tiles;
   int32_t num_waves;
   int32_t num_comm_ops;
-  int32_t raise_flags_on_abort;  // 1: a CTA that gave up on a wait raises every route flag before it leaves
   int32_t num_red;        // staged partial slabs to add in `reduce` routes
   int32_t red_ld;
   int32_t red_row0;       // global C row of the staged slabs' row 0
@@ -674,10 +674,11 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
   if constexpr (FUSED) {
     // Somebody outside the kernel may be waiting for the wave flags without a bound of its own (a
     // stream memory operation): after a failed wait the data are lost anyway, so let everybody go on.
-    if (threadIdx.x == 0 && *abort_word != 0 && p.raise_flags_on_abort) {
+    if (threadIdx.x == 0 && *abort_word != 0) {
       for (int w = 0; w < p.num_waves; ++w) {
         const int r = p.waves[w].route;
-        if (r >= 0 && p.routes[r].flag != nullptr) st_release_sys_u64(p.routes[r].flag, p.signal_value);
+        if (r >= 0 && p.routes[r].flag != nullptr && p.routes[r].raise_on_abort)
+          st_release_sys_u64(p.routes[r].flag, p.signal_value);
       }
     }
   }

@@ -224,13 +224,14 @@ class GemmReduceScatter:
 
     def __init__(self, ctx: SymmetricContext, M: int, N: int, dtype=torch.bfloat16, plan: str = "direct",
                  num_sms: int = 0, block_n: int = 0, timeout_ns: int = 0, lockstep: bool = True, comm: str = "sm",
-                 copy_streams: int = 2, chunk_split: int = 1):
+                 copy_streams: int = 2, chunk_split: int = 1, publish_pieces: bool = False):
         """``comm="sm"``: the GEMM's epilogue stores each tile straight into the target rank's staging
         slab (TMA stores to peer memory).  ``comm="ce"``: the epilogue stores locally and raises a
         local flag per wave; side streams wait for the flag (a stream memory operation), move the
         rows with a copy engine and raise the target's flag.  ``chunk_split`` sends every slab as
         that many row pieces; the rows kept here are then reduced piece by piece as the matching
-        pieces arrive."""
+        pieces arrive.  ``publish_pieces``: the kernel also raises the local flag ``out_flags[g]`` when
+        row piece g of the result is complete (for whoever passes the reduced rows on)."""
         if comm not in ("sm", "ce"):
             raise ValueError("comm must be 'sm' or 'ce'")
         self.ctx = ctx
@@ -238,6 +239,8 @@ class GemmReduceScatter:
         self.lockstep = lockstep
         self.world, self.rank = ctx.world, ctx.rank
         self.M, self.N, self.dtype = M, N, dtype
+        self.pieces = max(int(chunk_split), 1)   # row pieces of the slab kept here
+        self.out_flags = None
         self.slab = M // self.world
         self.num_sms, self.block_n, self.timeout_ns = num_sms, block_n, timeout_ns
         self.epoch = 0
@@ -251,6 +254,8 @@ class GemmReduceScatter:
         self.stage = ctx.alloc((2, self.world, self.slab, N), dtype)
         self.flags = ctx.alloc((max(self.info.recv_signal_num, 1),), torch.int64)
         self.counters = torch.zeros(NUM_COUNTERS, dtype=torch.int32, device=ctx.device)
+        if publish_pieces:
+            self.out_flags = torch.zeros(self.pieces, dtype=torch.int64, device=ctx.device)
         self.send = self.send_flags = None
         if comm == "ce":
             self.send = torch.empty(self.world, self.slab, N, dtype=dtype, device=ctx.device)
@@ -286,7 +291,7 @@ class GemmReduceScatter:
             gemm_rs(a, b, out, self.src_schedule, self.dst_schedule, self.remote_signals, self.stage.symm,
                     self.flags.symm, self.counters, epoch=self.epoch, num_sms=self.num_sms, block_n=self.block_n,
                     timeout_ns=self.timeout_ns, status=self.ctx.status, stream=cur, send_buf=self.send,
-                    send_flags=self.send_flags, trace=self.trace)
+                    send_flags=self.send_flags, trace=self.trace, out_flags=self.out_flags)
             side[0].wait_event(self._ev_start)
             if self.lockstep:
                 self.ctx.barrier(side[0])
@@ -303,7 +308,96 @@ class GemmReduceScatter:
         return gemm_rs(a, b, out, self.src_schedule, self.dst_schedule, self.remote_signals, self.stage.symm,
                        self.flags.symm, self.counters, epoch=self.epoch, num_sms=self.num_sms,
                        block_n=self.block_n, timeout_ns=self.timeout_ns, status=self.ctx.status, stream=cur,
-                       trace=self.trace)
+                       trace=self.trace, out_flags=self.out_flags)
+
+
+class GemmAllReduce:
+    """``out[M, N]`` (the same on every rank) ``= sum over ranks of A_r[M, K_r] @ B_r[N, K_r]^T``.
+
+    The reference overlaps a library all-reduce per row slice with the producer GEMM
+    (``build_all_reduce_plan(num_all_reduces=..., split_axis=0, compute_producer=True)``,
+    tests/test_gemm_ar_collective.py:97-160).  Here every slice is a GEMM + reduce-scatter (partial
+    sums pushed to the slab's owner, fp32 reduction in the owner's epilogue) whose reduced rows are
+    then all-gathered by copy engines: the kernel raises a local flag per finished row piece, side
+    streams wait for it and push the rows to every peer's copy of ``out``.  With ``num_splits`` > 1
+    the slices are separate launches, and the all-gather of one slice runs under the GEMM of the
+    next.  ``out`` is a symmetric buffer that the peers write: read it after the call has returned
+    in stream order (the call ends with a wait for every peer's rows) and before the next call
+    starts on any rank (``sync_after=True`` adds the barrier that guarantees the latter)."""
+
+    def __init__(self, ctx: SymmetricContext, M: int, N: int, dtype=torch.bfloat16, num_splits: int = 1,
+                 chunk_split: int = 1, comm: str = "ce", copy_streams: int = 2, timeout_ns: int = 0,
+                 lockstep: bool = True, sync_after: bool = False):
+        if M % (num_splits * ctx.world):
+            raise ValueError("M must be divisible by num_splits * world")
+        self.ctx, self.world, self.rank = ctx, ctx.world, ctx.rank
+        self.M, self.N, self.dtype = M, N, dtype
+        self.num_splits, self.sync_after = num_splits, sync_after
+        self.part_rows = M // num_splits
+        self.out = ctx.alloc((M, N), dtype)
+        self.rs = GemmReduceScatter(ctx, self.part_rows, N, dtype, plan="direct", timeout_ns=timeout_ns,
+                                    lockstep=lockstep, comm=comm, copy_streams=copy_streams, chunk_split=chunk_split,
+                                    publish_pieces=True)
+        self.slab = self.part_rows // self.world
+        if self.world == 1:
+            return
+        pieces = self.rs.pieces
+        self.gather_flags = ctx.alloc((self.world * pieces,), torch.int64)  # [sender][piece], raised by the sender
+        self._gather_streams = [torch.cuda.Stream(device=ctx.device) for _ in range(max(1, copy_streams))]
+        self._ev = torch.cuda.Event()
+        self._programs = []
+        for part in range(num_splits):
+            steps = self.gather_program(part)
+            self._programs.append((_L.make_ce_program(steps), len(steps)))
+
+    def piece_rows(self):
+        """``[(first row inside the slab, rows)]`` of the row pieces the slab is reduced (and published) in."""
+        rows = -(-self.slab // self.rs.pieces)
+        return [(lo, min(rows, self.slab - lo)) for lo in range(0, self.slab, rows)]
+
+    def gather_program(self, part: int):
+        """Copy-engine steps that pass this rank's reduced rows of slice ``part`` on: per row piece,
+        wait for the kernel's local flag, copy the rows into every peer's ``out`` (peers in swizzled
+        order), raise ``gather_flags[rank][piece]`` there.  A piece always uses the same stream, so
+        its flag on a peer never runs ahead of the rows of an earlier slice."""
+        row_bytes = self.N * self.dtype.itemsize
+        steps = []
+        for g, (lo, rows) in enumerate(self.piece_rows()):
+            first = part * self.part_rows + self.rank * self.slab + lo
+            wait = self.rs.out_flags.data_ptr() + 8 * g
+            for i in range(1, self.world):
+                peer = (self.rank + i) % self.world
+                steps.append((wait, self.out.symm.ptrs[peer] + first * row_bytes,
+                              self.out.symm.ptrs[self.rank] + first * row_bytes, rows * row_bytes,
+                              self.gather_flags.symm.ptrs[peer] + 8 * (self.rank * self.rs.pieces + g), g))
+        return steps
+
+    def __call__(self, a: torch.Tensor, b: torch.Tensor, stream=None) -> torch.Tensor:
+        cur = stream or torch.cuda.current_stream()
+        if self.world == 1:
+            return self.rs(a, b, self.out.local, stream=cur)
+        lib = _raw_lib()
+        for part in range(self.num_splits):
+            r0 = part * self.part_rows
+            own = self.out.local[r0 + self.rank * self.slab : r0 + (self.rank + 1) * self.slab]
+            self._ev.record(cur)
+            for s in self._gather_streams:
+                s.wait_event(self._ev)   # the previous call's readers of `out` are behind this point
+            self.rs(a[r0 : r0 + self.part_rows], b, own, stream=cur)
+            program, n = self._programs[part]
+            _L.ce_run(program, n, self._gather_streams, self.rs.epoch)
+        # every peer's rows of the last slice (and, flag by flag in order, of the earlier ones)
+        for src in range(self.world):
+            if src == self.rank:
+                continue
+            for g in range(self.rs.pieces):
+                _L.check(lib.syn_flag_wait_stream(self.gather_flags.local.data_ptr() + 8 * (src * self.rs.pieces + g),
+                                                  self.rs.epoch, cur.cuda_stream or None), "syn_flag_wait_stream")
+        for s in self._gather_streams:
+            cur.wait_stream(s)
+        if self.sync_after:
+            self.ctx.barrier(cur)
+        return self.out.local
 
 
 # ----------------------------------------------------------------------------------------------

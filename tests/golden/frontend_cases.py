@@ -82,6 +82,14 @@ def cases():
     add("dring_small_w4_g4", "build_double_ring_all_gather_plan", 4, "sm", shape=(64, 8), dtype=FP16, axis=0,
         inner_mesh_size=4, buffer_name="buf")
     add("ring_w1", "build_ring_all_gather_plan", 1, None, shape=(8, 8), dtype=FP16, axis=0, buffer_name="buf")
+    # ---- GEMM + all-reduce
+    add("ar_cfg2_w8_split4", "build_all_reduce_plan", 8, "sm", shape=(8192, 8192), dtype=BF16, buffer_name="c",
+        num_all_reduces=4, split_axis=0, compute_producer=True)
+    add("ar_plain_w2", "build_all_reduce_plan", 2, "sm", shape=(64, 32), dtype=FP16, buffer_name="c")
+    add("ar_axis1_w4", "build_all_reduce_plan", 4, "ce", shape=(16, 64), dtype=FP32, buffer_name="c",
+        num_all_reduces=2, split_axis=-1, compute_producer=False)
+    add("ar_nvsharp_w4", "build_all_reduce_nvsharp_plan", 4, "sm", shape=(512, 256), dtype=BF16, src_name="src",
+        dst_name="dst", num_all_reduces=2, split_axis=0, compute_producer=True)
     return out
 
 

@@ -14,6 +14,7 @@ os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
 from syncopate_b200.operators import (  # noqa: E402
     AllGatherGemm,
     ContextParallelAttention,
+    GemmAllReduce,
     GemmReduceScatter,
     UlyssesAttention,
 )
@@ -116,6 +117,29 @@ def main():
             if not (e < TOL and et < TOL):
                 failures.append(f"gemm_rs {kind}/{comm}/split{split} M={M} it={it} rank={rank}: relerr={e:.3e} tile={et:.3e}")
         del op, part, ref
+
+    # ---- GEMM + all-reduce: reduce-scatter in the kernel, reduced rows all-gathered by copy engines
+    for M, N, Kl, splits, pieces, comm in ((512 * world, 512, 256, 1, 1, "ce"), (1024 * world, 512, 256, 2, 2, "ce"),
+                                           (512 * world, 768, 128, 2, 1, "sm"), (8192, 8192, 28672 // world, 4, 1, "ce")):
+        if (M // splits // world) % (pieces * 128):
+            continue
+        op = GemmAllReduce(ctx, M, N, dt, num_splits=splits, chunk_split=pieces, comm=comm, timeout_ns=2_000_000_000,
+                           sync_after=True)
+        a = seeded(2500 + rank, (M, Kl), 1.0, dt, dev)
+        b = seeded(3500 + rank, (N, Kl), 0.02, dt, dev)
+        ref = a.float() @ b.float().t()
+        dist.all_reduce(ref)
+        for it in range(3):
+            op.out.local.fill_(float("nan"))
+            torch.cuda.synchronize()
+            ctx.barrier()
+            out = op(a, b)
+            ctx.check()
+            e, et = tile_ok(out, ref)
+            if not (e < TOL and et < TOL):
+                failures.append(f"gemm_ar M={M} splits={splits} pieces={pieces} {comm} it={it} rank={rank}: "
+                                f"relerr={e:.3e} tile={et:.3e}")
+        del op, ref
 
     # ---- attention operators (reference: gather with torch.distributed, dense fp32 attention per head)
     def dense(q, k, v, causal, q_pos=None, k_pos=None):

@@ -380,6 +380,8 @@ def test_fused_gemm_rs_with_split_slabs(world, M, N, Kl, split, transport, statu
                 rsig = rs_remote_signals(info, r, src)
                 sched, sig_sel, sel = _rs_phase_schedule(src, rsig, r, own)
                 kw = {}
+                if own:
+                    kw = dict(out_flags=torch.zeros(split, dtype=torch.int64, device="cuda"))
                 if transport == "local" and not own:
                     send = torch.full((world, slab, N), float("nan"), dtype=dt, device="cuda")
                     send_flags = torch.zeros(len(sel), dtype=torch.int64, device="cuda")
@@ -389,7 +391,9 @@ def test_fused_gemm_rs_with_split_slabs(world, M, N, Kl, split, transport, statu
                 torch.cuda.synchronize()
                 assert status.tolist() == [0, 0, 0, 0]
                 assert int(counters.abs().sum()) == 0
-                if kw:
+                if own:
+                    assert kw["out_flags"].tolist() == [epoch] * split    # one local flag per reduced row piece
+                elif kw:
                     assert send_flags.tolist() == [epoch] * len(sel)   # one local flag per wave
                     # the transport program addresses waves by their index in the schedule it is given
                     class _Sub:
