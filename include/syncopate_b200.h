@@ -321,7 +321,38 @@ typedef struct syn_attn_args {
   int32_t* status;
   const struct syn_attn_plan* plan; /* NULL, or a work-balanced ownership made by syn_attention_plan for
                                        exactly these shapes, waves, positions and num_sms */
+  const struct syn_attn_push* push; /* NULL, or the producer role: finished rows go to their destination ranks */
 } syn_attn_args;
+
+/* Producer role of the attention kernel (replaces the reference's per-wave tile counter that raises
+ * COMPUTE_DONE for a communication program to push the finished slab,
+ * syncopate/computation/attn/template.py:47-361 with the producer epilogue of
+ * computation/transform/transformer.py:882-903, driven as in tests/test_attn_all2all_transform.py:182-215).
+ * Here the kernel pushes by itself: when a 128-row query tile has had its LAST visit (syn_attn_plan
+ * visits), its final rows are not stored to `o` but staged in shared memory and sent with TMA
+ * stores into the destination rank's buffer dst.ptrs[dst_rank], a [Z, dst_rows, dst_heads, 128]
+ * tensor with element strides dst_strides (z, s, h), at row dst_row0 + (row - q_begin) and head
+ * head_offset + h; when every tile of a slab has landed, flags.ptrs[dst_rank][flag] is raised to
+ * the call's signal_value.  Needs a plan (fixed ownership lists), Sq a multiple of 128, slabs that
+ * start and end on 128-row boundaries and cover every query row exactly once, at most 64 units
+ * per CTA; tiles that no wave visits are not sent.  Earlier visits of a tile still merge through
+ * `o` (local), which therefore must be a private buffer of the rank. */
+typedef struct syn_attn_push_slab {
+  int32_t q_begin, q_rows; /* query rows [q_begin, q_begin + q_rows) of the kernel's output */
+  int32_t dst_rank;
+  int32_t dst_row0;        /* destination row of q_begin */
+  int32_t flag;            /* -1 = none */
+} syn_attn_push_slab;
+typedef struct syn_attn_push {
+  int32_t num_slabs;       /* at most SYN_MAX_WORLD */
+  const syn_attn_push_slab* slabs; /* host array */
+  syn_symm dst;
+  int64_t dst_strides[3];  /* elements: z, s, h */
+  int32_t dst_rows, dst_heads;
+  int32_t head_offset;
+  syn_symm flags;
+  uint32_t* counters;      /* device uint32[SYN_MAX_WORLD], zero before the first call (left zero by every call) */
+} syn_attn_push;
 
 /* Which CTA owns which unit of query rows for a whole launch (fixed ownership is what makes the
  * merge over waves lock-free).  Without a plan ownership is arithmetic (unit id modulo grid, or
@@ -331,13 +362,16 @@ typedef struct syn_attn_args {
  * work dynamically with a tile counter and a lock per query tile
  * (syncopate/computation/attn/template.py:80-121, :339-349). */
 #define SYN_ATTN_PLAN_MAX_GRID 160
-#define SYN_ATTN_PLAN_MAX_UNITS 1024
+#define SYN_ATTN_PLAN_MAX_UNITS 2048
 typedef struct syn_attn_plan {
   int32_t grid;       /* CTAs the plan was made for */
   int32_t unit_rows;  /* query rows per unit (128 or 256) */
   int32_t num_units;  /* Z * Hq * ceil(Sq / unit_rows) */
   uint16_t start[SYN_ATTN_PLAN_MAX_GRID + 1]; /* CTA c owns units[start[c] .. start[c + 1]) */
   uint16_t units[SYN_ATTN_PLAN_MAX_UNITS];    /* unit id = (z * Hq + h) * units_per_head + index */
+  /* visits[2 * unit + t]: in how many waves query tile t (0 / 1) of the unit takes part (has a
+   * visible key block); what tells the producer role of syn_attention a tile's last visit. */
+  uint8_t visits[2 * SYN_ATTN_PLAN_MAX_UNITS];
 } syn_attn_plan;
 
 /* Fills `out` for the launch that `args` + `sched` describe (pointers to tensors are not used).

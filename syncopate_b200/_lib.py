@@ -194,11 +194,35 @@ class AttnArgs(C.Structure):
         ("timeout_ns", C.c_uint64),
         ("status", C.c_void_p),
         ("plan", C.c_void_p),
+        ("push", C.c_void_p),
+    ]
+
+
+class AttnPushSlab(C.Structure):
+    """``syn_attn_push_slab``."""
+
+    _fields_ = [("q_begin", C.c_int32), ("q_rows", C.c_int32), ("dst_rank", C.c_int32), ("dst_row0", C.c_int32),
+                ("flag", C.c_int32)]
+
+
+class AttnPush(C.Structure):
+    """``syn_attn_push``: the attention kernel's producer role."""
+
+    _fields_ = [
+        ("num_slabs", C.c_int32),
+        ("slabs", C.POINTER(AttnPushSlab)),
+        ("dst", Symm),
+        ("dst_strides", C.c_int64 * 3),
+        ("dst_rows", C.c_int32),
+        ("dst_heads", C.c_int32),
+        ("head_offset", C.c_int32),
+        ("flags", Symm),
+        ("counters", C.c_void_p),
     ]
 
 
 ATTN_PLAN_MAX_GRID = 160
-ATTN_PLAN_MAX_UNITS = 1024
+ATTN_PLAN_MAX_UNITS = 2048
 
 
 class AttnPlan(C.Structure):
@@ -210,6 +234,7 @@ class AttnPlan(C.Structure):
         ("num_units", C.c_int32),
         ("start", C.c_uint16 * (ATTN_PLAN_MAX_GRID + 1)),
         ("units", C.c_uint16 * ATTN_PLAN_MAX_UNITS),
+        ("visits", C.c_uint8 * (2 * ATTN_PLAN_MAX_UNITS)),
     ]
 
 

@@ -93,6 +93,7 @@ def attention_forward(
     state: Optional[AttentionState] = None,
     signal_value: int = 1,
     comm: Optional[L.AttnComm] = None,
+    push: Optional[L.AttnPush] = None,
     num_sms: int = 0,
     timeout_ns: int = 0,
     status=None,
@@ -104,7 +105,9 @@ def attention_forward(
     metadata one wave covers everything.  ``cum_wave_sizes``, ``NUM_WAVES``, ``cum_tiles`` and
     ``counter_ptr`` are accepted for signature compatibility (they follow from the waves).
     ``balance`` plans a work-balanced ownership of the query tiles on the first call of a
-    configuration and reuses it afterwards.
+    configuration and reuses it afterwards.  ``push`` switches the kernel's producer role on (see
+    ``syn_attn_push``): rows leave for their destination ranks at their tile's last visit instead of
+    being stored to the output; it needs the planned ownership.
     Returns the output (``output_buffer`` if given)."""
     for name, t in (("q", q), ("k", k), ("v", v)):
         if not t.is_cuda or t.dtype not in _DTYPES:
@@ -134,12 +137,18 @@ def attention_forward(
     if offs is None:
         offs, sizes = [[0, 0, 0, 0]], [[Z, Hq, Sq, Skv]]
     sched, keep = L.make_schedule(offs, sizes, _tolist(signal_offsets), ndim=4)
+    if push is not None:
+        if not balance:
+            raise ValueError("the producer role needs the planned ownership (balance=True)")
+        a.push = C.addressof(push)
     if balance:
-        key = (os.environ.get("SYNCOPATE_B200_ATTN_TWO_TILE"), Z, Hq, Hkv, Sq, Skv, bool(causal), num_sms, tuple(map(tuple, offs)), tuple(map(tuple, sizes)),
+        key = (os.environ.get("SYNCOPATE_B200_ATTN_TWO_TILE"), push is not None, Z, Hq, Hkv, Sq, Skv, bool(causal), num_sms, tuple(map(tuple, offs)), tuple(map(tuple, sizes)),
                None if q_pos is None else (q_pos.data_ptr(), q_pos._version),
                None if kv_pos is None else (kv_pos.data_ptr(), kv_pos._version))
         plan = _owner_plan(a, sched, key, q_pos, kv_pos)
         a.plan = C.addressof(plan) if plan is not None else None
+        if push is not None and plan is None:
+            raise L.SynError(L.SYN_ERR_TOO_LARGE, "attention_forward", "too many units for the producer role's plan")
     if stream is None:
         stream = torch.cuda.current_stream()
     rc = L.lib().syn_attention(C.byref(a), C.byref(sched), C.byref(comm) if comm is not None else None,

@@ -115,12 +115,21 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bars + 26 + COMM_NBUF);
   volatile int* abort_word = reinterpret_cast<volatile int*>(tmem_holder + 1);
   int* abort_info = const_cast<int*>(abort_word) + 1;
+  // producer role: visits left per (unit of this CTA's list, tile)
+  volatile uint8_t* left = reinterpret_cast<volatile uint8_t*>(abort_info + 2);
+  const bool pushing = p.num_push > 0;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (pushing && threadIdx.x >= 128 && threadIdx.x < 128 + 2 * ATTN_PUSH_MAX_UNITS_PER_CTA) {
+    const int idx = threadIdx.x - 128, first = p.own_start[blockIdx.x], count = p.own_start[blockIdx.x + 1] - first;
+    left[idx] = (idx >> 1) < count ? p.visits[2 * p.own_units[first + (idx >> 1)] + (idx & 1)] : 0;
+  }
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
       mbar_init(&q_full[i], 1);
-      mbar_init(&q_empty[i], 1);
+      // with the producer role the softmax warpgroup stages its last rows in the Q tile's shared
+      // memory, so it (and not the issuer's last product) hands the tile back to the loader
+      mbar_init(&q_empty[i], pushing ? 128 : 1);
       mbar_init(&k_full[i], 1);
       mbar_init(&k_empty[i], 2);  // one release per MMA warp
       mbar_init(&v_full[i], 1);
@@ -382,7 +391,7 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
         if (act[x]) {
           if (elect_one()) {
             umma_commit(&o_full[x]);
-            umma_commit(&q_empty[x]);
+            if (!pushing) umma_commit(&q_empty[x]);
           }
           ++uqx;
         }
@@ -424,7 +433,8 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
       return ok;
     };
     while (ok && cur.next(p, z, h, un)) {
-      if (*abort_word != 0) break;
+      // (with the producer role the four warps of a tile leave together, at the unit's closing barrier)
+      if (!pushing && *abort_word != 0) break;
       const AttnWave& w = p.waves[cur.wave];
       const TileRole t = tile_role(p, w, 2 * un + x), other = tile_role(p, w, 2 * un + (x ^ 1));
       int active = 0;
@@ -538,15 +548,79 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
         }
         ++j;
       }
-      if (!ok) break;
-      // the unit's last product into O_x
-      if (!wait(&o_full[x], ux & 1u)) break;
-      tc_fence_after();
+      if (!pushing) {
+        if (!ok) break;
+        // the unit's last product into O_x
+        if (!wait(&o_full[x], ux & 1u)) break;
+        tc_fence_after();
 
-      attn_finish_row<BF16>(p, z, h, qt, row, m, l, o_tmem);
-      // O_x has been read: the next unit's first product may overwrite it
-      tc_fence_before();
-      mbar_arrive(&o_empty[x]);
+        attn_finish_row<BF16>(p, z, h, qt, row, m, l, o_tmem);
+        // O_x has been read: the next unit's first product may overwrite it
+        tc_fence_before();
+        mbar_arrive(&o_empty[x]);
+        ++ux;
+        continue;
+      }
+      // ---- producer role.  The tile's four warps meet at a barrier that also tells them whether
+      // any of them gave up, so that they leave the loop at the same unit.
+      const int pos = cur.slot - 1 - static_cast<int>(p.own_start[blockIdx.x]);
+      const bool last_visit = left[2 * pos + x] == 1;
+      int slab = 0;
+      if (ok) wait(&o_full[x], ux & 1u);
+      if (ok) {
+        tc_fence_after();
+        // The tile's last visit: its final rows (merged with what earlier visits left in `o`) are
+        // staged in the Q tile's shared memory, which nothing reads any more, and leave as two TMA
+        // stores per warp into the destination rank's buffer.
+        uint8_t* stage = last_visit ? sQ + x * ATTN_TILE_BYTES + q * 8192 : nullptr;
+        attn_finish_row<BF16>(p, z, h, qt, row, m, l, o_tmem, stage);
+        if (last_visit) {
+          while (slab + 1 < p.num_push && qt * ATTN_BM >= p.push[slab].s1) ++slab;
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            const int drow = p.push[slab].row0 + (qt * ATTN_BM - p.push[slab].s0) + q * 32;
+            tma_store_4d(&p.tmap_push[slab], stage, 0, drow, p.push_head0 + h, z);
+            tma_store_4d(&p.tmap_push[slab], stage + 4096, 64, drow, p.push_head0 + h, z);
+            bulk_commit();
+            bulk_wait<0>();       // landed (not just read): the slab's flag may follow
+            fence_proxy_async();
+            __threadfence_system();
+          }
+        }
+        tc_fence_before();
+      }
+      uint32_t anybody_failed;
+      asm volatile(
+          "{\n"
+          ".reg .pred pin, pout;\n"
+          "setp.ne.u32 pin, %1, 0;\n"
+          "barrier.cta.red.or.pred pout, %2, 128, pin;\n"
+          "selp.u32 %0, 1, 0, pout;\n"
+          "}\n"
+          : "=r"(anybody_failed)
+          : "r"(ok ? 0u : 1u), "r"(2 + x)
+          : "memory");
+      if (anybody_failed) {
+        ok = false;
+        break;
+      }
+      if ((threadIdx.x & 127) == 0) {
+        left[2 * pos + x] = static_cast<uint8_t>(left[2 * pos + x] - 1);
+        if (last_visit) {
+          // every warp's stores have landed (they waited before the barrier): count the tile in
+          const AttnPushSlab& ps = p.push[slab];
+          __threadfence_system();
+          const uint32_t old = atomicAdd(&p.push_counters[slab], 1u);
+          if (old + 1u == static_cast<uint32_t>(ps.tiles)) {
+            p.push_counters[slab] = 0;
+            __threadfence_system();
+            if (ps.flag != nullptr) st_release_sys_u64(ps.flag, p.signal_value);
+          }
+        }
+      }
+      mbar_arrive(&q_empty[x]);  // the staging space is the loader's again
+      mbar_arrive(&o_empty[x]);  // O_x has been read: the next unit's first product may overwrite it
       ++ux;
     }
   }

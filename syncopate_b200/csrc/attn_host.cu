@@ -115,8 +115,9 @@ static int launch_grid(const syn_attn_args* a, int* grid) {
 // A CTA takes about 1.5 times as long over a key block with two query tiles as with one.  The
 // two-tile kernel therefore wins unless the one-tile kernel, spreading the same rows over more
 // SMs, needs fewer than 1.5 times as many rounds.
-static bool use_two_tile(const AttnParams& p, int grid) {
+static bool use_two_tile(const AttnParams& p, int grid, bool push = false) {
   const int mode = two_tile_mode();
+  if (push) return true;  // the producer role lives in the two-tile kernel
   if (p.q_tiles < 2 || mode == 0) return false;
   if (mode == 2) return true;
   const long heads = static_cast<long>(p.Z) * p.Hq;
@@ -150,7 +151,7 @@ extern "C" int syn_attention_plan(const syn_attn_args* a, const syn_schedule* sc
     grid = a->num_sms;
   }
   if (grid > SYN_ATTN_PLAN_MAX_GRID) return SYN_ERR_TOO_LARGE;
-  const int shift = use_two_tile(p, grid) ? 1 : 0;
+  const int shift = use_two_tile(p, grid, a->push != nullptr) ? 1 : 0;
   const int per_head = (p.q_tiles + (1 << shift) - 1) >> shift;
   const long n_units = static_cast<long>(p.Z) * p.Hq * per_head;
   if (n_units > SYN_ATTN_PLAN_MAX_UNITS) return SYN_ERR_TOO_LARGE;
@@ -159,26 +160,38 @@ extern "C" int syn_attention_plan(const syn_attn_args* a, const syn_schedule* sc
   // fixed cost for loading Q and writing the result
   std::vector<long> weight(static_cast<size_t>(n_units), 0);
   std::vector<long> w_unit(static_cast<size_t>(per_head));
+  std::vector<int> visits(static_cast<size_t>(n_units) * 2, 0);  // waves each tile of a unit takes part in
+  std::vector<int> v_unit(static_cast<size_t>(per_head) * 2);
   for (int w = 0; w < p.num_waves; ++w) {
     const AttnWave& aw = p.waves[w];
     for (int u = 0; u < per_head; ++u) {
       long cnt = 0;
+      bool tile_seen[2] = {false, false};
       for (int kb = aw.kb0; kb < aw.kb1; ++kb) {
         const int kpos0 = kv_pos_host ? kv_pos_host[kb] : kb * ATTN_BN;
         bool seen = false;
         for (int x = 0; x < (1 << shift); ++x) {
           const int qt = (u << shift) + x;
-          if (qt < aw.q0t || qt >= aw.q0t + aw.nqt) continue;
+          if (qt < aw.q0t || qt >= aw.q0t + aw.nqt || qt >= p.q_tiles) continue;
           const int qpos0 = q_pos_host ? q_pos_host[qt] : qt * ATTN_BM;
-          seen = seen || block_visible(p.causal != 0, qpos0, kpos0);
+          const bool vis = block_visible(p.causal != 0, qpos0, kpos0);
+          seen = seen || vis;
+          tile_seen[x] = tile_seen[x] || vis;
         }
         cnt += seen ? 1 : 0;
       }
       w_unit[u] = cnt > 0 ? cnt + 2 : 0;
+      v_unit[2 * u] = tile_seen[0] ? 1 : 0;
+      v_unit[2 * u + 1] = tile_seen[1] ? 1 : 0;
     }
     for (int z = aw.z0; z < aw.z0 + aw.nz; ++z)
       for (int h = aw.h0; h < aw.h0 + aw.nh; ++h)
-        for (int u = 0; u < per_head; ++u) weight[(static_cast<size_t>(z) * p.Hq + h) * per_head + u] += w_unit[u];
+        for (int u = 0; u < per_head; ++u) {
+          const size_t id = (static_cast<size_t>(z) * p.Hq + h) * per_head + u;
+          weight[id] += w_unit[u];
+          visits[2 * id] += v_unit[2 * u];
+          visits[2 * id + 1] += v_unit[2 * u + 1];
+        }
   }
   // longest first, each to the least loaded CTA
   std::vector<int> order(static_cast<size_t>(n_units));
@@ -203,6 +216,7 @@ extern "C" int syn_attention_plan(const syn_attn_args* a, const syn_schedule* sc
     for (uint16_t id : lists[c]) out->units[pos++] = id;
   }
   for (int c = grid; c <= SYN_ATTN_PLAN_MAX_GRID; ++c) out->start[c] = static_cast<uint16_t>(pos);
+  for (long i = 0; i < 2 * n_units; ++i) out->visits[i] = static_cast<uint8_t>(std::min(visits[static_cast<size_t>(i)], 255));
   return SYN_OK;
 }
 
@@ -287,7 +301,7 @@ extern "C" int syn_attention(const syn_attn_args* a, const syn_schedule* sched, 
   int grid = 0;
   rc = launch_grid(a, &grid);
   if (rc != SYN_OK) return rc;
-  const bool two = use_two_tile(p, grid);
+  const bool two = use_two_tile(p, grid, a->push != nullptr);
   if (a->plan != nullptr) {
     const syn_attn_plan& pl = *a->plan;
     const int per_head = two ? (p.q_tiles + 1) / 2 : p.q_tiles;
@@ -297,6 +311,50 @@ extern "C" int syn_attention(const syn_attn_args* a, const syn_schedule* sched, 
     memcpy(p.own_start, pl.start, sizeof(p.own_start));
     memcpy(p.own_units, pl.units, sizeof(p.own_units));
     p.use_lists = 1;
+  }
+  if (a->push != nullptr) {
+    // producer role: destination maps, slab table, per-tile visit counts (from the plan)
+    const syn_attn_push& pu = *a->push;
+    if (a->plan == nullptr || !two) return SYN_ERR_INVALID;  // needs fixed ownership lists
+    if (pu.num_slabs <= 0 || pu.num_slabs > ATTN_MAX_PUSH || pu.slabs == nullptr || pu.counters == nullptr)
+      return SYN_ERR_INVALID;
+    if (a->Sq % ATTN_BM != 0) return SYN_ERR_SHAPE;
+    if (pu.dst.world <= 0 || pu.dst.world > SYN_MAX_WORLD) return SYN_ERR_INVALID;
+    for (int c = 0; c < grid; ++c)
+      if (a->plan->start[c + 1] - a->plan->start[c] > ATTN_PUSH_MAX_UNITS_PER_CTA) return SYN_ERR_TOO_LARGE;
+    memcpy(p.visits, a->plan->visits, sizeof(p.visits));
+    int covered = 0;
+    for (int i = 0; i < pu.num_slabs; ++i) {
+      const syn_attn_push_slab& sl = pu.slabs[i];
+      if (sl.q_begin != covered || sl.q_rows <= 0 || (sl.q_begin % ATTN_BM) || (sl.q_rows % ATTN_BM)) return SYN_ERR_SHAPE;
+      if (sl.dst_rank < 0 || sl.dst_rank >= pu.dst.world || pu.dst.ptrs[sl.dst_rank] == nullptr) return SYN_ERR_INVALID;
+      if (sl.dst_row0 < 0 || sl.dst_row0 + sl.q_rows > pu.dst_rows) return SYN_ERR_SHAPE;
+      covered += sl.q_rows;
+      AttnPushSlab& ps = p.push[i];
+      ps.s0 = sl.q_begin;
+      ps.s1 = sl.q_begin + sl.q_rows;
+      ps.row0 = sl.dst_row0;
+      ps.flag = nullptr;
+      if (sl.flag >= 0) {
+        if (pu.flags.ptrs[sl.dst_rank] == nullptr) return SYN_ERR_INVALID;
+        ps.flag = static_cast<uint64_t*>(pu.flags.ptrs[sl.dst_rank]) + sl.flag;
+      }
+      // tiles of the slab that any wave visits, over all (z, h)
+      int tiles = 0;
+      const int per_head = (p.q_tiles + 1) / 2;
+      for (long zh = 0; zh < static_cast<long>(a->Z) * a->Hq; ++zh)
+        for (int qt = ps.s0 / ATTN_BM; qt < ps.s1 / ATTN_BM; ++qt)
+          tiles += p.visits[2 * (zh * per_head + (qt >> 1)) + (qt & 1)] > 0 ? 1 : 0;
+      ps.tiles = tiles;
+      rc = encode_tmap_4d_sw128(&p.tmap_push[i], pu.dst.ptrs[sl.dst_rank], a->Z, pu.dst_heads, pu.dst_rows, ATTN_D,
+                                pu.dst_strides[0], pu.dst_strides[2], pu.dst_strides[1], 32, 64);
+      if (rc != SYN_OK) return rc;
+    }
+    if (covered != a->Sq) return SYN_ERR_SHAPE;
+    if (pu.head_offset < 0 || pu.head_offset + a->Hq > pu.dst_heads) return SYN_ERR_SHAPE;
+    p.num_push = pu.num_slabs;
+    p.push_head0 = pu.head_offset;
+    p.push_counters = pu.counters;
   }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (two) {

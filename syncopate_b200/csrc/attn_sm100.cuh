@@ -34,6 +34,17 @@ struct AttnWave {
   int32_t sig;             // flag index to wait for, -1 = none
 };
 
+constexpr int ATTN_MAX_PUSH = SYN_MAX_WORLD;
+constexpr int ATTN_PUSH_MAX_UNITS_PER_CTA = 64;
+
+// One destination slab of the producer role: query rows [s0, s1) go to one rank's buffer.
+struct AttnPushSlab {
+  int32_t s0, s1;     // query rows covered
+  int32_t row0;       // destination row of s0
+  int32_t tiles;      // 128-row tiles (over z and h) whose last visit completes the slab
+  uint64_t* flag;     // raised to signal_value once `tiles` tiles have landed; may be null
+};
+
 struct AttnParams {
   CUtensorMap tmap_q, tmap_k, tmap_v;  // 4-D (d, s, h, z), box 64 x 128
   void* o;
@@ -62,6 +73,13 @@ struct AttnParams {
   int32_t use_lists;       // 1: ownership comes from the lists below instead of the arithmetic rule
   uint16_t own_start[SYN_ATTN_PLAN_MAX_GRID + 1];
   uint16_t own_units[SYN_ATTN_PLAN_MAX_UNITS];
+  // producer role (two-tile kernel): a tile's rows leave for their destination rank at its last visit
+  int32_t num_push;        // 0 = off
+  int32_t push_head0;      // destination head of head 0
+  uint32_t* push_counters; // [num_push] tiles landed per slab, self-resetting
+  AttnPushSlab push[ATTN_MAX_PUSH];
+  CUtensorMap tmap_push[ATTN_MAX_PUSH];  // 4-D (d, s, h, z) maps of the destination buffers, box 64 x 32
+  uint8_t visits[2 * SYN_ATTN_PLAN_MAX_UNITS];  // per (unit, tile): waves it takes part in
 };
 
 // Enumerates, in wave order, the units this CTA owns.  All roles run the same enumeration.
@@ -172,9 +190,13 @@ __device__ __forceinline__ uint32_t pack2_f16(float lo, float hi) {
 // visited it) the stored (O, log2-LSE) and the new ones are merged first
 // (syncopate/computation/attn/template.py:339-349).  Every lane of the warp must call it (the
 // tensor-memory loads are warp-wide); rows past the end only skip the memory accesses.
+//
+// With `stage` (shared memory of this warp, 2 x 4 KB: d 0..63 and d 64..127 of its 32 rows in the
+// 128-byte swizzle of a TMA store box) the finished row goes there instead of `o`: the caller sends
+// it on (producer role).
 template <bool BF16>
 __device__ __forceinline__ void attn_finish_row(const AttnParams& p, int z, int h, int qt, int row, float m, float l,
-                                                uint32_t o_tmem) {
+                                                uint32_t o_tmem, uint8_t* stage = nullptr) {
   const int srow = qt * ATTN_BM + row;
   const bool valid = srow < p.Sq;
   const size_t stat_idx = (static_cast<size_t>(z) * p.Hq + h) * p.Sq + (valid ? srow : 0);
@@ -224,7 +246,13 @@ __device__ __forceinline__ void attn_finish_row(const AttnParams& p, int z, int 
         out.y = BF16 ? pack2_bf16(f[2], f[3]) : pack2_f16(f[2], f[3]);
         out.z = BF16 ? pack2_bf16(f[4], f[5]) : pack2_f16(f[4], f[5]);
         out.w = BF16 ? pack2_bf16(f[6], f[7]) : pack2_f16(f[6], f[7]);
-        o_ptr[v * 4 + c4] = out;
+        if (stage != nullptr) {
+          // 16-byte chunk v * 4 + c4 of the row's 16: half = chunk / 8, chunk inside the half swizzled
+          const int chunk = v * 4 + c4, lane32 = row & 31;
+          *reinterpret_cast<uint4*>(stage + (chunk >> 3) * 4096 + lane32 * 128 + (((chunk & 7) ^ (lane32 & 7)) << 4)) = out;
+        } else {
+          o_ptr[v * 4 + c4] = out;
+        }
       }
     }
   }

@@ -447,7 +447,13 @@ class UlyssesAttention:
     after ``wait_output`` and before the next call starts."""
 
     def __init__(self, ctx, B: int, H: int, S_local: int, D: int = 128, dtype=torch.bfloat16, causal: bool = True,
-                 sm_scale: Optional[float] = None, timeout_ns: int = 0, lockstep: bool = True, sync_after: bool = False):
+                 sm_scale: Optional[float] = None, timeout_ns: int = 0, lockstep: bool = True, sync_after: bool = False,
+                 overlap_out: bool = True):
+        """``overlap_out``: the attention kernel sends every query tile's final rows to their rank
+        itself, at the tile's last visit, while the other tiles are still being computed (the
+        reference's overlapped form, tests/test_attn_all2all_transform.py:182-215); otherwise, or
+        when the problem has more tile pairs than an ownership plan holds, the outbound all-to-all
+        is an SM copy kernel behind the attention kernel."""
         self.ctx, self.world, self.rank = ctx, ctx.world, ctx.rank
         self.lockstep, self.sync_after = lockstep, sync_after
         W = self.world
@@ -495,10 +501,40 @@ class UlyssesAttention:
         self.out_comm, self._keep_out = _L.make_attn_comm(
             self.out_ops, [_local_table(ctx, self.attn_out), self.out.symm], self.out_flags.symm,
             self.out_counters.data_ptr())
+        # ---- the same outbound plan as the kernel's producer role: one slab of query rows per target
+        units = B * self.Hl * ((self.S + 255) // 256)
+        self.push = None
+        if overlap_out and W > 1 and units <= _L.ATTN_PLAN_MAX_UNITS and S_local % 128 == 0 and D == 128:
+            slabs = []
+            rows = zip(self.out_schedule.gen_block_offset_lists(), self.out_schedule.gen_block_shape_lists(),
+                       self.out_schedule.gen_target_rank_list(), self.out_schedule.gen_dst_offset_lists(), sig)
+            head_offset = None
+            for off, shp, tgt, poff, rsig in rows:
+                head_offset = poff[2] if head_offset is None else head_offset
+                if (off[0], off[2], off[3]) != (0, 0, 0) or (shp[0], shp[2], shp[3]) != (B, self.Hl, D) or poff[2] != head_offset:
+                    slabs = None
+                    break
+                slabs.append((off[1], shp[1], self.rank if tgt < 0 else tgt, poff[1], rsig))
+            if slabs:
+                slabs.sort()
+                arr = (_L.AttnPushSlab * len(slabs))()
+                for i, (q0, qn, dst, row0, flag) in enumerate(slabs):
+                    arr[i].q_begin, arr[i].q_rows, arr[i].dst_rank, arr[i].dst_row0, arr[i].flag = q0, qn, dst, row0, flag
+                self.push_counters = torch.zeros(8, dtype=torch.int32, device=ctx.device)
+                push = _L.AttnPush()
+                push.num_slabs = len(slabs)
+                push.slabs = _C.cast(arr, _C.POINTER(_L.AttnPushSlab))
+                push.dst = self.out.symm
+                push.dst_strides = (_C.c_int64 * 3)(S_local * H * D, H * D, D)
+                push.dst_rows, push.dst_heads, push.head_offset = S_local, H, head_offset
+                push.flags = self.out_flags.symm
+                push.counters = self.push_counters.data_ptr()
+                self.push, self._keep_push = push, arr
         self.epoch = 0
 
-    def launch_attention(self, stream=None):
-        """Inbound all-to-all fused with attention; fills ``attn_out``."""
+    def launch_attention(self, stream=None, push: bool = False):
+        """Inbound all-to-all fused with attention; fills ``attn_out`` - or, with ``push``, sends every
+        tile's final rows to ``out`` on their rank and raises the slabs' flags there."""
         self.epoch += 1
         if self.lockstep and self.world > 1:
             self.ctx.barrier(stream)  # every peer's qkv_src is written before anybody pulls from it
@@ -507,7 +543,7 @@ class UlyssesAttention:
         attention_forward(q, k, v, self.sm_scale, self.attn_out.permute(0, 2, 1, 3), wave_offsets=offs,
                           wave_sizes=sizes, signal_ptr=self.in_flags.local, signal_offsets=sigs, causal=self.causal,
                           state=self.state, signal_value=self.epoch, comm=self.in_comm, timeout_ns=self.timeout_ns,
-                          status=self.ctx.status, stream=stream)
+                          status=self.ctx.status, stream=stream, push=self.push if push else None)
 
     def launch_scatter(self, stream=None):
         """Outbound all-to-all: pushes ``attn_out`` slabs to their ranks and raises their flags."""
@@ -523,8 +559,11 @@ class UlyssesAttention:
                                             self.ctx.status.data_ptr(), i, s), "syn_flag_wait")
 
     def __call__(self, stream=None) -> torch.Tensor:
-        self.launch_attention(stream)
-        self.launch_scatter(stream)
+        if self.push is not None:
+            self.launch_attention(stream, push=True)
+        else:
+            self.launch_attention(stream)
+            self.launch_scatter(stream)
         self.wait_output(stream)
         if self.sync_after and self.world > 1:
             self.ctx.barrier(stream)

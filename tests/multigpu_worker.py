@@ -155,23 +155,27 @@ def main():
         return out
 
     B, H, Sl = 1, 2 * world, 256
-    op = UlyssesAttention(ctx, B, H, Sl, 128, dt, causal=True, timeout_ns=2_000_000_000)
     qkv = seeded(7000 + rank, (3, B, H, Sl, 128), 1.0, dt, dev)
     gathered = [torch.empty_like(qkv) for _ in range(world)]
     dist.all_gather(gathered, qkv)
     full = torch.cat(gathered, dim=3)  # [3, B, H, S, D]
-    for it in range(2):
-        op.qkv_src.local.copy_(qkv)
-        torch.cuda.synchronize()
-        ctx.barrier()
-        out = op()
-        ctx.check()
-        ref = dense(full[0, 0], full[1, 0], full[2, 0], True)[:, rank * Sl : (rank + 1) * Sl].permute(1, 0, 2)
-        e = (out[0].float() - ref).abs().max().item()
-        if not e < 2e-2:
-            failures.append(f"ulysses it={it} rank={rank}: maxabs={e:.3e}")
-        ctx.barrier()
-        torch.cuda.synchronize()
+    ref = dense(full[0, 0], full[1, 0], full[2, 0], True)[:, rank * Sl : (rank + 1) * Sl].permute(1, 0, 2)
+    for overlap in (True, False):  # the kernel sends finished tiles itself / a copy kernel follows it
+        op = UlyssesAttention(ctx, B, H, Sl, 128, dt, causal=True, timeout_ns=2_000_000_000, overlap_out=overlap)
+        assert (op.push is not None) == overlap
+        for it in range(3):
+            op.qkv_src.local.copy_(qkv)
+            op.out.local.fill_(float("nan"))
+            torch.cuda.synchronize()
+            ctx.barrier()
+            out = op()
+            ctx.check()
+            e = (out[0].float() - ref).abs().max().item()
+            if not e < 2e-2:
+                failures.append(f"ulysses overlap_out={overlap} it={it} rank={rank}: maxabs={e:.3e}")
+            ctx.barrier()
+            torch.cuda.synchronize()
+        del op
 
     for plan in ("swizzle", "ring", "double_ring"):
         Hq, Hkv = 8, 2

@@ -331,3 +331,44 @@ def test_cfg4_rank0_sampled_rows(kernel_choice):
                                                    full[1, 0, h // (Hq // Hkv)], rows, q_pos, k_pos))
     print(f"cfg4 rank 0 (8 waves per row), sampled tiles: max-abs {worst:.2e}")
     assert worst < TOL
+
+
+@pytest.mark.parametrize("kernel_choice", ["two_tile"], indirect=True)
+@pytest.mark.parametrize("world,B,H,S_local,causal,num_sms", [(2, 1, 4, 256, True, 0), (4, 2, 4, 128, False, 0),
+                                                              (2, 1, 2, 512, True, 3), (4, 1, 8, 256, True, 0)])
+def test_ulysses_operator_pushes_finished_tiles(kernel_choice, world, B, H, S_local, causal, num_sms, monkeypatch):
+    """The attention kernel in its producer role: every query tile's final rows go straight to the
+    rank that owns them, at the tile's last visit (earlier visits merge through the local buffer),
+    and a slab's flag is raised by the tile that completes it.  All ranks run one after the other on
+    one GPU; with three CTAs a CTA owns several tile pairs, which it visits wave after wave."""
+    from syncopate_b200.operators import UlyssesAttention
+    from syncopate_b200.runtime import EmulatedWorld
+    import syncopate_b200.computation.attn as attn_mod
+
+    if num_sms:
+        real = attn_mod.attention_forward
+        monkeypatch.setattr("syncopate_b200.operators.attention_forward",
+                            lambda *a, **kw: real(*a, **{**kw, "num_sms": num_sms}))
+    ew = EmulatedWorld(world)
+    ops = [UlyssesAttention(c, B, H, S_local, 128, DT, causal=causal, timeout_ns=500_000_000, overlap_out=True)
+           for c in ew.contexts]
+    assert all(op.push is not None for op in ops)
+    qkv = [_seeded(80 + r, (3, B, H, S_local, 128)) for r in range(world)]
+    for r in range(world):
+        ops[r].qkv_src.local.copy_(qkv[r].cuda())
+    full = torch.cat(qkv, dim=3)
+    want = torch.stack([E.attention_dense(full[0, b], full[1, b], full[2, b], 128 ** -0.5, causal=causal)[0]
+                        for b in range(B)])  # [B, H, S, D]
+    for it in range(2):
+        for op in ops:
+            op.out.local.fill_(float("nan"))
+        for op in ops:
+            op.launch_attention(push=True)      # no copy kernel behind it
+        torch.cuda.synchronize()
+        for r, op in enumerate(ops):
+            op.ctx.check()
+            assert op.out_flags.local[:op.out_info.recv_signal_num].tolist() == [it + 1] * op.out_info.recv_signal_num
+            assert int(op.push_counters.abs().sum()) == 0
+            got = op.out.local.float().cpu()  # [B, S/W, H, D]
+            ref = want[:, :, r * S_local : (r + 1) * S_local].permute(0, 2, 1, 3)
+            assert (got - ref).abs().max().item() < TOL
