@@ -316,20 +316,21 @@ def run_own_arm(args):
                 "blocks": n_blocks, "steps_per_block": n_steps}
 
     def capture_trace(operator, call, rows, signals):
-        """Runs ``call`` three times with the kernel's wait stamps switched on and returns the last
-        call's per-wave rows and the kernel's duration (us)."""
+        """Per-wave wait stamps of one call in steady state: four calls back to back without a
+        synchronisation in between, the kernel's stamps switched on for the last one (a call made
+        on an idle GPU would give its transfers a head start over the kernel).  Returns the rows and
+        the kernel's duration (us)."""
         nw = len(rows)
         big = torch.iinfo(torch.int64).max
-        tr = None
-        for _ in range(3):
-            tr = torch.zeros(2 + 3 * nw, dtype=torch.int64, device=dev)
-            tr[0] = big
-            tr[2::3] = big
-            operator.trace = tr
-            sync_all()
+        tr = torch.zeros(2 + 3 * nw, dtype=torch.int64, device=dev)
+        tr[0] = big
+        tr[2::3] = big
+        sync_all()
+        for i in range(4):
+            operator.trace = tr if i == 3 else None
             call()
-            torch.cuda.synchronize()
         operator.trace = None
+        torch.cuda.synchronize()
         t = tr.tolist()
         out = [{"wave": w, "rows": rows[w], "flag": signals[w],
                 "wait_begin_us": (t[2 + 3 * w] - t[0]) / 1e3 if t[2 + 3 * w] != big else None,
@@ -347,7 +348,7 @@ def run_own_arm(args):
     shard_seed = lambda r: seeded(1000 + r, (ROWS, K_DIM), 1.0, dt)
     if world > 1:
         op = AllGatherGemm(ctx, ROWS, K_DIM, n_local, dt, plan="swizzle", comm=args.comm, chunk_split=args.chunk_split,
-                           copy_streams=args.copy_streams)
+                           copy_streams=args.copy_streams, transfer=args.ag_transfer if args.comm == "ce" else "pull")
         op.shard.copy_(shard_seed(rank).to(dev))
         step = lambda: op(b, c)
         kernels_per_step = 2  # the GEMM kernel and the lockstep barrier kernel
@@ -431,7 +432,8 @@ def run_own_arm(args):
         # and so finished pulling what step i - 3 left in that shard.
         a_host = shard_seed(rank).pin_memory()
         sets = [op] + [AllGatherGemm(ctx, ROWS, K_DIM, n_local, dt, plan="swizzle", comm=args.comm,
-                                     chunk_split=args.chunk_split, copy_streams=args.copy_streams) for _ in range(2)]
+                                     chunk_split=args.chunk_split, copy_streams=args.copy_streams,
+                                     transfer=args.ag_transfer if args.comm == "ce" else "pull") for _ in range(2)]
         ev_in = [torch.cuda.Event() for _ in range(3)]
         ev_comp = [torch.cuda.Event() for _ in range(3)]
         e2e_path = ("pinned host A shard -> symmetric device shard, fused operator, C -> pinned host; three operator "
@@ -747,9 +749,10 @@ def run_own_arm(args):
         }
         if trace_rows is not None:
             line["overlap_trace"] = {"kernel_us": kernel_us, "waves": trace_rows,
-                                     "note": "one call of the headline operator on rank 0: per wave, earliest flag-wait "
-                                             "begin and latest end over CTAs (us from the kernel's start) and the wait "
-                                             "summed over CTAs"}
+                                     "note": "one call of the headline operator on rank 0 in steady state (fourth of four "
+                                             "back-to-back calls): per wave, earliest flag-wait begin and latest end over "
+                                             "CTAs (us from the kernel's start) and the wait summed over CTAs; a wave's "
+                                             "latest end is also set by CTAs that reach the wave late"}
         if rs_trace_rows is not None:
             line["other_ops"]["gemm_rs"]["overlap_trace"] = {
                 "kernel_us": rs_kernel_us, "waves": rs_trace_rows,
@@ -779,10 +782,12 @@ def main():
     ap.add_argument("--comm", default="ce", choices=["sm", "ce"],
                     help="who moves the all-gather chunks: the kernel's comm warps (sm) or copy engines (ce)")
     ap.add_argument("--chunk-split", type=int, default=2, help="row pieces per remote all-gather slab")
+    ap.add_argument("--ag-transfer", default="pull", choices=["pull", "push"],
+                    help="copy-engine all-gather: receivers pull, or owners push")
     ap.add_argument("--rs-comm", default="ce", choices=["sm", "ce"],
                     help="GEMM+RS transport: the epilogue's TMA stores (sm) or copy engines (ce)")
-    ap.add_argument("--rs-split", type=int, default=2, help="row pieces per reduce-scatter slab")
-    ap.add_argument("--ar-splits", type=int, default=4, help="row slices of GEMM+AR (separate launches)")
+    ap.add_argument("--rs-split", type=int, default=1, help="row pieces per reduce-scatter slab")
+    ap.add_argument("--ar-splits", type=int, default=1, help="row slices of GEMM+AR (separate launches)")
     ap.add_argument("--copy-streams", type=int, default=2)
     args = ap.parse_args()
     if args.impl == "reference":

@@ -119,7 +119,13 @@ typedef struct syn_gemm_args {
 /* Un-fused / flag-gated persistent GEMM on one GPU.  `sched` may be NULL (one wave = whole C);
  * `producer_sched` is the RawSchedule of C when the GEMM feeds communication (may be NULL).
  * When both are given they must describe the same tile order (same shapes), as in the reference's
- * dual-role kernels (syncopate/computation/transform/transformer.py:1086-1116). */
+ * dual-role kernels (syncopate/computation/transform/transformer.py:1086-1116).
+ * `sched` may also have ndim = 3 with axes (M, N, K), the consumer form of all-to-all + GEMM
+ * (tests/test_all2all_gemm.py:83-110 builds exactly these waves): every wave covers all of C and one
+ * range of K (multiples of 64, disjoint, together all of K), A's columns of that range being valid
+ * once signal_ptr[signals[w]] >= signal_value.  Every tile then accumulates over the ranges in
+ * wave order, waiting for a range's flag before its first load from it (at most 16 ranges; not
+ * together with producer_sched). */
 int syn_gemm(const syn_gemm_args* args, const syn_schedule* sched, const syn_schedule* producer_sched,
              void* stream);
 
@@ -135,6 +141,13 @@ int syn_gemm(const syn_gemm_args* args, const syn_schedule* sched, const syn_sch
  * device share the array: two calls that may overlap on the GPU (different streams) race. */
 int syn_gemm_noalloc(const syn_gemm_args* args, const syn_schedule* sched, const syn_schedule* producer_sched,
                      void* stream);
+
+/* The same GEMM in its consumer role with the schedule given in closed form (the reference's
+ * Mod1DSchedule, syncopate/interface/tile_schedule.py:214-266: what SimplifiedSchedule reduces the
+ * schedule of a ring or swizzled direct all-gather to): num_waves equal blocks of `stride` rows
+ * (axis 0) or columns (axis 1), block w at (starting_offset + w * stride) mod (stride * num_waves),
+ * the first resident and block w > 0 waiting for flag w - 1 of args->consumer_signal_ptr. */
+int syn_gemm_mod1d(const syn_gemm_args* args, int num_waves, int stride, int starting_offset, int axis, void* stream);
 
 /* Smallest persistent-grid tail for an M x N output on `num_sms` SMs: returns the block_n the
  * library would choose for block_n = 0. */
@@ -160,7 +173,9 @@ typedef struct syn_symm {
 } syn_symm;
 
 int syn_ctx_create(int rank, int world, int device, const char* rendezvous_dir, syn_ctx** out);
-/* Unmaps peers, frees local buffers, removes this rank's rendezvous files.  Never blocks on peers. */
+/* Unmaps peers, frees local buffers, removes this rank's rendezvous files.  Never blocks on peers:
+ * call it on every rank after a syn_barrier and a synchronisation of the streams in use, so that no
+ * peer's kernel or copy still touches a buffer that is being freed. */
 int syn_ctx_destroy(syn_ctx* ctx);
 /* Collective: allocates `bytes` (zero-filled) on every rank and fills `out` with all ranks' pointers.
  * Waits at most `timeout_s` seconds for the peers (0 = 120 s) and returns SYN_ERR_RENDEZVOUS after. */

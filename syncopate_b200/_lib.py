@@ -298,6 +298,8 @@ def _declare(l: C.CDLL) -> None:
     l.syn_gemm.argtypes = [C.POINTER(GemmArgs), C.POINTER(Schedule), C.POINTER(Schedule), C.c_void_p]
     l.syn_gemm_noalloc.restype = C.c_int
     l.syn_gemm_noalloc.argtypes = [C.POINTER(GemmArgs), C.POINTER(Schedule), C.POINTER(Schedule), C.c_void_p]
+    l.syn_gemm_mod1d.restype = C.c_int
+    l.syn_gemm_mod1d.argtypes = [C.POINTER(GemmArgs), C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p]
     l.syn_gemm_pick_block_n.restype = C.c_int
     l.syn_gemm_pick_block_n.argtypes = [C.c_int, C.c_int, C.c_int]
     l.syn_ctx_create.restype = C.c_int

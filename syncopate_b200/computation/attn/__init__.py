@@ -49,6 +49,7 @@ def _tolist(x):
     return x
 
 
+_PLAN_MAX_PAIRS_PER_CTA = 8
 _PLANS: dict = {}  # configuration key -> AttnPlan, or None where the library declined to plan
 _PLANS_MAX = 256
 
@@ -141,6 +142,14 @@ def attention_forward(
         if not balance:
             raise ValueError("the producer role needs the planned ownership (balance=True)")
         a.push = C.addressof(push)
+    if balance and push is None:
+        # Planned ownership pays when a CTA holds only a few tile pairs of different length (cfg3 per
+        # rank: 3.5 per CTA, 1.01 ms planned against 1.13 ms arithmetic); with many pairs per CTA the
+        # arithmetic rule balances as well and keeps neighbouring CTAs on the same heads (cfg4 per rank:
+        # 13.8 per CTA, 8.8 ms arithmetic against 9.5 ms planned).
+        sms = num_sms or torch.cuda.get_device_properties(q.device).multi_processor_count
+        if Z * Hq * ((Sq + 255) // 256) > _PLAN_MAX_PAIRS_PER_CTA * sms:
+            balance = False
     if balance:
         key = (os.environ.get("SYNCOPATE_B200_ATTN_TWO_TILE"), push is not None, Z, Hq, Hkv, Sq, Skv, bool(causal), num_sms, tuple(map(tuple, offs)), tuple(map(tuple, sizes)),
                None if q_pos is None else (q_pos.data_ptr(), q_pos._version),

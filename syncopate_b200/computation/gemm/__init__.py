@@ -123,7 +123,9 @@ def gemm(
 ) -> torch.Tensor:
     """``c = a @ b.T`` with fp32 accumulation.
 
-    ``cur_wave_sizes`` / ``wave_offsets`` (``[W, 2]``, elements) give the wave order;
+    ``cur_wave_sizes`` / ``wave_offsets`` (``[W, 2]``, elements) give the wave order (``[W, 3]`` rows
+    are waves over (M, N, K): every wave all of C and one range of K, the consumer form of
+    all-to-all + GEMM, as tests/test_all2all_gemm.py:83-110 of the reference builds them);
     ``signal_ptr`` + ``signal_offsets`` make each wave wait for its flag (consumer role);
     ``producer_signal_ptr`` + ``producer_signal_offsets`` + ``counter_ptr`` make each wave raise its
     flag after its last tile (producer role).  ``BLOCK_SIZE_N = 0`` lets the library choose the tile
@@ -139,7 +141,9 @@ def gemm(
     cons = prod = None
     sizes, offs = _to_list(cur_wave_sizes), _to_list(wave_offsets)
     if sizes is not None:
-        s, k = L.make_schedule(offs, sizes, _to_list(signal_offsets))
+        # rows of three numbers are waves over (M, N, K): ranges of K that arrive separately
+        ndim = len(sizes[0]) if len(sizes) and isinstance(sizes[0], (list, tuple)) else 2
+        s, k = L.make_schedule(offs, sizes, _to_list(signal_offsets), ndim=ndim)
         keep.append(k)
         cons = s
         g.consumer_signal_ptr = _ptr(signal_ptr)
@@ -154,6 +158,22 @@ def gemm(
         _stream_ptr(stream),
     )
     L.check(rc, "syn_gemm")
+    return c
+
+
+def gemm_mod1d(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, schedule, signal_ptr, *, signal_value: int = 1,
+               num_sms: int = 0, block_n: int = 0, timeout_ns: int = 0, status=None, stream=None) -> torch.Tensor:
+    """Flag-gated GEMM whose wave schedule is given in closed form: ``schedule`` is a
+    ``Mod1DSchedule`` (what ``SimplifiedSchedule(raw).simplify()`` finds for ring and swizzled direct
+    all-gathers, syncopate/interface/tile_schedule.py:178-266) or a tuple ``(num_waves, stride,
+    starting_offset, axis)``.  No schedule arrays cross the boundary; the library expands the form."""
+    if hasattr(schedule, "num_waves"):
+        form = (schedule.num_waves, schedule.stride, schedule.starting_offset, schedule.schedule_axis)
+    else:
+        form = tuple(int(x) for x in schedule)
+    g = _gemm_args(a, b, c, num_sms, block_n, 8, signal_value, timeout_ns, status, stream)
+    g.consumer_signal_ptr = _ptr(signal_ptr)
+    L.check(L.lib().syn_gemm_mod1d(C.byref(g), form[0], form[1], form[2], form[3], _stream_ptr(stream)), "syn_gemm_mod1d")
     return c
 
 
@@ -261,4 +281,4 @@ def _schedule_struct(schedule, ndim: int = 2):
     return L.make_schedule(parts[0], parts[1], parts[2], parts[3], parts[4], ndim=ndim)
 
 
-__all__ = ["gemm", "ag_gemm", "gemm_rs"]
+__all__ = ["gemm", "gemm_mod1d", "ag_gemm", "gemm_rs"]

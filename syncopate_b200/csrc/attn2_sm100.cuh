@@ -508,10 +508,11 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
         if (both && !wait(&turn[x], x == 0 ? ((turns & 1u) ^ 1u) : (turns & 1u))) break;
         const uint64_t scale2 = f2_pack(p.scale_log2, p.scale_log2), negm2 = f2_pack(neg_m, neg_m);
         uint64_t ls2[2] = {0ull, 0ull};  // packed (0.f, 0.f)
-#pragma unroll
-        for (int c = 0; c < ATTN_BN / 32; ++c) {
-          // in place, stage by stage over the 32 values of the chunk, so that the independent
-          // exponentials are issued back to back instead of one dependent chain per pair
+        // One chunk = 32 values: scale (packed FMA) and exponentiate in place.  The exponentials of
+        // chunk c + 1 are issued BEFORE chunk c is summed, packed and stored, so that those consumers
+        // sit in the same instruction window as the next chunk's independent exponentials (measured
+        // neutral at S = 32768: 1.0147 ms with, 1.0146 ms without).
+        auto scale_exp = [&](int c) {
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             float x0, x1;
@@ -522,6 +523,11 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
           }
 #pragma unroll
           for (int i = 0; i < 32; ++i) sr[c][i] = __float_as_uint(ex2_approx(__uint_as_float(sr[c][i])));
+        };
+        scale_exp(0);
+#pragma unroll
+        for (int c = 0; c < ATTN_BN / 32; ++c) {
+          if (c + 1 < ATTN_BN / 32) scale_exp(c + 1);
           uint32_t pk[16];
 #pragma unroll
           for (int i = 0; i < 16; ++i) {

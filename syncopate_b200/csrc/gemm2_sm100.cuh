@@ -209,6 +209,7 @@ gemm2_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUten
       int stage = 0;
       uint32_t phase = 0;
       uint32_t issued = 0;
+      int gates_passed = 0;
       bool first = true;
       bool gave_up = false;
       PairWork wk;
@@ -238,19 +239,41 @@ gemm2_kernel(const __grid_constant__ GemmParams p, const __grid_constant__ CUten
         }
         const int row0 = m2_blk * GEMM2_BM + static_cast<int>(cta_rank) * GEMM_BM;
         const int col0 = n_blk * BN + static_cast<int>(cta_rank) * (BN / 2);
-        for (int kb = wk.kb0; kb < wk.kb1 && !gave_up; ++kb) {
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_word, p.timeout_ns)) {
-            gave_up = true;
-            break;
+        // (K gates and K slices of tail tiles do not occur together: the host splits no tail then)
+        const int ranges = p.num_kgates > 0 ? p.num_kgates : 1;
+        for (int g = 0; g < ranges && !gave_up; ++g) {
+          int kb_lo = wk.kb0, kb_hi = wk.kb1;
+          if (p.num_kgates > 0) {
+            kb_lo = p.kgate_kb0[g];
+            kb_hi = p.kgate_kb1[g];
+            if (g >= gates_passed) {
+              if (p.kgate_sig[g] >= 0 && p.csig != nullptr &&
+                  !flag_wait_ge(p.csig + p.kgate_sig[g], p.signal_value, abort_word, p.timeout_ns)) {
+                if (abort_info[0] < 0) {
+                  abort_info[0] = g;
+                  abort_info[1] = p.kgate_sig[g];
+                }
+                gave_up = true;
+                break;
+              }
+              fence_proxy_async();
+              gates_passed = g + 1;
+            }
           }
-          if (leader) mbar_expect_tx(&full_bar[stage], 2 * STAGE_BYTES);
-          const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
-          tma_load_2d_pair(sA + stage * A_BYTES, &p.tmap_a, bar, kb * GEMM_BK, row0);
-          tma_load_2d_pair(sB + stage * B_BYTES, &tmap_b_half, bar, kb * GEMM_BK, col0);
-          ++issued;
-          if (++stage == STAGES) {
-            stage = 0;
-            phase ^= 1u;
+          for (int kb = kb_lo; kb < kb_hi; ++kb) {
+            if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_word, p.timeout_ns)) {
+              gave_up = true;
+              break;
+            }
+            if (leader) mbar_expect_tx(&full_bar[stage], 2 * STAGE_BYTES);
+            const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
+            tma_load_2d_pair(sA + stage * A_BYTES, &p.tmap_a, bar, kb * GEMM_BK, row0);
+            tma_load_2d_pair(sB + stage * B_BYTES, &tmap_b_half, bar, kb * GEMM_BK, col0);
+            ++issued;
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1u;
+            }
           }
         }
       }

@@ -259,7 +259,7 @@ int gemm_launch_pair(const GemmParams& p_in, const syn_gemm_args* a, int bn, int
   memset(&tail, 0, sizeof(tail));
   const int pairs = g / 2;
   const int rem = pair_tiles % pairs, rounds = pair_tiles / pairs;
-  if (!routed && a->workspace != nullptr && rounds >= 1 && rem > 0 && rem * 4 <= pairs) {
+  if (!routed && p.num_kgates == 0 && a->workspace != nullptr && rounds >= 1 && rem > 0 && rem * 4 <= pairs) {
     const int slices = std::min(std::min(pairs / rem, p.k_blocks), 32);
     const size_t need = 256 + static_cast<size_t>(rem) * slices * GEMM2_BM * bn * sizeof(float);
     if (slices >= 2 && a->workspace_bytes >= need && (reinterpret_cast<uintptr_t>(a->workspace) & 255) == 0) {
@@ -321,9 +321,65 @@ int gemm_resolve_grid_and_bn(const syn_gemm_args* a, const syn_schedule* sched, 
   return SYN_OK;
 }
 
+// A consumer schedule over (M, N, K): every wave covers all of C and one range of K (A arrives as
+// column ranges, e.g. behind an all-to-all that splits the contraction axis).  The ranges become
+// the kernel's K gates, in wave (= arrival) order.
+int fill_kgates(GemmParams* p, const syn_gemm_args* a, const syn_schedule* s) {
+  if (s->num_waves <= 0 || s->offsets == nullptr || s->shapes == nullptr) return SYN_ERR_INVALID;
+  if (s->num_waves > GEMM_MAX_KGATES) return SYN_ERR_TOO_LARGE;
+  long covered = 0;
+  for (int w = 0; w < s->num_waves; ++w) {
+    const int32_t* off = s->offsets + 3 * w;
+    const int32_t* shp = s->shapes + 3 * w;
+    if (off[0] != 0 || off[1] != 0 || shp[0] != a->M || shp[1] != a->N) return SYN_ERR_UNSUPPORTED;
+    if (off[2] < 0 || shp[2] <= 0 || off[2] + shp[2] > a->K) return SYN_ERR_SHAPE;
+    if (off[2] % GEMM_BK != 0) return SYN_ERR_SHAPE;
+    if (shp[2] % GEMM_BK != 0 && off[2] + shp[2] != a->K) return SYN_ERR_SHAPE;
+    for (int v = 0; v < w; ++v) {  // ranges must not overlap
+      const int o2 = s->offsets[3 * v + 2], n2 = s->shapes[3 * v + 2];
+      if (off[2] < o2 + n2 && o2 < off[2] + shp[2]) return SYN_ERR_SHAPE;
+    }
+    const int sig = s->signals ? s->signals[w] : -1;
+    if (sig > 32767) return SYN_ERR_TOO_LARGE;
+    p->kgate_kb0[w] = static_cast<int16_t>(off[2] / GEMM_BK);
+    p->kgate_kb1[w] = static_cast<int16_t>((off[2] + shp[2] + GEMM_BK - 1) / GEMM_BK);
+    p->kgate_sig[w] = static_cast<int16_t>(a->consumer_signal_ptr != nullptr ? sig : -1);
+    covered += shp[2];
+  }
+  if (covered != a->K) return SYN_ERR_SHAPE;
+  p->num_kgates = s->num_waves;
+  return SYN_OK;
+}
+
 }  // namespace syn
 
 extern "C" {
+
+int syn_gemm_mod1d(const syn_gemm_args* args, int num_waves, int stride, int starting_offset, int axis, void* stream) {
+  // closed form -> wave table: block w starts at (starting_offset + w * stride) mod (stride * num_waves)
+  // along `axis`, spans the other axis, and waits for flag w - 1 (the first block is resident)
+  if (args == nullptr || num_waves <= 0 || num_waves > SYN_MAX_WAVES || stride <= 0 || starting_offset < 0) return SYN_ERR_INVALID;
+  if (axis != 0 && axis != 1) return SYN_ERR_UNSUPPORTED;
+  const long extent = static_cast<long>(stride) * num_waves;
+  if (extent != (axis == 0 ? args->M : args->N) || starting_offset % stride != 0 || starting_offset >= extent) return SYN_ERR_SHAPE;
+  int32_t offs[2 * SYN_MAX_WAVES], shapes[2 * SYN_MAX_WAVES], sigs[SYN_MAX_WAVES];
+  for (int w = 0; w < num_waves; ++w) {
+    const int at = static_cast<int>((starting_offset + static_cast<long>(w) * stride) % extent);
+    offs[2 * w + axis] = at;
+    offs[2 * w + 1 - axis] = 0;
+    shapes[2 * w + axis] = stride;
+    shapes[2 * w + 1 - axis] = axis == 0 ? args->N : args->M;
+    sigs[w] = w - 1;
+  }
+  syn_schedule s;
+  memset(&s, 0, sizeof(s));
+  s.num_waves = num_waves;
+  s.ndim = 2;
+  s.offsets = offs;
+  s.shapes = shapes;
+  s.signals = sigs;
+  return syn_gemm(args, &s, nullptr, stream);
+}
 
 int syn_gemm_pick_block_n(int M, int N, int num_sms) {
   if (M <= 0 || N <= 0 || num_sms <= 0) return SYN_ERR_INVALID;
@@ -334,6 +390,12 @@ int syn_gemm(const syn_gemm_args* args, const syn_schedule* sched, const syn_sch
              void* stream) {
   using namespace syn;
   if (args == nullptr) return SYN_ERR_INVALID;
+  // a consumer schedule over (M, N, K) gates ranges of K; the tiles then walk C as one wave
+  const syn_schedule* kgates = (sched != nullptr && sched->ndim == 3) ? sched : nullptr;
+  if (kgates != nullptr) {
+    if (producer_sched != nullptr) return SYN_ERR_UNSUPPORTED;
+    sched = nullptr;
+  }
   int grid = 0, bn = 0;
   bool want_pair = false;
   int rc = gemm_resolve_grid_and_bn(args, sched ? sched : producer_sched, &grid, &bn, 32,
@@ -343,6 +405,10 @@ int syn_gemm(const syn_gemm_args* args, const syn_schedule* sched, const syn_sch
   GemmParams p;
   rc = gemm_fill_common(&p, args, order, bn);
   if (rc != SYN_OK) return rc;
+  if (kgates != nullptr) {
+    rc = fill_kgates(&p, args, kgates);
+    if (rc != SYN_OK) return rc;
+  }
   bool fused = false;
   if (producer_sched != nullptr && args->producer_signal_ptr != nullptr) {
     if (args->producer_counter_ptr == nullptr) return SYN_ERR_INVALID;

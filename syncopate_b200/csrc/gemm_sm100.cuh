@@ -34,6 +34,7 @@ constexpr int EPI_STAGE_BYTES = 32 * 128;     // one epilogue warp's 32 rows x 6
 static_assert(COMM_PIECE * COMM_NBUF >= 4 * 2 * EPI_STAGE_BYTES,
               "the routed epilogue stages two 32 x 64 16-bit pieces per epilogue warp there");
 constexpr int GEMM_MAX_RED = 7;               // staged partial slabs an owner wave can add (world - 1)
+constexpr int GEMM_MAX_KGATES = 16;           // K ranges of A that arrive separately (all-to-all + GEMM)
 
 struct GemmWave {
   int16_t tiles_m, tiles_n;  // tile grid of the wave
@@ -95,6 +96,11 @@ struct GemmParams {
   uint64_t signal_value;
   uint64_t timeout_ns;
   int32_t* status;
+  // K gates (all-to-all + GEMM): A arrives as ranges of K, each with a flag; every tile walks the
+  // ranges in arrival order and waits for a range's flag before its first load from it
+  int32_t num_kgates;                 // 0 = K is walked front to back, ungated
+  int16_t kgate_kb0[GEMM_MAX_KGATES], kgate_kb1[GEMM_MAX_KGATES];  // k-block range [kb0, kb1)
+  int16_t kgate_sig[GEMM_MAX_KGATES]; // consumer flag index, -1 = resident
   const void* red_src[GEMM_MAX_RED];  // staged slabs (address of the slab's row 0)
   const uint64_t* red_flags;          // local flag array the reduce waves' red_sig index
   GemmWave waves[GEMM_MAX_WAVES];
@@ -382,6 +388,7 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
       int stage = 0;
       uint32_t phase = 0;
       uint32_t issued = 0;  // k-block loads issued so far
+      int gates_passed = 0;  // K ranges whose flag this CTA has seen up
       bool first = true;
       bool gave_up = false;
       for (uint32_t n = 0; !gave_up; ++n) {
@@ -418,18 +425,40 @@ gemm_kernel(const __grid_constant__ GemmParams p) {
           }
           first = false;
         }
-        for (int kb = 0; kb < p.k_blocks && !gave_up; ++kb) {
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_word, p.timeout_ns)) {
-            gave_up = true;  // somebody in the CTA gave up: the stage may never be released
-            break;
+        const int ranges = p.num_kgates > 0 ? p.num_kgates : 1;
+        for (int g = 0; g < ranges && !gave_up; ++g) {
+          int kb_lo = 0, kb_hi = p.k_blocks;
+          if (p.num_kgates > 0) {
+            kb_lo = p.kgate_kb0[g];
+            kb_hi = p.kgate_kb1[g];
+            if (g >= gates_passed) {
+              // first tile of this CTA that reaches the range: its flag must be up
+              if (p.kgate_sig[g] >= 0 && p.csig != nullptr &&
+                  !flag_wait_ge(p.csig + p.kgate_sig[g], p.signal_value, abort_word, p.timeout_ns)) {
+                if (abort_info[0] < 0) {
+                  abort_info[0] = g;
+                  abort_info[1] = p.kgate_sig[g];
+                }
+                gave_up = true;
+                break;
+              }
+              fence_proxy_async();
+              gates_passed = g + 1;
+            }
           }
-          mbar_expect_tx(&full_bar[stage], L::STAGE_BYTES);
-          tma_load_2d(sA + stage * L::A_BYTES, &p.tmap_a, &full_bar[stage], kb * GEMM_BK, m_blk * GEMM_BM);
-          tma_load_2d(sB + stage * L::B_BYTES, &p.tmap_b, &full_bar[stage], kb * GEMM_BK, n_blk * BN);
-          ++issued;
-          if (++stage == STAGES) {
-            stage = 0;
-            phase ^= 1u;
+          for (int kb = kb_lo; kb < kb_hi; ++kb) {
+            if (!mbar_wait(&empty_bar[stage], phase ^ 1u, abort_word, p.timeout_ns)) {
+              gave_up = true;  // somebody in the CTA gave up: the stage may never be released
+              break;
+            }
+            mbar_expect_tx(&full_bar[stage], L::STAGE_BYTES);
+            tma_load_2d(sA + stage * L::A_BYTES, &p.tmap_a, &full_bar[stage], kb * GEMM_BK, m_blk * GEMM_BM);
+            tma_load_2d(sB + stage * L::B_BYTES, &p.tmap_b, &full_bar[stage], kb * GEMM_BK, n_blk * BN);
+            ++issued;
+            if (++stage == STAGES) {
+              stage = 0;
+              phase ^= 1u;
+            }
           }
         }
       }

@@ -8,6 +8,8 @@
 // plugin loaded into a host that forbids allocation after initialisation.  For them the scratch
 // lives in this library's image instead: a file-scope device array, one copy per GPU that loads the
 // library, held until the process exits.
+#include <atomic>
+
 #include "gemm_host.h"
 
 namespace {
@@ -16,7 +18,9 @@ namespace {
 __device__ __align__(256) uint32_t g_wave_counters[SYN_MAX_WAVES];
 
 constexpr int kMaxDevices = 64;
-uint32_t* g_counters_addr[kMaxDevices];  // device address of g_wave_counters, per device, 0 = not set up
+// device address of g_wave_counters, per device, null = not looked up yet (two host threads that
+// look it up at the same time store the same value)
+std::atomic<uint32_t*> g_counters_addr[kMaxDevices];
 
 }  // namespace
 
@@ -30,15 +34,15 @@ extern "C" int syn_gemm_noalloc(const syn_gemm_args* args, const syn_schedule* s
   int dev = -1;
   SYN_CUDA_TRY(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kMaxDevices) return SYN_ERR_UNSUPPORTED;
-  if (g_counters_addr[dev] == nullptr) {
+  if (g_counters_addr[dev].load(std::memory_order_acquire) == nullptr) {
     // In host code the array's name is only a handle; the address kernels can use has to be asked
     // for, once per device, with that device current.
     void* p = nullptr;
     SYN_CUDA_TRY(cudaGetSymbolAddress(&p, g_wave_counters));
     if (p == nullptr) return SYN_ERR_CUDA;
-    g_counters_addr[dev] = static_cast<uint32_t*>(p);
+    g_counters_addr[dev].store(static_cast<uint32_t*>(p), std::memory_order_release);
   }
-  uint32_t* counters = g_counters_addr[dev];
+  uint32_t* counters = g_counters_addr[dev].load(std::memory_order_acquire);
   // Every call shares the array and it keeps what the last call left: a call that ended in a
   // timeout may leave partial counts behind, so start from zero each time (stream-ordered).
   SYN_CUDA_TRY(cudaMemsetAsync(counters, 0, sizeof(uint32_t) * SYN_MAX_WAVES, static_cast<cudaStream_t>(stream)));

@@ -37,13 +37,13 @@ NUM_COUNTERS = 130  # SYN_NUM_COUNTERS: wave counters, copy counters, tile sched
 
 
 def plan_all_gather(world: int, rows_per_rank: int, K: int, dtype: torch.dtype, kind: str = "swizzle",
-                    copy_engine: bool = False, chunk_split: int = 1):
+                    copy_engine: bool = False, chunk_split: int = 1, transfer: str = "pull"):
     """(generator, comm_info, lowered) for gathering ``[rows_per_rank, K]`` shards along dim 0.
     ``chunk_split`` > 1 cuts every remote slab into that many row pieces, each with a flag and a
     wave of its own (``split_transfers_along_axis``)."""
     shape = (rows_per_rank * world, K)
     if kind == "swizzle":
-        plans = {r: build_all_gather_plan_1d_swizzle(shape, dtype, 0, world, r, "a", "pull") for r in range(world)}
+        plans = {r: build_all_gather_plan_1d_swizzle(shape, dtype, 0, world, r, "a", transfer) for r in range(world)}
     elif kind == "ring":
         plans = {r: build_ring_all_gather_plan(shape, dtype, 0, world, r, "a") for r in range(world)}
     else:
@@ -113,9 +113,15 @@ class AllGatherGemm:
 
     def __init__(self, ctx: SymmetricContext, rows_per_rank: int, K: int, N: int, dtype=torch.bfloat16,
                  plan: str = "swizzle", num_sms: int = 0, block_n: int = 0, timeout_ns: int = 0, comm: str = "sm",
-                 copy_streams: int = 2, lockstep: bool = True, chunk_split: int = 1, sync_after: bool = False):
+                 copy_streams: int = 2, lockstep: bool = True, chunk_split: int = 1, sync_after: bool = False,
+                 transfer: str = "pull"):
+        """``transfer`` (copy-engine mode): ``"pull"`` - every rank's copy engines fetch the peers' slabs;
+        ``"push"`` - every rank's copy engines write its slab into the peers' buffers and raise the
+        peers' flags (the swizzled plan in its push form)."""
         if comm not in ("sm", "ce"):
             raise ValueError("comm must be 'sm' or 'ce'")
+        if transfer not in ("pull", "push") or (transfer == "push" and (comm != "ce" or plan != "swizzle")):
+            raise ValueError("transfer='push' needs the swizzled plan moved by copy engines")
         self.ctx = ctx
         self.world, self.rank = ctx.world, ctx.rank
         self.rows, self.K, self.N, self.dtype = rows_per_rank, K, N, dtype
@@ -130,7 +136,8 @@ class AllGatherGemm:
         self.sync_after = sync_after
         self.chunk_split = chunk_split
         self.generator, self.info, lowered = plan_all_gather(self.world, rows_per_rank, K, dtype, plan,
-                                                             copy_engine=(comm == "ce"), chunk_split=chunk_split)
+                                                             copy_engine=(comm == "ce"), chunk_split=chunk_split,
+                                                             transfer=transfer)
         self.schedule = lowered[self.rank]["a"]
         self.epoch = 0
         self.trace = None  # optional uint64 stamp buffer handed to the kernel (see syn_gemm_args.trace)
@@ -398,6 +405,146 @@ class GemmAllReduce:
         if self.sync_after:
             self.ctx.barrier(cur)
         return self.out.local
+
+
+class AllToAllGemm:
+    """``out[B * S / world, N] = all_to_all(x)[B, S / world, H, D].reshape(B * S / world, H * D) @ W[N, H * D]^T``:
+    the head-sharded attention output ``x`` ``[B, S, H / world, D]`` of every rank is re-sharded along
+    the sequence while the output projection already runs (the reference's
+    tests/test_all2all_gemm.py:112-160).  The all-to-all is the rank's SM-copy program on a side
+    stream (``CommContext.execute`` on ``num_copy_sms`` SMs: pushes, each followed by the receiver's
+    flag); the GEMM runs on the other SMs, and every tile walks the K ranges (one per sending rank)
+    in arrival order, waiting for a range's flag before its first load from it."""
+
+    __doc__ += _HAZARD_NOTE + """
+    The symmetric input is ``src``."""
+
+    def __init__(self, ctx, B: int, S: int, H: int, D: int, N: int, dtype=torch.bfloat16, num_copy_sms: int = 16,
+                 timeout_ns: int = 0, lockstep: bool = True, sync_after: bool = False):
+        from .communication.comm_runtime.communication_context import CommContext
+
+        self.ctx, self.world, self.rank = ctx, ctx.world, ctx.rank
+        W = self.world
+        self.B, self.S, self.H, self.D, self.N, self.dtype = B, S, H, D, N, dtype
+        self.Hl, self.S_local = H // W, S // W
+        self.lockstep, self.sync_after, self.timeout_ns = lockstep, sync_after, timeout_ns
+        plans = {r: build_all_to_all_plan_dim((B, S, self.Hl, D), dtype=dtype, mesh_size=W, rank=r, src_buffer="src",
+                                              dst_buffer="dst", src_split_axis=2, dst_split_axis=1, transfer_kind="push")
+                 for r in range(W)}
+        gen = CommGenerator(plans)
+        gen.plan_signals()
+        self.info = gen.generate_code_for_plan(CodeGenOptions(copy_engine=False))
+        self.info.local_world_size = W
+        self.info.num_copy_sms = num_copy_sms if W > 1 else 0
+        self.comm = CommContext(self.rank, self.info, symmetric=ctx, timeout_ns=timeout_ns)
+        dst = lower_comm_plan_to_raw_schedules(gen)[self.rank]["dst"]
+        rows = B * self.S_local
+        # one wave per arriving slab: all rows, all N, the K range of the sender's heads
+        self.wave_offsets = [[0, 0, o[2] * D + o[3]] for o in dst.gen_block_offset_lists()]
+        self.wave_sizes = [[s_[0] * s_[1], N, s_[2] * s_[3]] for s_ in dst.gen_block_shape_lists()]
+        self.signals = dst.gen_signal_lists()
+        assert all(sz[0] == rows for sz in self.wave_sizes)
+        self.src = self.comm.comm_buffers["src"][self.rank]
+        self.a = self.comm.comm_buffers["dst"][self.rank].view(rows, H * D)
+        self.num_gemm_sms = 0
+        if W > 1 and num_copy_sms > 0:
+            sms = torch.cuda.get_device_properties(ctx.device).multi_processor_count
+            self.num_gemm_sms = max(sms - num_copy_sms, 2) & ~1
+
+    def send(self, stream=None):
+        """The all-to-all: this rank's slabs to their ranks (side streams), each followed by its flag."""
+        cur = stream or torch.cuda.current_stream()
+        self.comm.next_epoch()
+        if self.lockstep and self.world > 1:
+            self.ctx.barrier(cur)
+        self.comm.start_after(cur)
+        self.comm.execute()
+
+    def consume(self, w: torch.Tensor, out: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+        """The projection over the K ranges as they arrive."""
+        cur = stream or torch.cuda.current_stream()
+        if out is None:
+            out = torch.empty(self.a.shape[0], self.N, dtype=self.dtype, device=self.ctx.device)
+        gemm(self.a, w, out, self.world, self.num_gemm_sms, cur_wave_sizes=self.wave_sizes, wave_offsets=self.wave_offsets,
+             signal_ptr=self.comm.recv_signal_bufs[self.rank], signal_offsets=self.signals,
+             signal_value=self.comm.signal_value, timeout_ns=self.timeout_ns, status=self.ctx.status, stream=cur)
+        self.comm.end_before(cur)
+        if self.sync_after and self.world > 1:
+            self.ctx.barrier(cur)
+        return out
+
+    def __call__(self, w: torch.Tensor, out: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+        self.send(stream)
+        return self.consume(w, out, stream)
+
+
+class GemmAllToAllGemm:
+    """Tensor-parallel MLP without a reduction: ``out[M / world, hidden] = all_to_all(x @ W1_r^T) @ W2^T``
+    (the reference's tests/test_gemm_all2all_gemm.py:126-207).  ``x`` ``[M, hidden]`` is replicated,
+    ``W1_r`` ``[ffn / world, hidden]`` is this rank's shard, ``W2`` ``[hidden, ffn]`` is whole.  The
+    first GEMM is a producer (one wave of rows per destination rank, raising a COMPUTE_DONE flag),
+    the rank's SM-copy program pushes each finished row block to its rank and raises the receiver's
+    flag, and the second GEMM consumes the arriving K ranges (one per sending rank)."""
+
+    def __init__(self, ctx, M: int, hidden: int, ffn: int, dtype=torch.bfloat16, num_copy_sms: int = 16,
+                 timeout_ns: int = 0, lockstep: bool = True):
+        from .communication.comm_runtime.communication_context import CommContext
+
+        self.ctx, self.world, self.rank = ctx, ctx.world, ctx.rank
+        W = self.world
+        self.M, self.hidden, self.ffn, self.dtype = M, hidden, ffn, dtype
+        self.rows, self.ffn_local = M // W, ffn // W
+        self.lockstep, self.timeout_ns = lockstep, timeout_ns
+        plans = {r: build_all_to_all_plan_dim((M, self.ffn_local), dtype=dtype, mesh_size=W, rank=r, src_buffer="src",
+                                              dst_buffer="dst", src_split_axis=1, dst_split_axis=0, transfer_kind="push",
+                                              compute_producer=True)
+                 for r in range(W)}
+        gen = CommGenerator(plans)
+        gen.plan_signals()
+        self.info = gen.generate_code_for_plan(CodeGenOptions(copy_engine=False))
+        self.info.local_world_size = W
+        self.info.num_copy_sms = num_copy_sms if W > 1 else 0
+        self.comm = CommContext(self.rank, self.info, symmetric=ctx, timeout_ns=timeout_ns)
+        low = lower_comm_plan_to_raw_schedules(gen)[self.rank]
+        src, dst = low["src"], low["dst"]
+        self.prod_offsets, self.prod_sizes = src.gen_block_offset_lists(), src.gen_block_shape_lists()
+        self.prod_signals = src.gen_signal_lists()
+        self.wave_offsets = [[o[0], 0, o[1]] for o in dst.gen_block_offset_lists()]
+        self.wave_sizes = [[s_[0], hidden, s_[1]] for s_ in dst.gen_block_shape_lists()]
+        self.signals = dst.gen_signal_lists()
+        self.counters = torch.zeros(NUM_COUNTERS, dtype=torch.int32, device=ctx.device)
+        self.mid = self.comm.comm_buffers["src"][self.rank]   # [M, ffn / world]: the first GEMM's output
+        self.a2 = self.comm.comm_buffers["dst"][self.rank]    # [M / world, ffn]: the second GEMM's input
+        self.num_gemm_sms = 0
+        if W > 1 and num_copy_sms > 0:
+            sms = torch.cuda.get_device_properties(ctx.device).multi_processor_count
+            self.num_gemm_sms = max(sms - num_copy_sms, 2) & ~1
+
+    def produce_and_send(self, x: torch.Tensor, w1: torch.Tensor, stream=None):
+        cur = stream or torch.cuda.current_stream()
+        self.comm.next_epoch()
+        if self.lockstep and self.world > 1:
+            self.ctx.barrier(cur)
+        self.comm.start_after(cur)
+        gemm(x, w1, self.mid, self.world, self.num_gemm_sms, cur_wave_sizes=self.prod_sizes, wave_offsets=self.prod_offsets,
+             signal_offsets=[-1] * len(self.prod_signals), producer_signal_ptr=self.comm.compute_signal_bufs[self.rank],
+             producer_signal_offsets=self.prod_signals, counter_ptr=self.counters, signal_value=self.comm.signal_value,
+             timeout_ns=self.timeout_ns, status=self.ctx.status, stream=cur)
+        self.comm.execute()
+
+    def consume(self, w2: torch.Tensor, out: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+        cur = stream or torch.cuda.current_stream()
+        if out is None:
+            out = torch.empty(self.rows, self.hidden, dtype=self.dtype, device=self.ctx.device)
+        gemm(self.a2, w2, out, self.world, self.num_gemm_sms, cur_wave_sizes=self.wave_sizes, wave_offsets=self.wave_offsets,
+             signal_ptr=self.comm.recv_signal_bufs[self.rank], signal_offsets=self.signals,
+             signal_value=self.comm.signal_value, timeout_ns=self.timeout_ns, status=self.ctx.status, stream=cur)
+        self.comm.end_before(cur)
+        return out
+
+    def __call__(self, x: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, out: Optional[torch.Tensor] = None, stream=None):
+        self.produce_and_send(x, w1, stream)
+        return self.consume(w2, out, stream)
 
 
 # ----------------------------------------------------------------------------------------------

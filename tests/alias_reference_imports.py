@@ -13,6 +13,7 @@ _SUBMODULES = [
     "communication.common_descriptors",
     "communication.common_descriptors.utils",
     "communication.common_descriptors.all_gather",
+    "communication.common_descriptors.all_reduce",
     "communication.common_descriptors.all_to_all",
     "communication.common_descriptors.reduce_scatter",
     "communication.comm_runtime",

@@ -1,14 +1,17 @@
 """Runs the reference project's own CPU unit tests (its known-answer vectors for plans, signals,
 generated programs and lowered schedules) against THIS package, by aliasing the ``syncopate``
-import name.  Only possible where the reference checkout is mounted; skipped elsewhere (the same
-vectors are then covered through tests/golden/frontend_golden.json)."""
+import name.  The reference checkout is looked for where the environment variable
+SYNCOPATE_REFERENCE points, else in a directory called ``reference`` next to this repository;
+without one the test is skipped (the same vectors are then covered through
+tests/golden/frontend_golden.json)."""
 import os
 import subprocess
 import sys
 
 import pytest
 
-REF = os.environ.get("SYNCOPATE_REFERENCE", "/root/reference")
+_REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF = os.environ.get("SYNCOPATE_REFERENCE") or os.path.join(os.path.dirname(_REPO), "reference")
 FILES = [
     "tests/test_comm_plan.py",
     "tests/test_descriptor.py",
@@ -20,6 +23,7 @@ FILES = [
     "tests/test_ring_allgather_codegen.py",
     "tests/test_double_ring_allgather_codegen.py",
     "tests/test_reduce_scatter_codegen.py",
+    "tests/test_all_reduce_descriptor.py",
 ]
 
 
