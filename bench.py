@@ -348,7 +348,8 @@ def run_own_arm(args):
     shard_seed = lambda r: seeded(1000 + r, (ROWS, K_DIM), 1.0, dt)
     if world > 1:
         op = AllGatherGemm(ctx, ROWS, K_DIM, n_local, dt, plan="swizzle", comm=args.comm, chunk_split=args.chunk_split,
-                           copy_streams=args.copy_streams, transfer=args.ag_transfer if args.comm == "ce" else "pull")
+                           copy_streams=args.copy_streams, transfer=args.ag_transfer if args.comm == "ce" else "pull",
+                           flag_stream=not args.no_flag_stream)
         op.shard.copy_(shard_seed(rank).to(dev))
         step = lambda: op(b, c)
         kernels_per_step = 2  # the GEMM kernel and the lockstep barrier kernel
@@ -502,7 +503,7 @@ def run_own_arm(args):
     rs_bytes_per_rank = (world - 1) * (RS_M // world) * RS_N * 2 if world > 1 else 0
     if world > 1:
         rs = GemmReduceScatter(ctx, RS_M, RS_N, dt, plan="direct", comm=args.rs_comm, chunk_split=args.rs_split,
-                               copy_streams=args.copy_streams)
+                               copy_streams=args.copy_streams, flag_stream=not args.no_flag_stream)
         rout = torch.empty(RS_M // world, RS_N, dtype=dt, device=dev)
         rs_t = timed(lambda: rs(ra, rb, rout), n_warm=3)
         # parity: fp32 product of this rank's operands, reduce-scattered with torch.distributed
@@ -568,6 +569,70 @@ def run_own_arm(args):
     rs_ms = rs_t["ms"]
     rs_flop = 2.0 * RS_M * RS_N * rs_k
     rs_per_gpu = rs_flop / (rs_ms * 1e-3) / 1e12
+
+    # ---------------- all-to-all + GEMM and GEMM + all-to-all + GEMM (the reference's LLaMA-3.1-70B shapes of
+    # tests/test_all2all_gemm.py:200-232 and tests/test_gemm_all2all_gemm.py:213-250; reported, not the headline)
+    a2a_results = {}
+    if world > 1 and not args.skip_a2a:
+        from syncopate_b200.operators import AllToAllGemm, GemmAllToAllGemm
+
+        hidden, heads, hd = 8192, 64, 128
+        Bq, Sq = 2, 2048 * world                       # 4096 rows per rank
+        ag2 = AllToAllGemm(ctx, Bq, Sq, heads, hd, hidden, dt, num_copy_sms=args.copy_sms)
+        xa = seeded(6000 + rank, (Bq, Sq, heads // world, hd), 1.0, dt).to(dev)
+        wa = seeded(6100, (hidden, hidden), 0.02, dt).to(dev)
+        oa = torch.empty(Bq * Sq // world, hidden, dtype=dt, device=dev)
+        ag2.src.copy_(xa)
+        sync_all()
+        t_a = timed(lambda: ag2(wa, oa), n_blocks=max(3, blocks // 2), n_warm=3)
+        parts = [torch.empty_like(xa) for _ in range(world)]
+        dist.all_gather(parts, xa)
+        Sl = Sq // world
+        a_ref = torch.cat(parts, dim=2)[:, rank * Sl:(rank + 1) * Sl].reshape(Bq * Sl, hidden)
+        del parts
+        worst = [0.0, 0.0]
+        for r0, ref in matmul_blocks(a_ref, wa):
+            glob, tile = gemm_parity(oa[r0:r0 + ref.shape[0]], ref)
+            worst = [max(worst[0], glob), max(worst[1], tile)]
+        same = bool(torch.equal(ag2.a, a_ref))
+        parity["a2a_gemm"] = {"rel_frobenius": worst[0], "worst_tile_rel_frobenius": worst[1], "tol": GEMM_TOL,
+                              "resharded_bit_exact": same}
+        fl = 2.0 * (Bq * Sl) * hidden * hidden
+        nbytes = (world - 1) * Bq * Sl * (heads // world) * hd * 2
+        a2a_results["a2a_gemm"] = {
+            "workload": f"all-to-all + GEMM bf16 TP={world}: x [{Bq},{Sq},{heads // world},{hd}] per rank -> [{Bq * Sl},{hidden}] @ W[{hidden},{hidden}]^T; "
+                        f"SM copies on {args.copy_sms} SMs, K-gated tcgen05 GEMM on the others",
+            "ms_per_step": t_a["ms"], "ms_min": t_a["ms_min"], "ms_max": t_a["ms_max"],
+            "per_gpu_tflops": fl / (t_a["ms"] * 1e-3) / 1e12, "frac_of_peak": fl / (t_a["ms"] * 1e-3) / 1e12 / peaks["bf16_tflops"],
+            "nvlink_gbs_achieved": nbytes / (t_a["ms"] * 1e-3) / 1e9}
+        del ag2, a_ref, xa, oa
+        Mm, ffn = 4096 * world, 28672
+        mlp = GemmAllToAllGemm(ctx, Mm, hidden, ffn, dt, num_copy_sms=args.copy_sms)
+        xm = seeded(6200, (Mm, hidden), 0.1, dt).to(dev)
+        w1 = seeded(6300 + rank, (ffn // world, hidden), 0.1, dt).to(dev)
+        w2 = seeded(6400, (hidden, ffn), 0.02, dt).to(dev)
+        om = torch.empty(Mm // world, hidden, dtype=dt, device=dev)
+        sync_all()
+        t_m = timed(lambda: mlp(xm, w1, w2, om), n_steps=max(3, min(steps, 10)), n_blocks=max(3, blocks // 2), n_warm=2)
+        w1s = [torch.empty_like(w1) for _ in range(world)]
+        dist.all_gather(w1s, w1)
+        rows = slice(rank * (Mm // world), (rank + 1) * (Mm // world))
+        mid = torch.empty(Mm // world, ffn, dtype=dt, device=dev)
+        for r0, blk in matmul_blocks(xm[rows], torch.cat(w1s, 0)):
+            mid[r0:r0 + blk.shape[0]] = blk.to(dt)
+        del w1s
+        worst = [0.0, 0.0]
+        for r0, ref in matmul_blocks(mid, w2):
+            glob, tile = gemm_parity(om[r0:r0 + ref.shape[0]], ref)
+            worst = [max(worst[0], glob), max(worst[1], tile)]
+        parity["gemm_a2a_gemm"] = {"rel_frobenius": worst[0], "worst_tile_rel_frobenius": worst[1], "tol": GEMM_TOL}
+        fl = 2.0 * Mm * (ffn // world) * hidden + 2.0 * (Mm // world) * hidden * ffn
+        a2a_results["gemm_a2a_gemm"] = {
+            "workload": f"GEMM + all-to-all + GEMM bf16 TP={world}: x [{Mm},{hidden}] @ W1_r[{ffn // world},{hidden}]^T -> all-to-all -> "
+                        f"[{Mm // world},{ffn}] @ W2[{hidden},{ffn}]^T; SM copies on {args.copy_sms} SMs",
+            "ms_per_step": t_m["ms"], "ms_min": t_m["ms_min"], "ms_max": t_m["ms_max"],
+            "per_gpu_tflops": fl / (t_m["ms"] * 1e-3) / 1e12, "frac_of_peak": fl / (t_m["ms"] * 1e-3) / 1e12 / peaks["bf16_tflops"]}
+        del mlp, mid, xm, w1, w2, om
 
     # ---------------- attention operators at the benchmark shapes (reported, not the headline)
     attn_results = {}
@@ -668,6 +733,13 @@ def run_own_arm(args):
             "frac_of_peak": c_flop / (c_t["ms"] * 1e-3) / 1e12 / peaks["bf16_tflops"]}
 
     # ---------------- verdict on parity (all ranks agree: the figures above are maxima over ranks)
+    for extra in ("a2a_gemm", "gemm_a2a_gemm"):
+        if extra in parity:
+            v = max_over_ranks([parity[extra]["rel_frobenius"], parity[extra]["worst_tile_rel_frobenius"],
+                                0.0 if parity[extra].get("resharded_bit_exact", True) else 1.0])
+            parity[extra]["rel_frobenius"], parity[extra]["worst_tile_rel_frobenius"] = v[0], v[1]
+            if "resharded_bit_exact" in parity[extra]:
+                parity[extra]["resharded_bit_exact"] = v[2] == 0.0
     ar_p = parity.get("gemm_ar", {"rel_frobenius": 0.0, "worst_tile_rel_frobenius": 0.0})
     flat = max_over_ranks([parity["ag_gemm"]["rel_frobenius"], parity["ag_gemm"]["worst_tile_rel_frobenius"],
                            parity["gemm_rs"]["rel_frobenius"], parity["gemm_rs"]["worst_tile_rel_frobenius"],
@@ -680,7 +752,9 @@ def run_own_arm(args):
     parity["gathered_bit_exact"] = flat[4] == 0.0
     ok = (flat[0] < GEMM_TOL and flat[1] < GEMM_TOL and flat[2] < GEMM_TOL and flat[3] < GEMM_TOL and flat[4] == 0.0
           and flat[5] < GEMM_TOL and flat[6] < GEMM_TOL
-          and all(parity[k]["max_abs_sampled_rows"] < ATTN_TOL for k in ("ulysses", "cp") if k in parity))
+          and all(parity[k]["max_abs_sampled_rows"] < ATTN_TOL for k in ("ulysses", "cp") if k in parity)
+          and all(parity[k]["rel_frobenius"] < GEMM_TOL and parity[k]["worst_tile_rel_frobenius"] < GEMM_TOL
+                  and parity[k].get("resharded_bit_exact", True) for k in ("a2a_gemm", "gemm_a2a_gemm") if k in parity))
     parity["ok"] = bool(ok)
     parity["how"] = ("checked on the device after the timed regions: AG+GEMM against an fp32 product of the gathered "
                      "A (torch.distributed all_gather) and the gathered buffer bit for bit; GEMM+RS against fp32 product "
@@ -744,6 +818,7 @@ def run_own_arm(args):
                             "compute_only_ms": rs_compute_only["ms"] if rs_compute_only else None,
                             "other_comm_mode": rs_other},
                 **({"gemm_ar": ar_result} if ar_result is not None else {}),
+                **a2a_results,
                 **attn_results,
             },
         }
@@ -779,6 +854,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-attention", action="store_true", help="leave the attention operators out of other_ops")
     ap.add_argument("--skip-alt-comm", action="store_true", help="do not time the other transport beside the chosen one")
+    ap.add_argument("--skip-a2a", action="store_true", help="leave the all-to-all + GEMM operators out of other_ops")
+    ap.add_argument("--copy-sms", type=int, default=16, help="SMs of the SM-copy programs beside a GEMM (all-to-all + GEMM)")
     ap.add_argument("--comm", default="ce", choices=["sm", "ce"],
                     help="who moves the all-gather chunks: the kernel's comm warps (sm) or copy engines (ce)")
     ap.add_argument("--chunk-split", type=int, default=2, help="row pieces per remote all-gather slab")
@@ -789,6 +866,8 @@ def main():
     ap.add_argument("--rs-split", type=int, default=1, help="row pieces per reduce-scatter slab")
     ap.add_argument("--ar-splits", type=int, default=1, help="row slices of GEMM+AR (separate launches)")
     ap.add_argument("--copy-streams", type=int, default=2)
+    ap.add_argument("--no-flag-stream", action="store_true",
+                    help="write each chunk's flag on its copy stream instead of a separate flag stream")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

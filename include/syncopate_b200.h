@@ -277,7 +277,9 @@ int syn_gemm_rs(const syn_gemm_rs_args* args, const syn_schedule* src_sched, con
  * streams[step.stream % num_streams], in array order per stream:
  *   wait_flag != NULL : stream waits until *wait_flag >= value (syn_flag_wait_stream: needs no SM)
  *   bytes > 0         : cudaMemcpyAsync(dst, src, bytes) (peer-mapped pointers allowed)
- *   set_flag != NULL  : *set_flag = value, ordered after the copy (syn_flag_set)
+ *   set_flag != NULL  : *set_flag = value, ordered after the copy (syn_flag_set); with `flag_stream`
+ *                       the write goes to that stream, behind an event recorded after the copy, so
+ *                       that the copy stream runs its copies back to back
  * One call issues the whole program from C, so a program of a few dozen steps costs a few dozen
  * driver calls and nothing else. */
 typedef struct syn_ce_step {
@@ -289,7 +291,8 @@ typedef struct syn_ce_step {
   int32_t stream;
   int32_t reserved;
 } syn_ce_step;
-int syn_ce_run(const syn_ce_step* steps, int num_steps, void* const* streams, int num_streams, uint64_t value);
+int syn_ce_run(const syn_ce_step* steps, int num_steps, void* const* streams, int num_streams, void* flag_stream,
+               uint64_t value);
 
 /* ------------------------------------------------------------------ attention
  * Flash-attention forward over a wave schedule (replaces the TLX kernel

@@ -156,10 +156,12 @@ def make_ce_program(steps):
     return arr
 
 
-def ce_run(program, num_steps: int, streams, value: int) -> None:
-    """Issues a copy-engine program (``make_ce_program``) on ``streams`` (torch streams)."""
+def ce_run(program, num_steps: int, streams, value: int, flag_stream=None) -> None:
+    """Issues a copy-engine program (``make_ce_program``) on ``streams`` (torch streams); with
+    ``flag_stream`` the flag writes go there, each behind an event recorded after its copy."""
     ptrs = (C.c_void_p * len(streams))(*[s.cuda_stream or None for s in streams])
-    check(lib().syn_ce_run(program, num_steps, ptrs, len(streams), value), "syn_ce_run")
+    fs = flag_stream.cuda_stream if flag_stream is not None else None
+    check(lib().syn_ce_run(program, num_steps, ptrs, len(streams), fs, value), "syn_ce_run")
 
 
 class AttnArgs(C.Structure):
@@ -325,7 +327,7 @@ def _declare(l: C.CDLL) -> None:
     l.syn_flag_wait_stream.restype = C.c_int
     l.syn_flag_wait_stream.argtypes = [C.c_void_p, C.c_uint64, C.c_void_p]
     l.syn_ce_run.restype = C.c_int
-    l.syn_ce_run.argtypes = [C.POINTER(CeStep), C.c_int, C.POINTER(C.c_void_p), C.c_int, C.c_uint64]
+    l.syn_ce_run.argtypes = [C.POINTER(CeStep), C.c_int, C.POINTER(C.c_void_p), C.c_int, C.c_void_p, C.c_uint64]
     l.syn_ag_gemm.restype = C.c_int
     l.syn_ag_gemm.argtypes = [C.POINTER(AgGemmArgs), C.POINTER(Schedule), C.c_void_p]
     l.syn_copy.restype = C.c_int

@@ -178,8 +178,24 @@ int syn_flag_wait_stream(const uint64_t* flag, uint64_t value, void* stream) {
   return SYN_OK;
 }
 
-int syn_ce_run(const syn_ce_step* steps, int num_steps, void* const* streams, int num_streams, uint64_t value) {
+// Events that order a flag write on the flag stream behind a copy on a copy stream (timing off).
+// A small ring per device: re-recording an event does not disturb waits already issued on it.
+static cudaEvent_t ce_event(int dev) {
+  constexpr int kRing = 256, kMaxDev = 64;
+  static cudaEvent_t ring[kMaxDev][kRing];
+  static unsigned next[kMaxDev];
+  if (dev < 0 || dev >= kMaxDev) return nullptr;
+  cudaEvent_t& e = ring[dev][next[dev]++ % kRing];
+  if (e == nullptr && cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) e = nullptr;
+  return e;
+}
+
+int syn_ce_run(const syn_ce_step* steps, int num_steps, void* const* streams, int num_streams, void* flag_stream,
+               uint64_t value) {
+  using namespace syn;
   if (steps == nullptr || num_steps < 0 || streams == nullptr || num_streams <= 0) return SYN_ERR_INVALID;
+  int dev = 0;
+  if (flag_stream != nullptr) SYN_CUDA_TRY(cudaGetDevice(&dev));
   for (int i = 0; i < num_steps; ++i) {
     const syn_ce_step& st = steps[i];
     if (st.stream < 0) return SYN_ERR_INVALID;
@@ -187,7 +203,18 @@ int syn_ce_run(const syn_ce_step* steps, int num_steps, void* const* streams, in
     int rc = SYN_OK;
     if (st.wait_flag != nullptr) rc = syn_flag_wait_stream(st.wait_flag, value, sp);
     if (rc == SYN_OK && st.bytes > 0) rc = syn_memcpy_async(st.dst, st.src, st.bytes, sp);
-    if (rc == SYN_OK && st.set_flag != nullptr) rc = syn_flag_set(st.set_flag, value, sp);
+    if (rc == SYN_OK && st.set_flag != nullptr) {
+      if (flag_stream != nullptr) {
+        // the copy stream goes straight on to its next copy; the flag follows the copy through an event
+        cudaEvent_t e = ce_event(dev);
+        if (e == nullptr) return SYN_ERR_CUDA;
+        SYN_CUDA_TRY(cudaEventRecord(e, static_cast<cudaStream_t>(sp)));
+        SYN_CUDA_TRY(cudaStreamWaitEvent(static_cast<cudaStream_t>(flag_stream), e, 0));
+        rc = syn_flag_set(st.set_flag, value, flag_stream);
+      } else {
+        rc = syn_flag_set(st.set_flag, value, sp);
+      }
+    }
     if (rc != SYN_OK) return rc;
   }
   return SYN_OK;

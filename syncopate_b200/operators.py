@@ -114,7 +114,7 @@ class AllGatherGemm:
     def __init__(self, ctx: SymmetricContext, rows_per_rank: int, K: int, N: int, dtype=torch.bfloat16,
                  plan: str = "swizzle", num_sms: int = 0, block_n: int = 0, timeout_ns: int = 0, comm: str = "sm",
                  copy_streams: int = 2, lockstep: bool = True, chunk_split: int = 1, sync_after: bool = False,
-                 transfer: str = "pull"):
+                 transfer: str = "pull", flag_stream: bool = True):
         """``transfer`` (copy-engine mode): ``"pull"`` - every rank's copy engines fetch the peers' slabs;
         ``"push"`` - every rank's copy engines write its slab into the peers' buffers and raise the
         peers' flags (the swizzled plan in its push form)."""
@@ -152,6 +152,9 @@ class AllGatherGemm:
             # are therefore issued round-robin on a few streams so that several are in flight.
             # Each (copy, flag) pair stays in order on its stream; chunks are independent.
             self._copy_streams = [torch.cuda.Stream(device=ctx.device) for _ in range(max(1, copy_streams))]
+            # flag writes go to a stream of their own (behind an event per copy): a copy stream then
+            # runs its copies back to back instead of stopping for a stream memory operation after each
+            self._flag_stream = torch.cuda.Stream(device=ctx.device) if flag_stream else None
             self._ev_start = torch.cuda.Event()
             self._ev_go = torch.cuda.Event()
             steps = self.copy_program()
@@ -203,13 +206,15 @@ class AllGatherGemm:
             self._ev_go.record(side[0])
             for s in side[1:]:
                 s.wait_event(self._ev_go)
-            _L.ce_run(self._program, self._program_len, side, self.epoch)
+            _L.ce_run(self._program, self._program_len, side, self.epoch, self._flag_stream)
             gemm(self.a.local, b, c, self.world, self.num_sms, BLOCK_SIZE_N=self.block_n,
                  cur_wave_sizes=self._wave_sizes, wave_offsets=self._wave_offsets, signal_ptr=self.flags.local,
                  signal_offsets=self._signals, signal_value=self.epoch, status=self.ctx.status,
                  timeout_ns=self.timeout_ns, trace=self.trace, stream=cur)
             for s in side:
                 cur.wait_stream(s)
+            if self._flag_stream is not None:
+                cur.wait_stream(self._flag_stream)
         else:
             if self.lockstep:
                 self.ctx.barrier(cur)
@@ -231,7 +236,7 @@ class GemmReduceScatter:
 
     def __init__(self, ctx: SymmetricContext, M: int, N: int, dtype=torch.bfloat16, plan: str = "direct",
                  num_sms: int = 0, block_n: int = 0, timeout_ns: int = 0, lockstep: bool = True, comm: str = "sm",
-                 copy_streams: int = 2, chunk_split: int = 1, publish_pieces: bool = False):
+                 copy_streams: int = 2, chunk_split: int = 1, publish_pieces: bool = False, flag_stream: bool = True):
         """``comm="sm"``: the GEMM's epilogue stores each tile straight into the target rank's staging
         slab (TMA stores to peer memory).  ``comm="ce"``: the epilogue stores locally and raises a
         local flag per wave; side streams wait for the flag (a stream memory operation), move the
@@ -268,6 +273,7 @@ class GemmReduceScatter:
             self.send = torch.empty(self.world, self.slab, N, dtype=dtype, device=ctx.device)
             self.send_flags = torch.zeros(len(self.remote_signals), dtype=torch.int64, device=ctx.device)
             self._copy_streams = [torch.cuda.Stream(device=ctx.device) for _ in range(max(1, copy_streams))]
+            self._flag_stream = torch.cuda.Stream(device=ctx.device) if flag_stream else None
             self._ev_start = torch.cuda.Event()
             self._ev_go = torch.cuda.Event()
             self._programs = []
@@ -306,9 +312,11 @@ class GemmReduceScatter:
             for s in side[1:]:
                 s.wait_event(self._ev_go)
             program, n = self._programs[self.epoch & 1]
-            _L.ce_run(program, n, side, self.epoch)
+            _L.ce_run(program, n, side, self.epoch, self._flag_stream)
             for s in side:
                 cur.wait_stream(s)  # the next call's kernel may overwrite the send slabs
+            if self._flag_stream is not None:
+                cur.wait_stream(self._flag_stream)
             return out
         if self.lockstep:
             self.ctx.barrier(cur)
@@ -351,6 +359,7 @@ class GemmAllReduce:
         pieces = self.rs.pieces
         self.gather_flags = ctx.alloc((self.world * pieces,), torch.int64)  # [sender][piece], raised by the sender
         self._gather_streams = [torch.cuda.Stream(device=ctx.device) for _ in range(max(1, copy_streams))]
+        self._gather_flag_stream = torch.cuda.Stream(device=ctx.device)
         self._ev = torch.cuda.Event()
         self._programs = []
         for part in range(num_splits):
@@ -392,7 +401,7 @@ class GemmAllReduce:
                 s.wait_event(self._ev)   # the previous call's readers of `out` are behind this point
             self.rs(a[r0 : r0 + self.part_rows], b, own, stream=cur)
             program, n = self._programs[part]
-            _L.ce_run(program, n, self._gather_streams, self.rs.epoch)
+            _L.ce_run(program, n, self._gather_streams, self.rs.epoch, self._gather_flag_stream)
         # every peer's rows of the last slice (and, flag by flag in order, of the earlier ones)
         for src in range(self.world):
             if src == self.rank:
@@ -400,7 +409,7 @@ class GemmAllReduce:
             for g in range(self.rs.pieces):
                 _L.check(lib.syn_flag_wait_stream(self.gather_flags.local.data_ptr() + 8 * (src * self.rs.pieces + g),
                                                   self.rs.epoch, cur.cuda_stream or None), "syn_flag_wait_stream")
-        for s in self._gather_streams:
+        for s in self._gather_streams + [self._gather_flag_stream]:
             cur.wait_stream(s)
         if self.sync_after:
             self.ctx.barrier(cur)

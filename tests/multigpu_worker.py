@@ -13,7 +13,9 @@ os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
 
 from syncopate_b200.operators import (  # noqa: E402
     AllGatherGemm,
+    AllToAllGemm,
     ContextParallelAttention,
+    GemmAllToAllGemm,
     GemmAllReduce,
     GemmReduceScatter,
     UlyssesAttention,
@@ -139,6 +141,47 @@ def main():
             if not (e < TOL and et < TOL):
                 failures.append(f"gemm_ar M={M} splits={splits} pieces={pieces} {comm} it={it} rank={rank}: "
                                 f"relerr={e:.3e} tile={et:.3e}")
+        del op, ref
+
+    # ---- all-to-all + GEMM: SM copies on a few SMs beside the K-gated consumer GEMM on the others
+    for B, S, H, D, N in ((1, 256 * world, 2 * world, 128, 512), (2, 512 * world, 8 * world, 128, 1024)):
+        op = AllToAllGemm(ctx, B, S, H, D, N, dt, num_copy_sms=16, timeout_ns=2_000_000_000, sync_after=True)
+        x = seeded(4000 + rank, (B, S, H // world, D), 1.0, dt, dev)
+        w = seeded(4100, (N, H * D), 0.02, dt, dev)
+        parts = [torch.empty_like(x) for _ in range(world)]
+        dist.all_gather(parts, x)
+        Sl = S // world
+        a_ref = torch.cat(parts, dim=2)[:, rank * Sl:(rank + 1) * Sl].reshape(B * Sl, H * D)
+        ref = a_ref.float() @ w.float().t()
+        for it in range(3):
+            op.src.copy_(x)
+            out = op(w)
+            ctx.check()
+            e, et = tile_ok(out, ref)
+            same = torch.equal(op.a, a_ref)
+            if not (e < TOL and et < TOL and same):
+                failures.append(f"a2a_gemm S={S} it={it} rank={rank}: relerr={e:.3e} tile={et:.3e} resharded_ok={same}")
+        del op, ref
+
+    # ---- GEMM + all-to-all + GEMM (tensor-parallel MLP without a reduction)
+    for M, hidden, ffn in ((256 * world, 512, 256 * world), (1024 * world, 1024, 512 * world)):
+        op = GemmAllToAllGemm(ctx, M, hidden, ffn, dt, num_copy_sms=16, timeout_ns=2_000_000_000)
+        x = seeded(4200, (M, hidden), 0.1, dt, dev)
+        w1 = seeded(4300 + rank, (ffn // world, hidden), 0.1, dt, dev)
+        w2 = seeded(4400, (hidden, ffn), 0.1, dt, dev)
+        w1s = [torch.empty_like(w1) for _ in range(world)]
+        dist.all_gather(w1s, w1)
+        rows = slice(rank * (M // world), (rank + 1) * (M // world))
+        mid = (x[rows].float() @ torch.cat(w1s, 0).float().t()).to(dt)
+        ref = mid.float() @ w2.float().t()
+        for it in range(3):
+            out = op(x, w1, w2)
+            ctx.check()
+            e, et = tile_ok(out, ref)
+            if not (e < TOL and et < TOL):
+                failures.append(f"gemm_a2a_gemm M={M} it={it} rank={rank}: relerr={e:.3e} tile={et:.3e}")
+            ctx.barrier()   # the peers' pushes of the next call land in this rank's buffers
+            torch.cuda.synchronize()
         del op, ref
 
     # ---- attention operators (reference: gather with torch.distributed, dense fp32 attention per head)
