@@ -346,13 +346,15 @@ def run_own_arm(args):
     b = seeded(5000 + rank, (n_local, K_DIM), 0.02, dt).to(dev)
     c = torch.empty(M, n_local, dtype=dt, device=dev)
     shard_seed = lambda r: seeded(1000 + r, (ROWS, K_DIM), 1.0, dt)
+    ag_lockstep = "pairwise" if (args.ag_lockstep == "pairwise" and args.comm == "ce" and args.ag_transfer == "pull") else True
     if world > 1:
         op = AllGatherGemm(ctx, ROWS, K_DIM, n_local, dt, plan="swizzle", comm=args.comm, chunk_split=args.chunk_split,
                            copy_streams=args.copy_streams, transfer=args.ag_transfer if args.comm == "ce" else "pull",
-                           flag_stream=not args.no_flag_stream)
+                           flag_stream=not args.no_flag_stream, lockstep=ag_lockstep)
         op.shard.copy_(shard_seed(rank).to(dev))
         step = lambda: op(b, c)
-        kernels_per_step = 2  # the GEMM kernel and the lockstep barrier kernel
+        # the GEMM kernel and, with a barrier in front of the transfers, the barrier kernel
+        kernels_per_step = 1 if ag_lockstep == "pairwise" else 2
     else:
         from syncopate_b200.operators import plan_all_gather
 
@@ -434,7 +436,8 @@ def run_own_arm(args):
         a_host = shard_seed(rank).pin_memory()
         sets = [op] + [AllGatherGemm(ctx, ROWS, K_DIM, n_local, dt, plan="swizzle", comm=args.comm,
                                      chunk_split=args.chunk_split, copy_streams=args.copy_streams,
-                                     transfer=args.ag_transfer if args.comm == "ce" else "pull") for _ in range(2)]
+                                     transfer=args.ag_transfer if args.comm == "ce" else "pull",
+                                     flag_stream=not args.no_flag_stream, lockstep=ag_lockstep) for _ in range(2)]
         ev_in = [torch.cuda.Event() for _ in range(3)]
         ev_comp = [torch.cuda.Event() for _ in range(3)]
         e2e_path = ("pinned host A shard -> symmetric device shard, fused operator, C -> pinned host; three operator "
@@ -497,13 +500,14 @@ def run_own_arm(args):
     ra = seeded(2000 + rank, (RS_M, rs_k), 1.0, dt).to(dev)
     rb = seeded(3000 + rank, (RS_N, rs_k), 0.02, dt).to(dev)
     rs_other = None
+    rs_other_reduce = None
     rs_compute_only = None
     rs_trace_rows = None
     ar_result = None
     rs_bytes_per_rank = (world - 1) * (RS_M // world) * RS_N * 2 if world > 1 else 0
     if world > 1:
         rs = GemmReduceScatter(ctx, RS_M, RS_N, dt, plan="direct", comm=args.rs_comm, chunk_split=args.rs_split,
-                               copy_streams=args.copy_streams, flag_stream=not args.no_flag_stream)
+                               copy_streams=args.copy_streams, flag_stream=not args.no_flag_stream, reduce=args.rs_reduce)
         rout = torch.empty(RS_M // world, RS_N, dtype=dt, device=dev)
         rs_t = timed(lambda: rs(ra, rb, rout), n_warm=3)
         # parity: fp32 product of this rank's operands, reduce-scattered with torch.distributed
@@ -530,7 +534,7 @@ def run_own_arm(args):
         from syncopate_b200.operators import GemmAllReduce
 
         ar = GemmAllReduce(ctx, RS_M, RS_N, dt, num_splits=args.ar_splits, chunk_split=1, comm=args.rs_comm,
-                           copy_streams=args.copy_streams, sync_after=True)
+                           copy_streams=args.copy_streams, sync_after=True, reduce=args.rs_reduce)
         ar_t = timed(lambda: ar(ra, rb), n_blocks=max(3, blocks // 2), n_warm=3)
         ar_ref = torch.empty(RS_M, RS_N, dtype=torch.float32, device=dev)
         for r0, blk in matmul_blocks(ra, rb):
@@ -557,6 +561,12 @@ def run_own_arm(args):
             rs_other = timed(lambda: rs2(ra, rb, rout), n_blocks=max(3, blocks // 2), n_warm=3)
             rs_other["comm_mode"] = alt
             del rs2
+            alt_red = "pass" if args.rs_reduce == "epilogue" else "epilogue"
+            rs3 = GemmReduceScatter(ctx, RS_M, RS_N, dt, plan="direct", comm=args.rs_comm, chunk_split=args.rs_split,
+                                    copy_streams=args.copy_streams, flag_stream=not args.no_flag_stream, reduce=alt_red)
+            rs_other_reduce = timed(lambda: rs3(ra, rb, rout), n_blocks=max(3, blocks // 2), n_warm=3)
+            rs_other_reduce["reduce_mode"] = alt_red
+            del rs3
     else:
         rout = torch.empty(RS_M, RS_N, dtype=dt, device=dev)
         rs_t = timed(lambda: gemm(ra, rb, rout, status=ctx.status), n_warm=3)
@@ -816,7 +826,8 @@ def run_own_arm(args):
                             "fused_roofline_ms": rs_roof_ms, "frac_of_fused_roofline": rs_roof_ms / rs_ms,
                             "nvlink_gbs_achieved": rs_bytes / (rs_ms * 1e-3) / 1e9 if world > 1 else None,
                             "compute_only_ms": rs_compute_only["ms"] if rs_compute_only else None,
-                            "other_comm_mode": rs_other},
+                            "reduce_mode": args.rs_reduce if world > 1 else None,
+                            "other_comm_mode": rs_other, "other_reduce_mode": rs_other_reduce},
                 **({"gemm_ar": ar_result} if ar_result is not None else {}),
                 **a2a_results,
                 **attn_results,
@@ -864,8 +875,12 @@ def main():
     ap.add_argument("--rs-comm", default="ce", choices=["sm", "ce"],
                     help="GEMM+RS transport: the epilogue's TMA stores (sm) or copy engines (ce)")
     ap.add_argument("--rs-split", type=int, default=1, help="row pieces per reduce-scatter slab")
+    ap.add_argument("--rs-reduce", default="epilogue", choices=["epilogue", "pass"],
+                    help="GEMM+RS / GEMM+AR: staged partial sums added in the own tiles' epilogue, or by a pass behind the kernel")
     ap.add_argument("--ar-splits", type=int, default=1, help="row slices of GEMM+AR (separate launches)")
-    ap.add_argument("--copy-streams", type=int, default=2)
+    ap.add_argument("--copy-streams", type=int, default=1)
+    ap.add_argument("--ag-lockstep", default="barrier", choices=["barrier", "pairwise"],
+                    help="AG+GEMM by copy-engine pulls: a barrier in front of the transfers, or one 'entered' word per peer")
     ap.add_argument("--no-flag-stream", action="store_true",
                     help="write each chunk's flag on its copy stream instead of a separate flag stream")
     args = ap.parse_args()

@@ -181,6 +181,11 @@ int syn_ctx_destroy(syn_ctx* ctx);
  * Waits at most `timeout_s` seconds for the peers (0 = 120 s) and returns SYN_ERR_RENDEZVOUS after. */
 int syn_symm_alloc(syn_ctx* ctx, size_t bytes, int timeout_s, syn_symm* out);
 int syn_symm_free(syn_ctx* ctx, void* local_ptr);
+/* Loads the code of every kernel of the library on the current device and waits for the device.
+ * syn_ctx_create calls it.  With lazy module loading the first launch of a kernel may wait for the
+ * kernels that are running on the device; a kernel that waits for a peer (a reduce wave, a barrier)
+ * must never be what such a first launch waits for, so the loading is done once, up front. */
+int syn_preload(void);
 /* Device-side barrier over all ranks on `stream` (replaces nvshmem_barrier_all_on_stream, e.g.
  * tests/test_ag_gemm_gen.py:53): a one-block kernel raises this rank's slot on every peer and waits,
  * bounded by timeout_ns (0 = 2 s), for all slots.  Errors surface through syn_ctx_status. */
@@ -267,6 +272,13 @@ typedef struct syn_gemm_rs_args {
    * all-gather of the reduced slabs; the reference runs a library all-reduce per slice behind the
    * producer GEMM instead, tests/test_gemm_ar_collective.py:97-160). */
   uint64_t* out_flags;
+  /* 0: the tiles of the own slab wait for the staged partial sums and add them in the epilogue
+   * (one kernel).  1: the kernel stores the own partial sum like any other (16 bit) and a reduce
+   * pass launched behind it on the same stream waits for the flags, adds the staged slabs with
+   * coalesced loads and raises out_flags; the own partial sum is then rounded to 16 bits before
+   * the fp32 sum, like those of the other ranks.  N must be a multiple of 8. */
+  int32_t reduce_pass;
+  int32_t reserved;
 } syn_gemm_rs_args;
 int syn_gemm_rs(const syn_gemm_rs_args* args, const syn_schedule* src_sched, const syn_schedule* dst_sched,
                 void* stream);

@@ -125,6 +125,8 @@ class GemmRsArgs(C.Structure):
         ("send_buf", C.c_void_p),
         ("send_flags", C.c_void_p),
         ("out_flags", C.c_void_p),
+        ("reduce_pass", C.c_int32),
+        ("reserved", C.c_int32),
     ]
 
 
@@ -312,6 +314,8 @@ def _declare(l: C.CDLL) -> None:
     l.syn_symm_alloc.argtypes = [C.c_void_p, C.c_size_t, C.c_int, C.POINTER(Symm)]
     l.syn_symm_free.restype = C.c_int
     l.syn_symm_free.argtypes = [C.c_void_p, C.c_void_p]
+    l.syn_preload.restype = C.c_int
+    l.syn_preload.argtypes = []
     l.syn_barrier.restype = C.c_int
     l.syn_barrier.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64]
     l.syn_ctx_status_ptr.restype = C.c_void_p

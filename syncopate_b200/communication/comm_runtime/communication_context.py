@@ -82,6 +82,7 @@ class CommContext:
             self.comm_buffers[name] = t.peers
         self.streams: List[torch.cuda.Stream] = []
         self.compute_stream: Optional[torch.cuda.Stream] = None
+        self._copy_cache: Dict[int, tuple] = {}
         self._make_streams()
 
     def _make_streams(self) -> None:
@@ -135,6 +136,14 @@ class CommContext:
     def _sm_copy(self, op: SMCopyOp, sp) -> None:
         """One ``SMCopyOp`` (an N-D box, optionally reducing) on the SM copy kernel: the box is cut
         into 2-D strided pieces and handed to ``syn_copy``, at most 64 pieces per launch."""
+        lib = L.lib()
+        status = self.symmetric.status.data_ptr()
+        n_sms = self.info.num_copy_sms if getattr(self.info, "num_copy_sms", 0) else 0
+        cached = self._copy_cache.get(id(op))
+        if cached is not None:  # the program is static: its boxes are cut into pieces once
+            for comm, _keep in cached[1]:
+                L.check(lib.syn_copy(C.byref(comm), n_sms, self.signal_value, self.timeout_ns, status, sp), "syn_copy")
+            return
         src_t, dst_t = self._buffers[op.src], self._buffers[op.dst]
         elem = src_t.dtype.itemsize
         src_off = [a.start for a in op.src_slice]
@@ -152,9 +161,8 @@ class CommContext:
                 raise NotImplementedError("reducing SM copies take fp16 / bf16 buffers of one type")
             reduce = 1
         pieces = box_copy_ops(src_t.shape, src_off, dst_t.shape, dst_off, extent_s, elem)
-        lib = L.lib()
-        status = self.symmetric.status.data_ptr()
-        n_sms = self.info.num_copy_sms if getattr(self.info, "num_copy_sms", 0) else 0
+        launches = []
+        self._copy_cache[id(op)] = (op, launches)  # (the op is kept so that its id stays unique)
         for first in range(0, len(pieces), _COPY_MAX_OPS):
             ops = []
             for so, do, rows, row_bytes, spitch, dpitch in pieces[first:first + _COPY_MAX_OPS]:
@@ -169,6 +177,7 @@ class CommContext:
                 c.dtype = _SYN_DTYPES.get(src_t.dtype, 0)
                 ops.append(c)
             comm, keep = L.make_attn_comm(ops, [src_t.symm, dst_t.symm], src_t.symm, None)
+            launches.append((comm, keep))
             L.check(lib.syn_copy(C.byref(comm), n_sms, self.signal_value, self.timeout_ns, status, sp), "syn_copy")
 
     def execute(self, neglect_local: bool = False):
@@ -253,6 +262,7 @@ class CommContext:
         if info.local_world_size == 0:
             info.local_world_size = info.world_size
         self.info = info
+        self._copy_cache = {}
         self._make_streams()
 
 

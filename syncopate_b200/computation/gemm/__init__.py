@@ -233,12 +233,14 @@ def gemm_rs(
     send_flags: Optional[torch.Tensor] = None,
     trace=None,
     out_flags: Optional[torch.Tensor] = None,
+    reduce_pass: bool = False,
 ) -> torch.Tensor:
     """GEMM + reduce-scatter.  ``a`` ``[M, K_local]``, ``b`` ``[N, K_local]``; ``out``
     ``[M / world, N]`` receives the fp32 sum over ranks of this rank's row slab.  With ``send_buf``
     ``[world, M / world, N]`` and ``send_flags`` (int64, one word per wave of ``src_schedule``) the
     kernel stores the rows for other ranks locally and raises the local flag of each wave; moving
-    them is the caller's job."""
+    them is the caller's job.  ``reduce_pass``: the kernel stores this rank's own partial sum and a
+    coalesced pass launched behind it adds the staged ones (instead of the epilogue of the own tiles)."""
     g = _gemm_args(a, b, None, num_sms, block_n, group_size_m, epoch, timeout_ns, status, stream)
     _check_mat("out", out)
     g.trace = _ptr(trace)
@@ -256,6 +258,7 @@ def gemm_rs(
         args.send_flags = send_flags.data_ptr()
     if out_flags is not None:
         args.out_flags = out_flags.data_ptr()  # int64, one word per row piece of the slab kept here
+    args.reduce_pass = 1 if reduce_pass else 0
     s, keep1 = _schedule_struct(src_schedule)
     d, keep2 = _schedule_struct(dst_schedule)
     rc = L.lib().syn_gemm_rs(C.byref(args), C.byref(s), C.byref(d), _stream_ptr(stream))

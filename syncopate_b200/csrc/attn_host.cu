@@ -17,7 +17,7 @@ static int check_strides(const int64_t s[3]) {
 }
 
 template <bool FUSED, bool BF16>
-static int launch_attn(const AttnParams& p, int grid, cudaStream_t stream) {
+static int launch_attn(const AttnParams& p, int grid, cudaStream_t stream, bool configure_only = false) {
   constexpr int smem = 1024 + (2 + 2 * ATTN_KV_STAGES) * ATTN_TILE_BYTES + (FUSED ? COMM_NBUF * COMM_PIECE : 0) + 512;
   static_assert(smem <= 232448, "attention kernel exceeds the shared memory of an SM");
   auto kern = attn_kernel<FUSED, BF16>;
@@ -28,13 +28,14 @@ static int launch_attn(const AttnParams& p, int grid, cudaStream_t stream) {
     SYN_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured_dev = dev;
   }
+  if (configure_only) return SYN_OK;
   kern<<<grid, 256, smem, stream>>>(p);
   SYN_CUDA_TRY(cudaGetLastError());
   return SYN_OK;
 }
 
 template <bool FUSED, bool BF16>
-static int launch_attn2(const AttnParams& p, int grid, cudaStream_t stream) {
+static int launch_attn2(const AttnParams& p, int grid, cudaStream_t stream, bool configure_only = false) {
   constexpr int smem = 1024 + (2 + 2 * ATTN_KV_STAGES) * ATTN_TILE_BYTES + (FUSED ? COMM_NBUF * COMM_PIECE : 0) + 512;
   static_assert(smem <= 232448, "attention kernel exceeds the shared memory of an SM");
   auto kern = attn2_kernel<FUSED, BF16>;
@@ -45,9 +46,23 @@ static int launch_attn2(const AttnParams& p, int grid, cudaStream_t stream) {
     SYN_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured_dev = dev;
   }
+  if (configure_only) return SYN_OK;
   kern<<<grid, ATTN2_THREADS, smem, stream>>>(p);
   SYN_CUDA_TRY(cudaGetLastError());
   return SYN_OK;
+}
+
+int preload_attn_kernels() {
+  static AttnParams p;  // never read: configure_only
+  int rc = launch_attn<false, false>(p, 0, nullptr, true);
+  if (rc == SYN_OK) rc = launch_attn<false, true>(p, 0, nullptr, true);
+  if (rc == SYN_OK) rc = launch_attn<true, false>(p, 0, nullptr, true);
+  if (rc == SYN_OK) rc = launch_attn<true, true>(p, 0, nullptr, true);
+  if (rc == SYN_OK) rc = launch_attn2<false, false>(p, 0, nullptr, true);
+  if (rc == SYN_OK) rc = launch_attn2<false, true>(p, 0, nullptr, true);
+  if (rc == SYN_OK) rc = launch_attn2<true, false>(p, 0, nullptr, true);
+  if (rc == SYN_OK) rc = launch_attn2<true, true>(p, 0, nullptr, true);
+  return rc;
 }
 
 // SYNCOPATE_B200_ATTN_TWO_TILE=0 keeps the one-tile kernel, =2 takes the two-tile kernel whenever

@@ -97,6 +97,12 @@ __global__ void __launch_bounds__(COPY_THREADS) copy_kernel(const __grid_constan
   }
 }
 
+int preload_copy_kernels() {
+  cudaFuncAttributes attr;
+  SYN_CUDA_TRY(cudaFuncGetAttributes(&attr, copy_kernel));
+  return SYN_OK;
+}
+
 }  // namespace syn
 
 extern "C" int syn_copy(const syn_attn_comm* comm, int num_sms, uint64_t signal_value, uint64_t timeout_ns,

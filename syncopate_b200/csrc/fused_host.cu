@@ -26,6 +26,83 @@ static int check_symm(const syn_symm& s) {
   return SYN_OK;
 }
 
+
+// Reduce pass of GEMM + reduce-scatter: out[rows, N] (the rank's own 16-bit partial sums, stored by
+// the GEMM) += the partial sums the other ranks staged, in fp32, fixed slab order.  A stand-alone
+// pass reads whole 128-byte lines with coalesced 16-byte loads, which the routed epilogue (one
+// thread per accumulator row, rows 16 KB apart) cannot; it costs a launch and one more rounding of
+// the own partial sum to 16 bits, the rounding every other rank's partial sum gets anyway.
+struct RsReduceParams {
+  void* out;              // row 0 of the piece
+  int ldo, rows, n_vec;   // n_vec = N / 8
+  int num_red, dtype;
+  const void* src[GEMM_MAX_RED];  // row 0 of the piece in each staged slab
+  int src_ld;
+  const uint64_t* flags;
+  int16_t sig[GEMM_MAX_RED];
+  uint64_t value, timeout_ns;
+  int32_t* status;
+  int wave;
+};
+
+__global__ void __launch_bounds__(256) rs_reduce_kernel(const RsReduceParams p) {
+  __shared__ int abort_word;
+  if (threadIdx.x == 0) abort_word = 0;
+  __syncthreads();
+  if (threadIdx.x < p.num_red) {
+    volatile int* aw = &abort_word;
+    if (!flag_wait_ge(p.flags + p.sig[threadIdx.x], p.value, aw, p.timeout_ns) && p.status != nullptr) {
+      if (atomicCAS(p.status, 0, SYN_DEV_TIMEOUT_FLAG) == 0) {
+        p.status[1] = p.wave;
+        p.status[2] = -2 - static_cast<int>(threadIdx.x);
+        p.status[3] = static_cast<int>(blockIdx.x);
+      }
+    }
+  }
+  __syncthreads();
+  if (abort_word != 0) return;  // the rows keep the own partial sum; the error is in the status block
+  const size_t total = static_cast<size_t>(p.rows) * p.n_vec;
+  for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const size_t row = i / p.n_vec, v = i % p.n_vec;
+    uint4* dst = reinterpret_cast<uint4*>(static_cast<char*>(p.out) + (row * p.ldo + v * 8) * 2);
+    uint4 u[GEMM_MAX_RED];
+    const uint4 own = *dst;
+#pragma unroll
+    for (int s = 0; s < GEMM_MAX_RED; ++s)
+      if (s < p.num_red)
+        u[s] = __ldcs(reinterpret_cast<const uint4*>(static_cast<const char*>(p.src[s]) + (row * p.src_ld + v * 8) * 2));
+    const uint32_t o4[4] = {own.x, own.y, own.z, own.w};
+    float2 acc[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[j] = unpack2(o4[j], p.dtype);
+#pragma unroll
+    for (int s = 0; s < GEMM_MAX_RED; ++s) {
+      if (s < p.num_red) {
+        const uint32_t w4[4] = {u[s].x, u[s].y, u[s].z, u[s].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = unpack2(w4[j], p.dtype);
+          acc[j].x += f.x;
+          acc[j].y += f.y;
+        }
+      }
+    }
+    uint4 r;
+    r.x = pack2(acc[0].x, acc[0].y, p.dtype);
+    r.y = pack2(acc[1].x, acc[1].y, p.dtype);
+    r.z = pack2(acc[2].x, acc[2].y, p.dtype);
+    r.w = pack2(acc[3].x, acc[3].y, p.dtype);
+    *dst = r;
+  }
+}
+
+int preload_fused_kernels() {
+  cudaFuncAttributes attr;
+  SYN_CUDA_TRY(cudaFuncGetAttributes(&attr, rs_reduce_kernel));
+  return SYN_OK;
+}
+
 }  // namespace syn
 
 extern "C" {
@@ -263,10 +340,16 @@ int syn_gemm_rs(const syn_gemm_rs_args* args, const syn_schedule* src_sched, con
     if (tgt == rank) {
       slab0 = static_cast<char*>(args->out);
       slab_ld = ldo;
-      rt.flag = args->out_flags != nullptr ? args->out_flags + pc.group : nullptr;
-      rt.raise_on_abort = 1;
-      rt.reduce = 1;
-      for (int i = 0; i < n_red; ++i) rt.red_sig[i] = static_cast<int16_t>(groups[pc.group].sig[i]);
+      if (args->reduce_pass) {
+        // plain store of the own partial sum; the pass behind the kernel adds the staged ones
+        rt.flag = nullptr;
+        rt.reduce = 0;
+      } else {
+        rt.flag = args->out_flags != nullptr ? args->out_flags + pc.group : nullptr;
+        rt.raise_on_abort = 1;
+        rt.reduce = 1;
+        for (int i = 0; i < n_red; ++i) rt.red_sig[i] = static_cast<int16_t>(groups[pc.group].sig[i]);
+      }
     } else if (args->send_buf != nullptr) {
       // transport by the caller: local send slab, local flag per wave
       slab0 = static_cast<char*>(args->send_buf) + static_cast<size_t>(tgt) * slab_elems * 2;
@@ -308,12 +391,49 @@ int syn_gemm_rs(const syn_gemm_rs_args* args, const syn_schedule* src_sched, con
   p.counters = args->counters;
   p.c = args->out;
   p.ldc = ldo;
-  if (want_pair && pair_eligible(p, bn, grid))
-    return gemm_launch_pair(p, &g, bn, grid, /*fused=*/true, static_cast<cudaStream_t>(stream));
-  if (dynamic_sched()) p.sched = args->counters + SYN_MAX_WAVES + SYN_MAX_COMM_OPS;
-  grid = std::min(grid, p.total_tiles);
-  if (grid <= 0) return SYN_ERR_INVALID;
-  return gemm_launch(p, bn, /*fused=*/true, grid, static_cast<cudaStream_t>(stream));
+  cudaStream_t cs = static_cast<cudaStream_t>(stream);
+  if (want_pair && pair_eligible(p, bn, grid)) {
+    rc = gemm_launch_pair(p, &g, bn, grid, /*fused=*/true, cs);
+  } else {
+    if (dynamic_sched()) p.sched = args->counters + SYN_MAX_WAVES + SYN_MAX_COMM_OPS;
+    grid = std::min(grid, p.total_tiles);
+    if (grid <= 0) return SYN_ERR_INVALID;
+    rc = gemm_launch(p, bn, /*fused=*/true, grid, cs);
+  }
+  if (rc != SYN_OK || !args->reduce_pass) return rc;
+  // ---- reduce pass: one launch per row piece of the own slab, its flag raised behind it
+  int sms = 0;
+  rc = device_sm_count(&sms);
+  if (rc != SYN_OK) return rc;
+  for (size_t gi = 0; gi < groups.size(); ++gi) {
+    RsReduceParams q;
+    memset(&q, 0, sizeof(q));
+    q.out = static_cast<char*>(args->out) + static_cast<size_t>(groups[gi].off) * ldo * 2;
+    q.ldo = ldo;
+    q.rows = groups[gi].rows;
+    q.n_vec = g.N / 8;
+    q.num_red = n_red;
+    q.dtype = p.dtype;
+    for (int i = 0; i < n_red; ++i) {
+      q.src[i] = static_cast<const char*>(p.red_src[i]) + static_cast<size_t>(groups[gi].off) * g.N * 2;
+      q.sig[i] = static_cast<int16_t>(groups[gi].sig[i]);
+    }
+    q.src_ld = g.N;
+    q.flags = p.red_flags;
+    q.value = epoch;
+    q.timeout_ns = p.timeout_ns;
+    q.status = p.status;
+    q.wave = static_cast<int>(gi);
+    const size_t total = static_cast<size_t>(q.rows) * q.n_vec;
+    const int blocks = static_cast<int>(std::min<size_t>((total + 255) / 256, static_cast<size_t>(sms) * 4));
+    rs_reduce_kernel<<<blocks, 256, 0, cs>>>(q);
+    SYN_CUDA_TRY(cudaGetLastError());
+    if (args->out_flags != nullptr) {
+      rc = syn_flag_set(args->out_flags + gi, epoch, stream);
+      if (rc != SYN_OK) return rc;
+    }
+  }
+  return SYN_OK;
 }
 
 }  // extern "C"

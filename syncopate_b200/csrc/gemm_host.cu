@@ -172,8 +172,9 @@ int gemm_fill_common(GemmParams* p, const syn_gemm_args* a, const syn_schedule* 
   return SYN_OK;
 }
 
+// `configure_only`: load the kernel and set its shared-memory limit, launch nothing.
 template <int BN, bool FUSED>
-static int launch_bn(const GemmParams& p, int grid, cudaStream_t stream) {
+static int launch_bn(const GemmParams& p, int grid, cudaStream_t stream, bool configure_only = false) {
   using L = GemmSmem<BN>;
   constexpr int kMaxSmem = 232448;
   constexpr int kFixed = 1024 /*alignment slack*/ + (FUSED ? COMM_NBUF * COMM_PIECE : 0) + 512 /*barriers, queues*/;
@@ -191,6 +192,7 @@ static int launch_bn(const GemmParams& p, int grid, cudaStream_t stream) {
     configured = true;
     configured_dev = dev;
   }
+  if (configure_only) return SYN_OK;
   kern<<<grid, GEMM_THREADS, smem, stream>>>(p);
   SYN_CUDA_TRY(cudaGetLastError());
   return SYN_OK;
@@ -198,7 +200,7 @@ static int launch_bn(const GemmParams& p, int grid, cudaStream_t stream) {
 
 template <int BN, bool FUSED>
 static int launch_pair_bn(const GemmParams& p, const CUtensorMap& tmap_b_half, int pair_tiles, int grid,
-                          const PairTail& tail, cudaStream_t stream) {
+                          const PairTail& tail, cudaStream_t stream, bool configure_only = false) {
   constexpr int kStage = GEMM_BM * GEMM_BK * 2 + (BN / 2) * GEMM_BK * 2;
   constexpr int kFixed = 1024 + 512 + (FUSED ? COMM_NBUF * COMM_PIECE : 0);
   constexpr int kStagesRaw = (232448 - kFixed) / kStage;
@@ -213,6 +215,7 @@ static int launch_pair_bn(const GemmParams& p, const CUtensorMap& tmap_b_half, i
     SYN_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured_dev = dev;
   }
+  if (configure_only) return SYN_OK;
   kern<<<grid, GEMM_THREADS, smem, stream>>>(p, tmap_b_half, pair_tiles, tail);
   SYN_CUDA_TRY(cudaGetLastError());
   return SYN_OK;
@@ -304,6 +307,27 @@ int gemm_launch(const GemmParams& p, int bn, bool fused, int grid, cudaStream_t 
       return SYN_ERR_UNSUPPORTED;
   }
 #undef SYN_BN_CASE
+}
+
+int preload_gemm_kernels() {
+  static GemmParams p;  // never read: configure_only
+  static CUtensorMap map;
+  static PairTail tail;
+  int rc = SYN_OK;
+#define SYN_PRELOAD(BN_)                                                              \
+  if (rc == SYN_OK) rc = launch_bn<BN_, false>(p, 0, nullptr, true);                  \
+  if (rc == SYN_OK) rc = launch_bn<BN_, true>(p, 0, nullptr, true);                   \
+  if (rc == SYN_OK) rc = launch_pair_bn<BN_, false>(p, map, 0, 0, tail, nullptr, true); \
+  if (rc == SYN_OK) rc = launch_pair_bn<BN_, true>(p, map, 0, 0, tail, nullptr, true);
+  SYN_PRELOAD(256)
+  SYN_PRELOAD(224)
+  SYN_PRELOAD(192)
+  SYN_PRELOAD(160)
+  SYN_PRELOAD(128)
+  SYN_PRELOAD(96)
+  SYN_PRELOAD(64)
+#undef SYN_PRELOAD
+  return rc;
 }
 
 int gemm_resolve_grid_and_bn(const syn_gemm_args* a, const syn_schedule* sched, int* grid, int* bn, int multiple,

@@ -246,34 +246,33 @@ __device__ __forceinline__ void drain_stage(uint64_t* full_bar, uint32_t fills, 
 }
 
 // Adds the 16-bit partial sums staged by the peers (slab order = rank order, fixed) to 32 fp32
-// accumulator values of one output row; four slabs' loads are in flight at a time.
+// accumulator values of one output row.  The loads of all slabs are issued before the first add:
+// the rows are 16 KB or more apart, so the reads are latency-bound and one round trip per chunk
+// of columns is what the epilogue pays.
 __device__ __forceinline__ void epi_add_staged(const GemmParams& p, uint32_t (&r)[32], int grow, int col) {
   const size_t elem = static_cast<size_t>(grow - p.red_row0) * p.red_ld + col;
+  uint4 u[GEMM_MAX_RED][4];
 #pragma unroll
-  for (int g = 0; g < 2; ++g) {
-    uint4 u[4][4];
+  for (int s = 0; s < GEMM_MAX_RED; ++s) {
+    if (s < p.num_red) {
+      const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(p.red_src[s]) + elem * 2);
 #pragma unroll
-    for (int s = 0; s < 4; ++s) {
-      if (g * 4 + s < p.num_red) {
-        const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(p.red_src[(g * 4 + s) % GEMM_MAX_RED]) + elem * 2);
-#pragma unroll
-        for (int v = 0; v < 4; ++v)
-          if (col + v * 8 < p.N) u[s][v] = __ldcg(src + v);
-      }
+      for (int v = 0; v < 4; ++v)
+        if (col + v * 8 < p.N) u[s][v] = __ldcg(src + v);
     }
+  }
 #pragma unroll
-    for (int s = 0; s < 4; ++s) {
-      if (g * 4 + s < p.num_red) {
+  for (int s = 0; s < GEMM_MAX_RED; ++s) {
+    if (s < p.num_red) {
 #pragma unroll
-        for (int v = 0; v < 4; ++v) {
-          if (col + v * 8 < p.N) {
-            const uint32_t w4[4] = {u[s][v].x, u[s][v].y, u[s][v].z, u[s][v].w};
+      for (int v = 0; v < 4; ++v) {
+        if (col + v * 8 < p.N) {
+          const uint32_t w4[4] = {u[s][v].x, u[s][v].y, u[s][v].z, u[s][v].w};
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 f = unpack2(w4[j], p.dtype);
-              r[v * 8 + 2 * j] = __float_as_uint(__uint_as_float(r[v * 8 + 2 * j]) + f.x);
-              r[v * 8 + 2 * j + 1] = __float_as_uint(__uint_as_float(r[v * 8 + 2 * j + 1]) + f.y);
-            }
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = unpack2(w4[j], p.dtype);
+            r[v * 8 + 2 * j] = __float_as_uint(__uint_as_float(r[v * 8 + 2 * j]) + f.x);
+            r[v * 8 + 2 * j + 1] = __float_as_uint(__uint_as_float(r[v * 8 + 2 * j + 1]) + f.y);
           }
         }
       }

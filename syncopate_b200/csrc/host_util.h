@@ -38,6 +38,14 @@ int encode_tmap_3d_sw128(CUtensorMap* out, const void* base, uint64_t d2, uint64
 int encode_tmap_4d_sw128(CUtensorMap* out, const void* base, uint64_t d3, uint64_t d2, uint64_t rows, uint64_t cols,
                          uint64_t s3, uint64_t s2, uint64_t ld, uint32_t box_rows, uint32_t box_cols);
 
+// Kernel loading, one function per translation unit (see syn_preload): each loads the code of its
+// kernels on the current device.
+int preload_symm_kernels();
+int preload_copy_kernels();
+int preload_fused_kernels();
+int preload_gemm_kernels();
+int preload_attn_kernels();
+
 // Maps a device status code (ptx.cuh) to the negative C-ABI code.
 int status_to_err(int dev_code);
 

@@ -98,9 +98,28 @@ __global__ void flag_wait_kernel(const uint64_t* flag, uint64_t value, uint64_t 
   }
 }
 
+int preload_symm_kernels() {
+  cudaFuncAttributes attr;
+  SYN_CUDA_TRY(cudaFuncGetAttributes(&attr, barrier_kernel));
+  SYN_CUDA_TRY(cudaFuncGetAttributes(&attr, flag_set_kernel));
+  SYN_CUDA_TRY(cudaFuncGetAttributes(&attr, flag_wait_kernel));
+  return SYN_OK;
+}
+
 }  // namespace syn
 
 extern "C" {
+
+int syn_preload(void) {
+  using namespace syn;
+  int rc = preload_symm_kernels();
+  if (rc == SYN_OK) rc = preload_copy_kernels();
+  if (rc == SYN_OK) rc = preload_fused_kernels();
+  if (rc == SYN_OK) rc = preload_gemm_kernels();
+  if (rc == SYN_OK) rc = preload_attn_kernels();
+  if (rc == SYN_OK) SYN_CUDA_TRY(cudaDeviceSynchronize());
+  return rc;
+}
 
 int syn_memcpy_async(void* dst, const void* src, size_t bytes, void* stream) {
   using namespace syn;
@@ -242,6 +261,10 @@ int syn_ctx_create(int rank, int world, int device, const char* rendezvous_dir, 
     return SYN_ERR_CUDA;
   }
   int rc = syn_symm_alloc(c, sizeof(uint64_t) * SYN_MAX_WORLD, 0, &c->barrier_flags);
+  // every kernel of the library is loaded now, while the GPU is idle: with lazy loading the first
+  // launch of a kernel can wait for the kernels that are running, and a kernel that waits for a
+  // peer must never be what such a launch waits for
+  if (rc == SYN_OK) rc = syn_preload();
   if (rc != SYN_OK) {
     syn_ctx_destroy(c);
     return rc;

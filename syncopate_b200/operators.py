@@ -113,7 +113,7 @@ class AllGatherGemm:
 
     def __init__(self, ctx: SymmetricContext, rows_per_rank: int, K: int, N: int, dtype=torch.bfloat16,
                  plan: str = "swizzle", num_sms: int = 0, block_n: int = 0, timeout_ns: int = 0, comm: str = "sm",
-                 copy_streams: int = 2, lockstep: bool = True, chunk_split: int = 1, sync_after: bool = False,
+                 copy_streams: int = 1, lockstep=True, chunk_split: int = 1, sync_after: bool = False,
                  transfer: str = "pull", flag_stream: bool = True):
         """``transfer`` (copy-engine mode): ``"pull"`` - every rank's copy engines fetch the peers' slabs;
         ``"push"`` - every rank's copy engines write its slab into the peers' buffers and raise the
@@ -132,6 +132,11 @@ class AllGatherGemm:
         # move in step; free-running ranks drift, two of them then load the same peer's link and
         # the transfers slow down.  A device-side barrier at the start of each call keeps them
         # aligned (and orders the peers' shard writes before the pulls).
+        # lockstep="pairwise" (copy-engine pulls only): no barrier; every rank tells every peer that it
+        # has entered the call (a flag write per peer) and a pull from peer p waits for p's word only,
+        # so that a pull from a rank that is already there does not wait for the slowest rank.
+        if lockstep == "pairwise" and (comm != "ce" or transfer != "pull"):
+            raise ValueError("lockstep='pairwise' needs copy-engine pulls")
         self.lockstep = lockstep
         self.sync_after = sync_after
         self.chunk_split = chunk_split
@@ -148,15 +153,23 @@ class AllGatherGemm:
             self._wave_offsets = [[o[0], 0] for o in self.schedule.gen_block_offset_lists()]
             self._wave_sizes = [[s[0], N] for s in self.schedule.gen_block_shape_lists()]
             self._signals = self.schedule.gen_signal_lists()
-            # One chunk copy does not fill the link while the GEMM is running; consecutive chunks
-            # are therefore issued round-robin on a few streams so that several are in flight.
-            # Each (copy, flag) pair stays in order on its stream; chunks are independent.
+            # Consecutive chunks go round-robin over the copy streams.  Measured on eight GPUs under
+            # the running GEMM: ONE stream whose copies run back to back (flags on the flag stream)
+            # moves the most bytes per second; copies in flight on several streams slow each other
+            # down and delay the first chunk, the one the GEMM waits for.
             self._copy_streams = [torch.cuda.Stream(device=ctx.device) for _ in range(max(1, copy_streams))]
             # flag writes go to a stream of their own (behind an event per copy): a copy stream then
             # runs its copies back to back instead of stopping for a stream memory operation after each
             self._flag_stream = torch.cuda.Stream(device=ctx.device) if flag_stream else None
             self._ev_start = torch.cuda.Event()
             self._ev_go = torch.cuda.Event()
+            self._ready = None
+            if lockstep == "pairwise" and self.world > 1:
+                self._ready = ctx.alloc((self.world,), torch.int64)   # [peer]: the peer's last entered call
+                self._announce_stream = torch.cuda.Stream(device=ctx.device)
+                hello = [(0, 0, 0, 0, self._ready.symm.ptrs[(self.rank + i) % self.world] + 8 * self.rank, 0)
+                         for i in range(1, self.world)]
+                self._hello, self._hello_len = _L.make_ce_program(hello), len(hello)
             steps = self.copy_program()
             self._program, self._program_len = _L.make_ce_program(steps), len(steps)
 
@@ -173,11 +186,12 @@ class AllGatherGemm:
                 if op.src_rank == op.dst_rank:
                     continue
                 pending.append((self.a.symm.ptrs[op.dst_rank] + op.dst_offset, self.a.symm.ptrs[op.src_rank] + op.src_offset,
-                                op.size))
+                                op.size, op.src_rank))
             elif kind == "IntraNodeSignal" and pending:
                 flag = self.flags.symm.ptrs[op.rank] + 8 * op.offset
-                for i, (dst, src, nbytes) in enumerate(pending):
-                    steps.append((0, dst, src, nbytes, flag if i == len(pending) - 1 else 0, group))
+                for i, (dst, src, nbytes, src_rank) in enumerate(pending):
+                    wait = self._ready.local.data_ptr() + 8 * src_rank if self._ready is not None else 0
+                    steps.append((wait, dst, src, nbytes, flag if i == len(pending) - 1 else 0, group))
                 pending = []
                 group += 1
         return steps
@@ -201,7 +215,10 @@ class AllGatherGemm:
             side = self._copy_streams
             self._ev_start.record(cur)
             side[0].wait_event(self._ev_start)
-            if self.lockstep:
+            if self._ready is not None:
+                self._announce_stream.wait_event(self._ev_start)
+                _L.ce_run(self._hello, self._hello_len, [self._announce_stream], self.epoch, None)
+            elif self.lockstep:
                 self.ctx.barrier(side[0])
             self._ev_go.record(side[0])
             for s in side[1:]:
@@ -215,6 +232,8 @@ class AllGatherGemm:
                 cur.wait_stream(s)
             if self._flag_stream is not None:
                 cur.wait_stream(self._flag_stream)
+            if self._ready is not None:
+                cur.wait_stream(self._announce_stream)
         else:
             if self.lockstep:
                 self.ctx.barrier(cur)
@@ -236,16 +255,24 @@ class GemmReduceScatter:
 
     def __init__(self, ctx: SymmetricContext, M: int, N: int, dtype=torch.bfloat16, plan: str = "direct",
                  num_sms: int = 0, block_n: int = 0, timeout_ns: int = 0, lockstep: bool = True, comm: str = "sm",
-                 copy_streams: int = 2, chunk_split: int = 1, publish_pieces: bool = False, flag_stream: bool = True):
+                 copy_streams: int = 2, chunk_split: int = 1, publish_pieces: bool = False, flag_stream: bool = True,
+                 reduce: str = "epilogue"):
         """``comm="sm"``: the GEMM's epilogue stores each tile straight into the target rank's staging
         slab (TMA stores to peer memory).  ``comm="ce"``: the epilogue stores locally and raises a
         local flag per wave; side streams wait for the flag (a stream memory operation), move the
         rows with a copy engine and raise the target's flag.  ``chunk_split`` sends every slab as
         that many row pieces; the rows kept here are then reduced piece by piece as the matching
         pieces arrive.  ``publish_pieces``: the kernel also raises the local flag ``out_flags[g]`` when
-        row piece g of the result is complete (for whoever passes the reduced rows on)."""
+        row piece g of the result is complete (for whoever passes the reduced rows on).
+        ``reduce="epilogue"``: the tiles of the rows kept here wait for the staged partial sums and
+        add them in their epilogue (one kernel).  ``reduce="pass"``: the kernel stores the own partial
+        sum and a pass launched behind it adds the staged slabs with coalesced loads (and raises
+        ``out_flags``); the own partial sum is then rounded to 16 bits before the sum."""
         if comm not in ("sm", "ce"):
             raise ValueError("comm must be 'sm' or 'ce'")
+        if reduce not in ("epilogue", "pass"):
+            raise ValueError("reduce must be 'epilogue' or 'pass'")
+        self.reduce_pass = reduce == "pass"
         self.ctx = ctx
         self.comm = comm
         self.lockstep = lockstep
@@ -297,18 +324,23 @@ class GemmReduceScatter:
                         timeout_ns=self.timeout_ns, stream=stream)
         cur = stream or torch.cuda.current_stream()
         if self.comm == "ce":
-            # the kernel first (a launch that fails must not leave stream waits behind), then the
-            # transport: wait for the wave's local flag, copy its rows, raise the target's flag
+            # Order of issue: the barrier kernel (side stream) BEFORE the kernels - it must be on the
+            # GPU before a kernel that waits for the peers' partial sums, never launched past one - and
+            # the flag-gated copies AFTER the kernel that raises their flags: a stream wait issued
+            # ahead of its producer can block the producer where the two streams share a hardware
+            # queue.  Per wave the transport is "wait for the wave's local flag, copy its rows, raise
+            # the target's flag".
             side = self._copy_streams
             self._ev_start.record(cur)
-            gemm_rs(a, b, out, self.src_schedule, self.dst_schedule, self.remote_signals, self.stage.symm,
-                    self.flags.symm, self.counters, epoch=self.epoch, num_sms=self.num_sms, block_n=self.block_n,
-                    timeout_ns=self.timeout_ns, status=self.ctx.status, stream=cur, send_buf=self.send,
-                    send_flags=self.send_flags, trace=self.trace, out_flags=self.out_flags)
             side[0].wait_event(self._ev_start)
             if self.lockstep:
                 self.ctx.barrier(side[0])
             self._ev_go.record(side[0])
+            gemm_rs(a, b, out, self.src_schedule, self.dst_schedule, self.remote_signals, self.stage.symm,
+                    self.flags.symm, self.counters, epoch=self.epoch, num_sms=self.num_sms, block_n=self.block_n,
+                    timeout_ns=self.timeout_ns, status=self.ctx.status, stream=cur, send_buf=self.send,
+                    send_flags=self.send_flags, trace=self.trace, out_flags=self.out_flags,
+                    reduce_pass=self.reduce_pass)
             for s in side[1:]:
                 s.wait_event(self._ev_go)
             program, n = self._programs[self.epoch & 1]
@@ -323,7 +355,7 @@ class GemmReduceScatter:
         return gemm_rs(a, b, out, self.src_schedule, self.dst_schedule, self.remote_signals, self.stage.symm,
                        self.flags.symm, self.counters, epoch=self.epoch, num_sms=self.num_sms,
                        block_n=self.block_n, timeout_ns=self.timeout_ns, status=self.ctx.status, stream=cur,
-                       trace=self.trace, out_flags=self.out_flags)
+                       trace=self.trace, out_flags=self.out_flags, reduce_pass=self.reduce_pass)
 
 
 class GemmAllReduce:
@@ -342,7 +374,7 @@ class GemmAllReduce:
 
     def __init__(self, ctx: SymmetricContext, M: int, N: int, dtype=torch.bfloat16, num_splits: int = 1,
                  chunk_split: int = 1, comm: str = "ce", copy_streams: int = 2, timeout_ns: int = 0,
-                 lockstep: bool = True, sync_after: bool = False):
+                 lockstep: bool = True, sync_after: bool = False, reduce: str = "epilogue"):
         if M % (num_splits * ctx.world):
             raise ValueError("M must be divisible by num_splits * world")
         self.ctx, self.world, self.rank = ctx, ctx.world, ctx.rank
@@ -352,7 +384,7 @@ class GemmAllReduce:
         self.out = ctx.alloc((M, N), dtype)
         self.rs = GemmReduceScatter(ctx, self.part_rows, N, dtype, plan="direct", timeout_ns=timeout_ns,
                                     lockstep=lockstep, comm=comm, copy_streams=copy_streams, chunk_split=chunk_split,
-                                    publish_pieces=True)
+                                    publish_pieces=True, reduce=reduce)
         self.slab = self.part_rows // self.world
         if self.world == 1:
             return

@@ -52,13 +52,16 @@ def main():
         r = rp.reshape(gm, 128, gn, 256).permute(0, 2, 1, 3).reshape(gm, gn, -1)
         return rel(x, ref), (d.norm(dim=-1) / r.norm(dim=-1).clamp_min(1e-30)).max().item()
 
-    for kind, comm, rows, K, N, split in (("swizzle", "sm", 256, 512, 512, 1), ("ring", "sm", 128, 256, 512, 1),
-                                          ("swizzle", "ce", 256, 512, 512, 1), ("swizzle", "sm", 512, 512, 512, 2),
-                                          ("swizzle", "ce", 512, 256, 768, 4),
-                                          ("swizzle", "sm", 1024, 8192, 28672 // world, 1),
-                                          ("swizzle", "sm", 1024, 8192, 28672 // world, 2),
-                                          ("swizzle", "ce", 1024, 8192, 28672 // world, 2)):
-        op = AllGatherGemm(ctx, rows, K, N, dt, plan=kind, comm=comm, timeout_ns=2_000_000_000, chunk_split=split)
+    for kind, comm, rows, K, N, split, lock in (
+            ("swizzle", "sm", 256, 512, 512, 1, True), ("ring", "sm", 128, 256, 512, 1, True),
+            ("swizzle", "ce", 256, 512, 512, 1, True), ("swizzle", "sm", 512, 512, 512, 2, True),
+            ("swizzle", "ce", 512, 256, 768, 4, "pairwise"),
+            ("swizzle", "sm", 1024, 8192, 28672 // world, 1, True),
+            ("swizzle", "sm", 1024, 8192, 28672 // world, 2, True),
+            ("swizzle", "ce", 1024, 8192, 28672 // world, 2, True),
+            ("swizzle", "ce", 1024, 8192, 28672 // world, 2, "pairwise")):
+        op = AllGatherGemm(ctx, rows, K, N, dt, plan=kind, comm=comm, timeout_ns=2_000_000_000, chunk_split=split,
+                           lockstep=lock)
         shards = [seeded(1000 + r, (rows, K), 1.0, dt, dev) for r in range(world)]
         b = seeded(5000 + rank, (N, K), 0.02, dt, dev)
         full = torch.cat(shards, 0)
@@ -98,15 +101,17 @@ def main():
         del op
 
     # comm "sm": the epilogue pushes tiles to the peers; "ce": local slabs moved by copy engines
-    for kind, M, N, Kl, comm, split in (("direct", 256 * world, 512, 256, "sm", 1), ("a2a", 128 * world, 1024, 512, "sm", 1),
-                                        ("direct", 8192, 8192, 28672 // world, "sm", 1),
-                                        ("direct", 256 * world, 512, 256, "ce", 1), ("a2a", 128 * world, 1024, 512, "ce", 1),
-                                        ("direct", 512 * world, 512, 256, "sm", 2), ("direct", 512 * world, 512, 256, "ce", 2),
-                                        ("direct", 8192, 8192, 28672 // world, "sm", 2),
-                                        ("direct", 8192, 8192, 28672 // world, "ce", 2)):
+    for kind, M, N, Kl, comm, split, red in (
+            ("direct", 256 * world, 512, 256, "sm", 1, "epilogue"), ("a2a", 128 * world, 1024, 512, "sm", 1, "epilogue"),
+            ("direct", 8192, 8192, 28672 // world, "sm", 1, "epilogue"),
+            ("direct", 256 * world, 512, 256, "ce", 1, "epilogue"), ("a2a", 128 * world, 1024, 512, "ce", 1, "pass"),
+            ("direct", 512 * world, 512, 256, "sm", 2, "pass"), ("direct", 512 * world, 512, 256, "ce", 2, "epilogue"),
+            ("direct", 8192, 8192, 28672 // world, "sm", 2, "epilogue"),
+            ("direct", 8192, 8192, 28672 // world, "ce", 2, "pass"), ("direct", 8192, 8192, 28672 // world, "ce", 1, "pass")):
         if split > 1 and (M // world) % (split * 128):
             continue
-        op = GemmReduceScatter(ctx, M, N, dt, plan=kind, timeout_ns=2_000_000_000, comm=comm, chunk_split=split)
+        op = GemmReduceScatter(ctx, M, N, dt, plan=kind, timeout_ns=2_000_000_000, comm=comm, chunk_split=split,
+                               reduce=red)
         a = seeded(2000 + rank, (M, Kl), 1.0, dt, dev)
         b = seeded(3000 + rank, (N, Kl), 0.02, dt, dev)
         part = a.float() @ b.float().t()
@@ -117,16 +122,41 @@ def main():
             ctx.check()
             e, et = tile_ok(out, ref)
             if not (e < TOL and et < TOL):
-                failures.append(f"gemm_rs {kind}/{comm}/split{split} M={M} it={it} rank={rank}: relerr={e:.3e} tile={et:.3e}")
+                failures.append(f"gemm_rs {kind}/{comm}/split{split}/{red} M={M} it={it} rank={rank}: relerr={e:.3e} tile={et:.3e}")
         del op, part, ref
 
+    # ---- the same operator called back to back (no host synchronisation between the calls): a rank may
+    # be one call ahead of a peer; both reduce modes, one and two copy streams
+    M, N, Kl = 8192, 8192, 28672 // world
+    a = seeded(2000 + rank, (M, Kl), 1.0, dt, dev)
+    b = seeded(3000 + rank, (N, Kl), 0.02, dt, dev)
+    part = a.float() @ b.float().t()
+    dist.all_reduce(part)
+    ref = part[rank * (M // world) : (rank + 1) * (M // world)].clone()
+    del part
+    for red, streams, comm in (("epilogue", 2, "ce"), ("pass", 2, "ce"), ("pass", 1, "ce"), ("pass", 1, "sm")):
+        op = GemmReduceScatter(ctx, M, N, dt, plan="direct", timeout_ns=2_000_000_000, comm=comm, copy_streams=streams,
+                               reduce=red)
+        outs = [torch.empty(M // world, N, dtype=dt, device=dev) for _ in range(2)]
+        for it in range(12):
+            op(a, b, outs[it & 1])
+        ctx.check()
+        for o in outs:
+            e, et = tile_ok(o, ref)
+            if not (e < TOL and et < TOL):
+                failures.append(f"gemm_rs back to back {comm}/{red}/{streams} streams rank={rank}: relerr={e:.3e} tile={et:.3e}")
+        del op, outs
+    del ref
+
     # ---- GEMM + all-reduce: reduce-scatter in the kernel, reduced rows all-gathered by copy engines
-    for M, N, Kl, splits, pieces, comm in ((512 * world, 512, 256, 1, 1, "ce"), (1024 * world, 512, 256, 2, 2, "ce"),
-                                           (512 * world, 768, 128, 2, 1, "sm"), (8192, 8192, 28672 // world, 4, 1, "ce")):
+    for M, N, Kl, splits, pieces, comm, red in (
+            (512 * world, 512, 256, 1, 1, "ce", "epilogue"), (1024 * world, 512, 256, 2, 2, "ce", "pass"),
+            (512 * world, 768, 128, 2, 1, "sm", "epilogue"), (8192, 8192, 28672 // world, 4, 1, "ce", "epilogue"),
+            (8192, 8192, 28672 // world, 1, 1, "ce", "pass")):
         if (M // splits // world) % (pieces * 128):
             continue
         op = GemmAllReduce(ctx, M, N, dt, num_splits=splits, chunk_split=pieces, comm=comm, timeout_ns=2_000_000_000,
-                           sync_after=True)
+                           sync_after=True, reduce=red)
         a = seeded(2500 + rank, (M, Kl), 1.0, dt, dev)
         b = seeded(3500 + rank, (N, Kl), 0.02, dt, dev)
         ref = a.float() @ b.float().t()
@@ -139,7 +169,7 @@ def main():
             ctx.check()
             e, et = tile_ok(out, ref)
             if not (e < TOL and et < TOL):
-                failures.append(f"gemm_ar M={M} splits={splits} pieces={pieces} {comm} it={it} rank={rank}: "
+                failures.append(f"gemm_ar M={M} splits={splits} pieces={pieces} {comm} {red} it={it} rank={rank}: "
                                 f"relerr={e:.3e} tile={et:.3e}")
         del op, ref
 

@@ -347,12 +347,14 @@ def _rs_phase_schedule(src, rsig, rank, own: bool):
 
 @pytest.mark.parametrize("world,M,N,Kl,split,transport", [(2, 1024, 512, 256, 2, "push"), (4, 2048, 256, 128, 2, "push"),
                                                           (2, 1024, 512, 256, 2, "local"), (4, 1536, 256, 128, 3, "push")])
-def test_fused_gemm_rs_with_split_slabs(world, M, N, Kl, split, transport, status):
+@pytest.mark.parametrize("reduce_pass", [False, True])
+def test_fused_gemm_rs_with_split_slabs(world, M, N, Kl, split, transport, reduce_pass, status):
     """Every slab leaves as ``split`` row pieces (flags of their own) and the rows kept by a rank are
     reduced piece by piece.  ``push``: the epilogue's TMA stores write the peers' staging slabs;
     ``local``: the epilogue fills the local send buffer and raises the local per-wave flags, and the
     test plays the transport (copy the rows, raise the receiver's flag).  256-row pieces run on the
-    CTA-pair kernel, 128-row pieces on the one-CTA kernel."""
+    CTA-pair kernel, 128-row pieces on the one-CTA kernel.  ``reduce_pass``: the staged partial sums
+    are added by the pass behind the kernel instead of the own tiles' epilogue."""
     from syncopate_b200 import _lib as L
     from syncopate_b200.computation.gemm import gemm_rs
     from syncopate_b200.computation.gemm.plan import rs_remote_signals, rs_transport_program
@@ -381,7 +383,7 @@ def test_fused_gemm_rs_with_split_slabs(world, M, N, Kl, split, transport, statu
                 sched, sig_sel, sel = _rs_phase_schedule(src, rsig, r, own)
                 kw = {}
                 if own:
-                    kw = dict(out_flags=torch.zeros(split, dtype=torch.int64, device="cuda"))
+                    kw = dict(out_flags=torch.zeros(split, dtype=torch.int64, device="cuda"), reduce_pass=reduce_pass)
                 if transport == "local" and not own:
                     send = torch.full((world, slab, N), float("nan"), dtype=dt, device="cuda")
                     send_flags = torch.zeros(len(sel), dtype=torch.int64, device="cuda")
@@ -412,3 +414,42 @@ def test_fused_gemm_rs_with_split_slabs(world, M, N, Kl, split, transport, statu
         for r in range(world):
             assert_gemm_close(outs[r], want[r], f"rank {r} epoch {epoch}")
             outs[r].zero_()
+
+
+def test_reduce_pass_with_a_missing_partial_sum_times_out_cleanly(status):
+    """The reduce pass behind the kernel waits with a bound: when a peer's partial sum never
+    arrives, the pass records the timeout, leaves the own partial sum in place, and the local
+    flag of the piece is still raised, so that nothing downstream is left waiting."""
+    from syncopate_b200 import _lib as L
+    from syncopate_b200.computation.gemm import gemm_rs
+    from syncopate_b200.computation.gemm.plan import rs_remote_signals
+    from syncopate_b200.operators import plan_reduce_scatter
+
+    world, M, N, Kl, dt = 2, 512, 256, 128, torch.bfloat16
+    slab = M // world
+    _gen, info, low = plan_reduce_scatter(world, M, N, dt, "direct")
+    src, dst = low[0]["src"], low[0]["dst"]
+    rsig = rs_remote_signals(info, 0, src)
+    sched, sig_sel, _sel = _rs_phase_schedule(src, rsig, 0, own=True)
+    a, b = _seeded(70, (M, Kl), 1.0, dt).cuda(), _seeded(71, (N, Kl), 0.02, dt).cuda()
+    stages = [torch.zeros(2, world, slab, N, dtype=dt, device="cuda") for _ in range(world)]
+    flags = [torch.zeros(max(info.recv_signal_num, 1), dtype=torch.int64, device="cuda") for _ in range(world)]
+    out = torch.zeros(slab, N, dtype=dt, device="cuda")
+    out_flags = torch.zeros(1, dtype=torch.int64, device="cuda")
+    counters = torch.zeros(130, dtype=torch.int32, device="cuda")
+    gemm_rs(a, b, out, sched, dst, sig_sel, L.Symm.of(0, [x.data_ptr() for x in stages]),
+            L.Symm.of(0, [x.data_ptr() for x in flags]), counters, epoch=1, timeout_ns=20_000_000, status=status,
+            out_flags=out_flags, reduce_pass=True)
+    torch.cuda.synchronize()
+    got = status.tolist()
+    assert got[0] == 1 and got[2] <= -2, got       # flag timeout, in a reduce wait
+    assert out_flags.tolist() == [1]
+    assert_gemm_close(out, a[:slab].float().cpu() @ b.float().cpu().t(), "own partial sum")
+    # the same launch succeeds once the partial sum is there
+    status.zero_()
+    flags[0].fill_(2)
+    gemm_rs(a, b, out, sched, dst, sig_sel, L.Symm.of(0, [x.data_ptr() for x in stages]),
+            L.Symm.of(0, [x.data_ptr() for x in flags]), counters, epoch=2, timeout_ns=20_000_000, status=status,
+            out_flags=out_flags, reduce_pass=True)
+    torch.cuda.synchronize()
+    assert status.tolist() == [0, 0, 0, 0] and out_flags.tolist() == [2]
