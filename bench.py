@@ -557,7 +557,7 @@ def run_own_arm(args):
         if not args.skip_alt_comm:
             alt = "sm" if args.rs_comm == "ce" else "ce"
             rs2 = GemmReduceScatter(ctx, RS_M, RS_N, dt, plan="direct", comm=alt, chunk_split=args.rs_split,
-                                    copy_streams=args.copy_streams)
+                                    copy_streams=args.copy_streams, reduce=args.rs_reduce)
             rs_other = timed(lambda: rs2(ra, rb, rout), n_blocks=max(3, blocks // 2), n_warm=3)
             rs_other["comm_mode"] = alt
             del rs2
@@ -872,7 +872,7 @@ def main():
     ap.add_argument("--chunk-split", type=int, default=2, help="row pieces per remote all-gather slab")
     ap.add_argument("--ag-transfer", default="pull", choices=["pull", "push"],
                     help="copy-engine all-gather: receivers pull, or owners push")
-    ap.add_argument("--rs-comm", default="ce", choices=["sm", "ce"],
+    ap.add_argument("--rs-comm", default="sm", choices=["sm", "ce"],
                     help="GEMM+RS transport: the epilogue's TMA stores (sm) or copy engines (ce)")
     ap.add_argument("--rs-split", type=int, default=1, help="row pieces per reduce-scatter slab")
     ap.add_argument("--rs-reduce", default="epilogue", choices=["epilogue", "pass"],

@@ -256,7 +256,7 @@ class GemmReduceScatter:
     def __init__(self, ctx: SymmetricContext, M: int, N: int, dtype=torch.bfloat16, plan: str = "direct",
                  num_sms: int = 0, block_n: int = 0, timeout_ns: int = 0, lockstep: bool = True, comm: str = "sm",
                  copy_streams: int = 2, chunk_split: int = 1, publish_pieces: bool = False, flag_stream: bool = True,
-                 reduce: str = "epilogue"):
+                 reduce: str = "pass"):
         """``comm="sm"``: the GEMM's epilogue stores each tile straight into the target rank's staging
         slab (TMA stores to peer memory).  ``comm="ce"``: the epilogue stores locally and raises a
         local flag per wave; side streams wait for the flag (a stream memory operation), move the
@@ -267,7 +267,10 @@ class GemmReduceScatter:
         ``reduce="epilogue"``: the tiles of the rows kept here wait for the staged partial sums and
         add them in their epilogue (one kernel).  ``reduce="pass"``: the kernel stores the own partial
         sum and a pass launched behind it adds the staged slabs with coalesced loads (and raises
-        ``out_flags``); the own partial sum is then rounded to 16 bits before the sum."""
+        ``out_flags``); the own partial sum is then rounded to 16 bits before the sum.  Measured on
+        eight GPUs at M = N = 8192, K = 3584 per rank: sm + pass 0.417 ms, ce + pass 0.44-0.46,
+        sm + epilogue 0.47, ce + epilogue 0.55 (the reduce waves sit at the end of the kernel, behind
+        the last arrival, where nothing overlaps their latency-bound reads)."""
         if comm not in ("sm", "ce"):
             raise ValueError("comm must be 'sm' or 'ce'")
         if reduce not in ("epilogue", "pass"):
@@ -364,8 +367,9 @@ class GemmAllReduce:
     The reference overlaps a library all-reduce per row slice with the producer GEMM
     (``build_all_reduce_plan(num_all_reduces=..., split_axis=0, compute_producer=True)``,
     tests/test_gemm_ar_collective.py:97-160).  Here every slice is a GEMM + reduce-scatter (partial
-    sums pushed to the slab's owner, fp32 reduction in the owner's epilogue) whose reduced rows are
-    then all-gathered by copy engines: the kernel raises a local flag per finished row piece, side
+    sums pushed to the slab's owner, fp32 reduction by the owner: in the reduce pass behind the kernel,
+    or in the own tiles' epilogue with ``reduce="epilogue"``) whose reduced rows are
+    then all-gathered by copy engines: a local flag is raised per finished row piece, side
     streams wait for it and push the rows to every peer's copy of ``out``.  With ``num_splits`` > 1
     the slices are separate launches, and the all-gather of one slice runs under the GEMM of the
     next.  ``out`` is a symmetric buffer that the peers write: read it after the call has returned
@@ -373,8 +377,8 @@ class GemmAllReduce:
     starts on any rank (``sync_after=True`` adds the barrier that guarantees the latter)."""
 
     def __init__(self, ctx: SymmetricContext, M: int, N: int, dtype=torch.bfloat16, num_splits: int = 1,
-                 chunk_split: int = 1, comm: str = "ce", copy_streams: int = 2, timeout_ns: int = 0,
-                 lockstep: bool = True, sync_after: bool = False, reduce: str = "epilogue"):
+                 chunk_split: int = 1, comm: str = "sm", copy_streams: int = 2, timeout_ns: int = 0,
+                 lockstep: bool = True, sync_after: bool = False, reduce: str = "pass"):
         if M % (num_splits * ctx.world):
             raise ValueError("M must be divisible by num_splits * world")
         self.ctx, self.world, self.rank = ctx, ctx.world, ctx.rank
