@@ -803,9 +803,11 @@ def run_own_arm(args):
             "gpu_launches": launches[0],
             "roofline": {"bound": "tensor", "achieved": per_gpu, "peak": peak, "unit": "TFLOP/s",
                          "frac": per_gpu / peak,
-                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel on this
-                         # workload, from an ncu capture of this very command
-                         "traffic": 610.7e6 if world == 1 else None,
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch of gemm2_kernel<256,7,0> on
+                         # this workload (557.4 MB read + 51.9 MB written, mean of three launches), from an ncu
+                         # capture of `bench.py --steps 2 --warmup 3 --skip-attention` with the library as built
+                         # from this tree
+                         "traffic": 609.4e6 if world == 1 else None,
                          "algorithmic_bytes": (M * K_DIM + n_local * K_DIM + M * n_local) * 2,
                          "peak_source": f"{peaks['source']} cuBLAS bf16 burst (MEASURED_PEAKS.json)",
                          "cublas_same_shape_ms": cublas["ms"],

@@ -84,33 +84,6 @@ __device__ __forceinline__ uint64_t f2_add(uint64_t a, uint64_t b) {
   asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
   return d;
 }
-// Of every eight pairs of a chunk, this many take their exponential on the FMA and integer pipes
-// (ex2_poly2) instead of the special-function unit: the unit's 4 results per clock and scheduler
-// are what bounds a warp's exponential phase, and the FMA pipe is mostly idle there.
-#ifndef SYN_ATTN_POLY_OF8
-#define SYN_ATTN_POLY_OF8 3
-#endif
-
-// 2^t for two values t <= 0 without the special-function unit.  t = j + f with j = round(t) (the
-// low mantissa bits of t + 1.5 * 2^23) and f in [-0.5, 0.5]; 2^f by a cubic fitted for the smallest
-// maximum relative error on that interval (7.5e-5, far below the 16-bit rounding of P); 2^j by
-// adding j to the exponent field.  Values below -126 (masked keys: -inf) give about 2^-126.
-__device__ __forceinline__ void ex2_poly2(float t0, float t1, uint32_t& p0, uint32_t& p1) {
-  constexpr float kMagic = 12582912.f;
-  const uint64_t t2 = f2_pack(fmaxf(t0, -126.f), fmaxf(t1, -126.f));
-  const uint64_t r2 = f2_add(t2, f2_pack(kMagic, kMagic));
-  const uint64_t j2 = f2_add(r2, f2_pack(-kMagic, -kMagic));
-  const uint64_t f2 = f2_fma(j2, f2_pack(-1.f, -1.f), t2);
-  uint64_t q2 = f2_fma(f2, f2_pack(0.0551716648f, 0.0551716648f), f2_pack(0.2426111251f, 0.2426111251f));
-  q2 = f2_fma(q2, f2, f2_pack(0.6932609677f, 0.6932609677f));
-  q2 = f2_fma(q2, f2, f2_pack(0.9999280572f, 0.9999280572f));
-  float q0, q1, r0, r1;
-  f2_unpack(q2, q0, q1);
-  f2_unpack(r2, r0, r1);
-  p0 = __float_as_uint(q0) + (__float_as_uint(r0) << 23);
-  p1 = __float_as_uint(q1) + (__float_as_uint(r1) << 23);
-}
-
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
@@ -545,13 +518,11 @@ __global__ void __launch_bounds__(ATTN2_THREADS, 1) attn2_kernel(const __grid_co
             float x0, x1;
             f2_unpack(f2_fma(f2_pack(__uint_as_float(sr[c][2 * i]), __uint_as_float(sr[c][2 * i + 1])), scale2, negm2),
                       x0, x1);
-            if ((i & 7) < SYN_ATTN_POLY_OF8) {
-              ex2_poly2(x0, x1, sr[c][2 * i], sr[c][2 * i + 1]);
-            } else {
-              sr[c][2 * i] = __float_as_uint(ex2_approx(x0));
-              sr[c][2 * i + 1] = __float_as_uint(ex2_approx(x1));
-            }
+            sr[c][2 * i] = __float_as_uint(x0);
+            sr[c][2 * i + 1] = __float_as_uint(x1);
           }
+#pragma unroll
+          for (int i = 0; i < 32; ++i) sr[c][i] = __float_as_uint(ex2_approx(__uint_as_float(sr[c][i])));
         };
         scale_exp(0);
 #pragma unroll
