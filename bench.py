@@ -877,7 +877,7 @@ def main():
     ap.add_argument("--rs-comm", default="sm", choices=["sm", "ce"],
                     help="GEMM+RS transport: the epilogue's TMA stores (sm) or copy engines (ce)")
     ap.add_argument("--rs-split", type=int, default=1, help="row pieces per reduce-scatter slab")
-    ap.add_argument("--rs-reduce", default="epilogue", choices=["epilogue", "pass"],
+    ap.add_argument("--rs-reduce", default="pass", choices=["epilogue", "pass"],
                     help="GEMM+RS / GEMM+AR: staged partial sums added in the own tiles' epilogue, or by a pass behind the kernel")
     ap.add_argument("--ar-splits", type=int, default=1, help="row slices of GEMM+AR (separate launches)")
     ap.add_argument("--copy-streams", type=int, default=1)
