@@ -501,6 +501,7 @@ def run_own_arm(args):
     rb = seeded(3000 + rank, (RS_N, rs_k), 0.02, dt).to(dev)
     rs_other = None
     rs_other_reduce = None
+    rs_reduce_mode = None
     rs_compute_only = None
     rs_trace_rows = None
     ar_result = None
@@ -508,6 +509,7 @@ def run_own_arm(args):
     if world > 1:
         rs = GemmReduceScatter(ctx, RS_M, RS_N, dt, plan="direct", comm=args.rs_comm, chunk_split=args.rs_split,
                                copy_streams=args.copy_streams, flag_stream=not args.no_flag_stream, reduce=args.rs_reduce)
+        rs_reduce_mode = rs.reduce
         rout = torch.empty(RS_M // world, RS_N, dtype=dt, device=dev)
         rs_t = timed(lambda: rs(ra, rb, rout), n_warm=3)
         # parity: fp32 product of this rank's operands, reduce-scattered with torch.distributed
@@ -561,7 +563,7 @@ def run_own_arm(args):
             rs_other = timed(lambda: rs2(ra, rb, rout), n_blocks=max(3, blocks // 2), n_warm=3)
             rs_other["comm_mode"] = alt
             del rs2
-            alt_red = "pass" if args.rs_reduce == "epilogue" else "epilogue"
+            alt_red = "pass" if rs.reduce == "epilogue" else "epilogue"
             rs3 = GemmReduceScatter(ctx, RS_M, RS_N, dt, plan="direct", comm=args.rs_comm, chunk_split=args.rs_split,
                                     copy_streams=args.copy_streams, flag_stream=not args.no_flag_stream, reduce=alt_red)
             rs_other_reduce = timed(lambda: rs3(ra, rb, rout), n_blocks=max(3, blocks // 2), n_warm=3)
@@ -828,7 +830,7 @@ def run_own_arm(args):
                             "fused_roofline_ms": rs_roof_ms, "frac_of_fused_roofline": rs_roof_ms / rs_ms,
                             "nvlink_gbs_achieved": rs_bytes / (rs_ms * 1e-3) / 1e9 if world > 1 else None,
                             "compute_only_ms": rs_compute_only["ms"] if rs_compute_only else None,
-                            "reduce_mode": args.rs_reduce if world > 1 else None,
+                            "reduce_mode": rs_reduce_mode,
                             "other_comm_mode": rs_other, "other_reduce_mode": rs_other_reduce},
                 **({"gemm_ar": ar_result} if ar_result is not None else {}),
                 **a2a_results,
@@ -877,7 +879,7 @@ def main():
     ap.add_argument("--rs-comm", default="sm", choices=["sm", "ce"],
                     help="GEMM+RS transport: the epilogue's TMA stores (sm) or copy engines (ce)")
     ap.add_argument("--rs-split", type=int, default=1, help="row pieces per reduce-scatter slab")
-    ap.add_argument("--rs-reduce", default="pass", choices=["epilogue", "pass"],
+    ap.add_argument("--rs-reduce", default="auto", choices=["auto", "epilogue", "pass"],
                     help="GEMM+RS / GEMM+AR: staged partial sums added in the own tiles' epilogue, or by a pass behind the kernel")
     ap.add_argument("--ar-splits", type=int, default=1, help="row slices of GEMM+AR (separate launches)")
     ap.add_argument("--copy-streams", type=int, default=1)

@@ -256,7 +256,7 @@ class GemmReduceScatter:
     def __init__(self, ctx: SymmetricContext, M: int, N: int, dtype=torch.bfloat16, plan: str = "direct",
                  num_sms: int = 0, block_n: int = 0, timeout_ns: int = 0, lockstep: bool = True, comm: str = "sm",
                  copy_streams: int = 2, chunk_split: int = 1, publish_pieces: bool = False, flag_stream: bool = True,
-                 reduce: str = "pass"):
+                 reduce: str = "auto"):
         """``comm="sm"``: the GEMM's epilogue stores each tile straight into the target rank's staging
         slab (TMA stores to peer memory).  ``comm="ce"``: the epilogue stores locally and raises a
         local flag per wave; side streams wait for the flag (a stream memory operation), move the
@@ -273,8 +273,14 @@ class GemmReduceScatter:
         the last arrival, where nothing overlaps their latency-bound reads)."""
         if comm not in ("sm", "ce"):
             raise ValueError("comm must be 'sm' or 'ce'")
-        if reduce not in ("epilogue", "pass"):
-            raise ValueError("reduce must be 'epilogue' or 'pass'")
+        if reduce not in ("auto", "epilogue", "pass"):
+            raise ValueError("reduce must be 'auto', 'epilogue' or 'pass'")
+        # "auto": the pass pays once seven slabs are staged (eight ranks: 0.40 ms against 0.47); with one
+        # or three staged slabs and waves that are long against a transfer the epilogue form is level
+        # or ahead (two ranks 1.49 against 1.62 ms, four ranks 0.71 against 0.71-0.79)
+        if reduce == "auto":
+            reduce = "pass" if ctx.world >= 6 else "epilogue"
+        self.reduce = reduce
         self.reduce_pass = reduce == "pass"
         self.ctx = ctx
         self.comm = comm
@@ -378,7 +384,7 @@ class GemmAllReduce:
 
     def __init__(self, ctx: SymmetricContext, M: int, N: int, dtype=torch.bfloat16, num_splits: int = 1,
                  chunk_split: int = 1, comm: str = "sm", copy_streams: int = 2, timeout_ns: int = 0,
-                 lockstep: bool = True, sync_after: bool = False, reduce: str = "pass"):
+                 lockstep: bool = True, sync_after: bool = False, reduce: str = "auto"):
         if M % (num_splits * ctx.world):
             raise ValueError("M must be divisible by num_splits * world")
         self.ctx, self.world, self.rank = ctx, ctx.world, ctx.rank
