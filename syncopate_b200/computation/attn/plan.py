@@ -62,6 +62,43 @@ def all_gather_wave_metadata(schedule, q_rows: int, axes: Dict[str, int], q_head
     return offsets, shapes, schedule.gen_signal_lists(), cum
 
 
+def merge_wave_tail(waves, keep: int):
+    """Joins the waves behind the first ``keep`` into as few waves as their key ranges allow: waves
+    that follow each other, cover the same (batch, head, query) box and whose key ranges are
+    adjacent in the buffer become one wave over the joined range, gated by the flag of the LAST of
+    them.  That flag implies the earlier ones when the chunks arrive in wave order (the comm warps
+    walk the rank's op list in order, and a chunk's flag rises only after every CTA has finished
+    its pieces of it).  Fewer waves = fewer visits of every query tile (one Q load, one merge through
+    the stored O per visit); the price is that the joined wave starts after its last chunk, which
+    is free once the transfers run ahead of the attention, i.e. for all but the first few waves.
+    ``waves`` = ``(offsets, shapes, signals, cum)`` as built by ``all_gather_wave_metadata``."""
+    offsets, shapes, signals, cum = waves
+    n = len(offsets)
+    if keep < 0 or keep >= n - 1:
+        return waves
+    out_o, out_s, out_g, out_c = [list(o) for o in offsets[:keep]], [list(x) for x in shapes[:keep]], list(signals[:keep]), list(cum[:keep])
+    i = keep
+    while i < n:
+        o, sh, g = list(offsets[i]), list(shapes[i]), signals[i]
+        j = i + 1
+        while j < n and offsets[j][:3] == o[:3] and shapes[j][:3] == sh[:3] and signals[j] >= 0:
+            if offsets[j][3] == o[3] + sh[3]:          # next chunk continues this range upwards
+                sh[3] += shapes[j][3]
+            elif offsets[j][3] + shapes[j][3] == o[3]:  # or downwards
+                o[3] = offsets[j][3]
+                sh[3] += shapes[j][3]
+            else:
+                break
+            g = signals[j]
+            j += 1
+        out_o.append(o)
+        out_s.append(sh)
+        out_g.append(g)
+        out_c.append(cum[j - 1])
+        i = j
+    return out_o, out_s, out_g, out_c
+
+
 # --------------------------------------------------------------------------- box copies
 def _strides(shape: Sequence[int]) -> List[int]:
     out, acc = [], 1
@@ -228,6 +265,7 @@ def zigzag_tables(world: int, rank: int, seq_total: int, block: int = 128):
 __all__ = [
     "all_to_all_wave_metadata",
     "all_gather_wave_metadata",
+    "merge_wave_tail",
     "box_copy_ops",
     "pull_ops_from_schedule",
     "push_ops_from_schedule",

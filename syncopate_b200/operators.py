@@ -612,6 +612,7 @@ from .computation.attn.plan import (
     all_gather_wave_metadata,
     all_to_all_wave_metadata,
     completion_signals,
+    merge_wave_tail,
     pull_ops_from_schedule,
     push_ops_from_schedule,
     zigzag_tables,
@@ -781,7 +782,11 @@ class ContextParallelAttention:
 
     def __init__(self, ctx, B: int, Hq: int, Hkv: int, S_local: int, D: int = 128, dtype=torch.bfloat16,
                  causal: bool = True, zigzag: bool = True, plan: str = "swizzle", inner_mesh_size: int = 2,
-                 sm_scale: Optional[float] = None, timeout_ns: int = 0, lockstep: bool = True, sync_after: bool = False):
+                 sm_scale: Optional[float] = None, timeout_ns: int = 0, lockstep: bool = True, sync_after: bool = False,
+                 merge_waves_after: int = -1):
+        """``merge_waves_after`` = k >= 1: the waves behind the first k are joined where their key ranges
+        are adjacent in the gathered buffer (``merge_wave_tail``): fewer visits per query tile once the
+        transfers run ahead of the attention.  -1 = one wave per chunk."""
         self.ctx, self.world, self.rank = ctx, ctx.world, ctx.rank
         self.lockstep, self.sync_after = lockstep, sync_after
         W = self.world
@@ -805,6 +810,8 @@ class ContextParallelAttention:
         self.flags = ctx.alloc((max(self.info.recv_signal_num, 1),), torch.int64)
         self.counters = torch.zeros(NUM_COUNTERS, dtype=torch.int32, device=ctx.device)
         self.waves = all_gather_wave_metadata(self.schedule, S_local, {"batch": 1, "head": 2, "seq": 3}, q_heads=Hq)
+        if merge_waves_after >= 1:
+            self.waves = merge_wave_tail(self.waves, merge_waves_after)
         self.ops = pull_ops_from_schedule(self.schedule, self.rank, W, self.kv_shape, self.kv_shape, dtype.itemsize,
                                           src_buf=0, dst_buf=0, gather_axis=3)
         self.comm, self._keep = _L.make_attn_comm(self.ops, [self.kv.symm], self.flags.symm, self.counters.data_ptr())

@@ -184,14 +184,19 @@ def test_ulysses_operator_emulated_ranks(world, B, H, S_local, causal):
 
 @pytest.mark.parametrize("world,Hq,Hkv,plan,zigzag", [(2, 4, 2, "swizzle", True), (4, 8, 2, "ring", True),
                                                        (4, 4, 4, "double_ring", False)])
-def test_context_parallel_operator_emulated_ranks(world, Hq, Hkv, plan, zigzag):
+@pytest.mark.parametrize("merge", [-1, 1])
+def test_context_parallel_operator_emulated_ranks(world, Hq, Hkv, plan, zigzag, merge):
+    """``merge`` = 1: the waves behind the first are joined where their key ranges are adjacent
+    (one flag, the last chunk's, gates the joined wave)."""
     from syncopate_b200.operators import ContextParallelAttention
     from syncopate_b200.runtime import EmulatedWorld
 
     B, S_local = 1, 256
     ew = EmulatedWorld(world)
     ops = [ContextParallelAttention(c, B, Hq, Hkv, S_local, 128, DT, causal=True, zigzag=zigzag, plan=plan,
-                                    timeout_ns=500_000_000) for c in ew.contexts]
+                                    timeout_ns=500_000_000, merge_waves_after=merge) for c in ew.contexts]
+    if merge >= 1 and world > 2:
+        assert any(len(op.waves[0]) < world for op in ops)   # something was joined
     kv = [_seeded(40 + r, (2, B, Hkv, S_local, 128)) for r in range(world)]
     q = [_seeded(60 + r, (B, Hq, S_local, 128)) for r in range(world)]
     full = torch.cat(kv, dim=3)
@@ -297,7 +302,8 @@ def test_cfg3_ulysses_world8_emulated_sampled_rows(kernel_choice):
 
 
 @pytest.mark.parametrize("kernel_choice", ["two_tile"], indirect=True)
-def test_cfg4_rank0_sampled_rows(kernel_choice):
+@pytest.mark.parametrize("merge", [-1, 3])
+def test_cfg4_rank0_sampled_rows(kernel_choice, merge):
     """Rank 0 of the context-parallel benchmark (64 query / 8 KV heads, 8192 local queries against
     65536 keys, zigzag positions, eight waves gated by the in-kernel K/V gather from eight emulated
     ranks): gathered K/V bit-exact, sampled query tiles against fp32 dense attention with the true
@@ -309,7 +315,7 @@ def test_cfg4_rank0_sampled_rows(kernel_choice):
     ew = EmulatedWorld(W)
     g = torch.Generator(device="cuda").manual_seed(8000)
     ops = [ContextParallelAttention(c, 1, Hq, Hkv, Sl, 128, DT, causal=True, zigzag=True, plan="swizzle",
-                                    timeout_ns=2_000_000_000) for c in ew.contexts]
+                                    timeout_ns=2_000_000_000, merge_waves_after=merge) for c in ew.contexts]
     for op in ops:
         op.kv.local.fill_(float("nan"))
         op.kv_shard.copy_(torch.randn(2, 1, Hkv, Sl, 128, generator=g, device="cuda", dtype=torch.float32).to(DT))
@@ -329,7 +335,7 @@ def test_cfg4_rank0_sampled_rows(kernel_choice):
             rows = torch.arange(t * 128, (t + 1) * 128, device="cuda")
             worst = max(worst, _sampled_rows_error(out[0, h], q[0, h], full[0, 0, h // (Hq // Hkv)],
                                                    full[1, 0, h // (Hq // Hkv)], rows, q_pos, k_pos))
-    print(f"cfg4 rank 0 (8 waves per row), sampled tiles: max-abs {worst:.2e}")
+    print(f"cfg4 rank 0 ({len(op.waves[0])} waves per row), sampled tiles: max-abs {worst:.2e}")
     assert worst < TOL
 
 

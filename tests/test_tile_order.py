@@ -28,3 +28,32 @@ def test_known_answer_one_wave():
 def test_known_answer_two_waves():
     got = tile_order([(0, 0), (2, 0)], [(2, 2), (2, 2)], 1, 1, 8)
     assert got == [(0, 0), (1, 0), (0, 1), (1, 1), (2, 0), (3, 0), (2, 1), (3, 1)]
+
+
+def test_merge_wave_tail_joins_adjacent_key_ranges():
+    """Wave list of rank 2 of 8 in swizzled order (chunks 2, 3, ..., 7, 0, 1): behind the first
+    ``keep`` waves, chunks that are adjacent in the buffer become one wave gated by the last flag."""
+    from syncopate_b200.computation.attn.plan import merge_wave_tail
+
+    rows = 8192
+    order = (2, 3, 4, 5, 6, 7, 0, 1)
+    offs = [[0, 0, 0, r * rows] for r in order]
+    shapes = [[1, 64, rows, rows] for _ in order]
+    sigs = [-1, 0, 1, 2, 3, 4, 5, 6]
+    cum = list(range(1, 9))
+    waves = (offs, shapes, sigs, cum)
+    assert merge_wave_tail(waves, -1) is waves
+    assert merge_wave_tail(waves, 7) is waves
+    o, s, g, c = merge_wave_tail(waves, 3)
+    assert [x[3] for x in o] == [2 * rows, 3 * rows, 4 * rows, 5 * rows, 0]
+    assert [x[3] for x in s] == [rows, rows, rows, 3 * rows, 2 * rows]
+    assert g == [-1, 0, 1, 4, 6] and c == [1, 2, 3, 6, 8]
+    # every key of every chunk is still covered exactly once
+    covered = sorted((x[3], x[3] + y[3]) for x, y in zip(o, s))
+    assert covered[0][0] == 0 and covered[-1][1] == 8 * rows
+    assert all(a[1] == b[0] for a, b in zip(covered, covered[1:]))
+    # a different query box is never joined
+    shapes2 = [list(x) for x in shapes]
+    shapes2[5][1] = 32
+    o2, _s2, _g2, _c2 = merge_wave_tail((offs, shapes2, sigs, cum), 3)
+    assert len(o2) == 6
