@@ -15,17 +15,53 @@ from syncopate_b200 import _lib as L
 
 
 # --------------------------------------------------------------------------- wave metadata
-def all_to_all_wave_metadata(schedule, axes: Dict[str, int]):
+def _runs_of(slabs):
+    """``[(offset, length)]`` sorted by offset -> the maximal contiguous runs ``[(offset, length)]``."""
+    out = []
+    for off, n in sorted(slabs):
+        if out and out[-1][0] + out[-1][1] == off:
+            out[-1] = (out[-1][0], out[-1][1] + n)
+        else:
+            out.append((off, n))
+    return out
+
+
+def all_to_all_wave_metadata(schedule, axes: Dict[str, int], causal: bool = False):
     """Waves for attention fed by a sequence all-to-all.  Slab n (Q, K and V rows of one source rank)
     arrives with flag n; once it is there the kernel can run (Q_n, KV_n) and, for every earlier slab
     j, (Q_j, KV_n) and (Q_n, KV_j).  Returns ``(offsets, shapes, signals, cum_rows)`` with 4-entry
-    rows (z, h, q, kv) in tokens; ``cum_rows`` counts Z * H * Q rows as the reference does."""
+    rows (z, h, q, kv) in tokens; ``cum_rows`` counts Z * H * Q rows as the reference does.
+
+    ``causal`` (positions = sequence offsets): a pair whose keys all lie behind its queries does no
+    work, so slab n only brings (Q_n, KV of every arrived slab at or below n) - one wave per
+    contiguous key range - and (Q of the arrived slabs above n, KV_n) - one wave per contiguous
+    query range.  All of them are gated by flag n, which implies the flags of the slabs that arrived
+    before (the comm warps walk the op list in order).  A query tile is then visited once per slab
+    that arrives after its own instead of once per slab."""
     offs_src = schedule.gen_block_offset_lists()
     shp_src = schedule.gen_block_shape_lists()
     sig_src = schedule.gen_signal_lists()
     b, h, s = axes["batch"], axes["head"], axes["seq"]
     offsets, shapes, signals, cum = [], [], [], []
     total = 0
+    if causal:
+        for n in range(len(shp_src)):
+            on, sn = offs_src[n], shp_src[n]
+            below = [(offs_src[j][s], shp_src[j][s]) for j in range(n) if offs_src[j][s] < on[s]]
+            above = [(offs_src[j][s], shp_src[j][s]) for j in range(n) if offs_src[j][s] > on[s]]
+            for k_off, k_len in _runs_of(below + [(on[s], sn[s])]):
+                offsets.append([on[b], on[h], on[s], k_off])
+                shapes.append([sn[b], sn[h], sn[s], k_len])
+                signals.append(sig_src[n])
+                total += sn[b] * sn[h] * sn[s]
+                cum.append(total)
+            for q_off, q_len in _runs_of(above):
+                offsets.append([on[b], on[h], q_off, on[s]])
+                shapes.append([sn[b], sn[h], q_len, sn[s]])
+                signals.append(sig_src[n])
+                total += sn[b] * sn[h] * q_len
+                cum.append(total)
+        return offsets, shapes, signals, cum
 
     def emit(q_wave, kv_wave, sig):
         nonlocal total

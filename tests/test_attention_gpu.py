@@ -149,14 +149,16 @@ def test_rejects_unsupported_shapes():
 
 
 @pytest.mark.parametrize("world,B,H,S_local,causal", [(2, 1, 4, 256, True), (4, 2, 4, 128, False)])
-def test_ulysses_operator_emulated_ranks(world, B, H, S_local, causal):
+@pytest.mark.parametrize("join", [False, True])
+def test_ulysses_operator_emulated_ranks(world, B, H, S_local, causal, join):
     """All ranks on one GPU: inbound all-to-all inside the attention kernel, outbound by the SM
     copy kernel; every rank's [B, S/W, H, D] result equals dense attention over the full sequence."""
     from syncopate_b200.operators import UlyssesAttention
     from syncopate_b200.runtime import EmulatedWorld
 
     ew = EmulatedWorld(world)
-    ops = [UlyssesAttention(c, B, H, S_local, 128, DT, causal=causal, timeout_ns=500_000_000) for c in ew.contexts]
+    ops = [UlyssesAttention(c, B, H, S_local, 128, DT, causal=causal, timeout_ns=500_000_000, join_waves=join)
+           for c in ew.contexts]
     qkv = [_seeded(20 + r, (3, B, H, S_local, 128)) for r in range(world)]
     for r in range(world):
         ops[r].qkv_src.local.copy_(qkv[r].cuda())
@@ -264,16 +266,21 @@ def test_cfg3_local_shape_sampled_rows(kernel_choice):
 
 
 @pytest.mark.parametrize("kernel_choice", ["two_tile"], indirect=True)
-def test_cfg3_ulysses_world8_emulated_sampled_rows(kernel_choice):
+@pytest.mark.parametrize("join", [False, True])
+def test_cfg3_ulysses_world8_emulated_sampled_rows(kernel_choice, join):
     """The Ulysses benchmark configuration itself on eight emulated ranks (32 heads, 4096 tokens per
-    rank): 64 (Q slab, KV slab) waves per rank gated by the in-kernel all-to-all, outbound copy,
-    and every rank's sampled output rows against fp32 dense attention over the full sequence."""
+    rank): 64 (Q slab, KV slab) waves per rank - or, joined, the 8 to 14 waves of contiguous key and
+    query ranges that the causal mask leaves - gated by the in-kernel all-to-all, the outbound
+    all-to-all, and every rank's sampled output rows against fp32 dense attention over the full
+    sequence."""
     from syncopate_b200.operators import UlyssesAttention
     from syncopate_b200.runtime import EmulatedWorld
 
     W, H, Sl = 8, 32, 4096
     ew = EmulatedWorld(W)
-    ops = [UlyssesAttention(c, 1, H, Sl, 128, DT, causal=True, timeout_ns=2_000_000_000) for c in ew.contexts]
+    ops = [UlyssesAttention(c, 1, H, Sl, 128, DT, causal=True, timeout_ns=2_000_000_000, join_waves=join)
+           for c in ew.contexts]
+    assert all((len(op.waves[0]) == 64) != join for op in ops)
     g = torch.Generator(device="cuda").manual_seed(7100)
     for op in ops:
         op.qkv_src.local.copy_(torch.randn(3, 1, H, Sl, 128, generator=g, device="cuda", dtype=torch.float32).to(DT))
