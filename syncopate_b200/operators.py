@@ -638,7 +638,8 @@ class UlyssesAttention:
     Per rank: ``qkv`` ``[3, B, H, S / world, D]`` in, ``[B, S / world, H, D]`` out.  The inbound
     all-to-all runs inside the attention kernel (comm warps pull the slabs in the plan's order, the
     tiles follow the triangular (Q slab, KV slab) order of the reference driver,
-    tests/test_all2all_attn_transform.py:58-117); the outbound one is an SM copy kernel launched
+    tests/test_all2all_attn_transform.py:58-117, with the pairs a causal mask leaves joined into
+    contiguous ranges); the outbound one is an SM copy kernel launched
     behind it (tests/test_attn_all2all_transform.py is the reference's overlapped form)."""
 
     __doc__ += _HAZARD_NOTE + """
