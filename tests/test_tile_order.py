@@ -57,3 +57,42 @@ def test_merge_wave_tail_joins_adjacent_key_ranges():
     shapes2[5][1] = 32
     o2, _s2, _g2, _c2 = merge_wave_tail((offs, shapes2, sigs, cum), 3)
     assert len(o2) == 6
+
+
+@pytest.mark.parametrize("order", [(0, 1, 2, 3, 4, 5, 6, 7), (2, 3, 4, 5, 6, 7, 0, 1), (7, 0, 1, 2, 3, 4, 5, 6), (1, 0)])
+def test_causal_all_to_all_waves_cover_every_visible_pair_once(order):
+    """The joined causal waves of the Ulysses operator: whatever the arrival order of the slabs,
+    every (query slab, key slab at or below it) pair is covered exactly once, no wave covers a pair
+    without a visible key, a wave is gated by the flag of the slab that arrives last among those it
+    touches, and there are far fewer waves than slab pairs."""
+    from syncopate_b200.computation.attn.plan import all_to_all_wave_metadata
+
+    rows = 4096
+
+    class Schedule:
+        def gen_block_offset_lists(self):
+            return [[0, 0, 0, r * rows, 0] for r in order]
+
+        def gen_block_shape_lists(self):
+            return [[3, 1, 4, rows, 128] for _ in order]
+
+        def gen_signal_lists(self):
+            return list(range(len(order)))
+
+    axes = {"batch": 1, "head": 2, "seq": 3}
+    offs, shapes, sigs, cum = all_to_all_wave_metadata(Schedule(), axes, causal=True)
+    arrival = {slab: step for step, slab in enumerate(order)}
+    seen = {}
+    for o, s, g in zip(offs, shapes, sigs):
+        assert o[:2] == [0, 0] and s[:2] == [1, 4]
+        touched = set()
+        for q in range(o[2] // rows, (o[2] + s[2]) // rows):
+            for k in range(o[3] // rows, (o[3] + s[3]) // rows):
+                seen[(q, k)] = seen.get((q, k), 0) + 1
+                touched |= {q, k}
+        assert g == max(arrival[t] for t in touched)
+    n = len(order)
+    assert seen == {(q, k): 1 for q in range(n) for k in range(q + 1)}
+    assert len(offs) <= 2 * n and cum[-1] == sum(s[0] * s[1] * s[2] for s in shapes)
+    # the un-joined form: one wave per ordered pair of slabs
+    assert len(all_to_all_wave_metadata(Schedule(), axes)[0]) == n * n
