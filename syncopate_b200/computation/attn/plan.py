@@ -26,7 +26,7 @@ def _runs_of(slabs):
     return out
 
 
-def all_to_all_wave_metadata(schedule, axes: Dict[str, int], causal: bool = False):
+def all_to_all_wave_metadata(schedule, axes: Dict[str, int], causal: bool = False, join: bool = False):
     """Waves for attention fed by a sequence all-to-all.  Slab n (Q, K and V rows of one source rank)
     arrives with flag n; once it is there the kernel can run (Q_n, KV_n) and, for every earlier slab
     j, (Q_j, KV_n) and (Q_n, KV_j).  Returns ``(offsets, shapes, signals, cum_rows)`` with 4-entry
@@ -37,18 +37,21 @@ def all_to_all_wave_metadata(schedule, axes: Dict[str, int], causal: bool = Fals
     contiguous key range - and (Q of the arrived slabs above n, KV_n) - one wave per contiguous
     query range.  All of them are gated by flag n, which implies the flags of the slabs that arrived
     before (the comm warps walk the op list in order).  A query tile is then visited once per slab
-    that arrives after its own instead of once per slab."""
+    that arrives after its own instead of once per slab.  ``join`` without ``causal``: the same
+    joining with every arrived slab on both sides (slab n's queries against all arrived keys, the
+    earlier slabs' queries against its keys)."""
     offs_src = schedule.gen_block_offset_lists()
     shp_src = schedule.gen_block_shape_lists()
     sig_src = schedule.gen_signal_lists()
     b, h, s = axes["batch"], axes["head"], axes["seq"]
     offsets, shapes, signals, cum = [], [], [], []
     total = 0
-    if causal:
+    if causal or join:
         for n in range(len(shp_src)):
             on, sn = offs_src[n], shp_src[n]
-            below = [(offs_src[j][s], shp_src[j][s]) for j in range(n) if offs_src[j][s] < on[s]]
-            above = [(offs_src[j][s], shp_src[j][s]) for j in range(n) if offs_src[j][s] > on[s]]
+            # slabs whose keys slab n's queries see / whose queries see slab n's keys
+            below = [(offs_src[j][s], shp_src[j][s]) for j in range(n) if not causal or offs_src[j][s] < on[s]]
+            above = [(offs_src[j][s], shp_src[j][s]) for j in range(n) if not causal or offs_src[j][s] > on[s]]
             for k_off, k_len in _runs_of(below + [(on[s], sn[s])]):
                 offsets.append([on[b], on[h], on[s], k_off])
                 shapes.append([sn[b], sn[h], sn[s], k_len])

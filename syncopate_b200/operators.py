@@ -649,9 +649,9 @@ class UlyssesAttention:
     def __init__(self, ctx, B: int, H: int, S_local: int, D: int = 128, dtype=torch.bfloat16, causal: bool = True,
                  sm_scale: Optional[float] = None, timeout_ns: int = 0, lockstep: bool = True, sync_after: bool = False,
                  overlap_out: bool = True, join_waves: bool = True):
-        """``join_waves`` (causal only): a slab's arrival opens one wave per contiguous range of keys
-        (its queries against every arrived slab at or below it) and of queries (the arrived slabs
-        above it against its keys) instead of one wave per pair of slabs, so that a query tile is
+        """``join_waves``: a slab's arrival opens one wave per contiguous range of keys (its queries
+        against every arrived slab - with a causal mask: at or below it) and of queries (the arrived
+        slabs - causal: above it - against its keys) instead of one wave per pair of slabs, so that a query tile is
         visited a few times instead of once per slab (``all_to_all_wave_metadata(causal=True)``).
         ``overlap_out``: the attention kernel sends every query tile's final rows to their rank
         itself, at the tile's last visit, while the other tiles are still being computed (the
@@ -678,7 +678,7 @@ class UlyssesAttention:
         self.in_flags = ctx.alloc((max(self.in_info.recv_signal_num, 1),), torch.int64)
         self.qkv_dst = torch.zeros(self.in_dst_shape, dtype=dtype, device=ctx.device)
         self.waves = all_to_all_wave_metadata(self.in_schedule, {"batch": 1, "head": 2, "seq": 3},
-                                              causal=causal and join_waves)
+                                              causal=causal and join_waves, join=join_waves)
         self.in_ops = pull_ops_from_schedule(self.in_schedule, self.rank, W, self.in_src_shape, self.in_dst_shape, es,
                                              src_buf=0, dst_buf=1)
         self.counters = torch.zeros(NUM_COUNTERS, dtype=torch.int32, device=ctx.device)

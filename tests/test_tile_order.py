@@ -96,3 +96,34 @@ def test_causal_all_to_all_waves_cover_every_visible_pair_once(order):
     assert len(offs) <= 2 * n and cum[-1] == sum(s[0] * s[1] * s[2] for s in shapes)
     # the un-joined form: one wave per ordered pair of slabs
     assert len(all_to_all_wave_metadata(Schedule(), axes)[0]) == n * n
+
+
+@pytest.mark.parametrize("order", [(0, 1, 2, 3), (2, 3, 0, 1), (1, 3, 0, 2)])
+def test_joined_all_to_all_waves_without_a_mask_cover_every_pair_once(order):
+    from syncopate_b200.computation.attn.plan import all_to_all_wave_metadata
+
+    rows = 512
+
+    class Schedule:
+        def gen_block_offset_lists(self):
+            return [[0, 0, 0, r * rows, 0] for r in order]
+
+        def gen_block_shape_lists(self):
+            return [[3, 2, 4, rows, 128] for _ in order]
+
+        def gen_signal_lists(self):
+            return list(range(len(order)))
+
+    offs, shapes, sigs, _cum = all_to_all_wave_metadata(Schedule(), {"batch": 1, "head": 2, "seq": 3}, join=True)
+    arrival = {slab: step for step, slab in enumerate(order)}
+    seen = {}
+    for o, s, g in zip(offs, shapes, sigs):
+        touched = set()
+        for q in range(o[2] // rows, (o[2] + s[2]) // rows):
+            for k in range(o[3] // rows, (o[3] + s[3]) // rows):
+                seen[(q, k)] = seen.get((q, k), 0) + 1
+                touched |= {q, k}
+        assert g == max(arrival[t] for t in touched)
+    n = len(order)
+    assert seen == {(q, k): 1 for q in range(n) for k in range(n)}
+    assert len(offs) < n * n
